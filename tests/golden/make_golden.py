@@ -1,0 +1,196 @@
+"""Generate the golden vectors under tests/golden/ by running the UNMODIFIED reference.
+
+Run once in a container that has the reference checked out (path in $PHASORKV_REFERENCE, default
+/root/reference); the produced .npz files are committed, this script is not needed to run the
+tests. Everything is seeded; sizes are small so the fixtures stay a few hundred KB.
+
+  python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+REF = os.environ.get("PHASORKV_REFERENCE", "/root/reference")
+sys.path.insert(0, REF)
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+from phasorkv import quant                                   # noqa: E402
+from phasorkv.factorize import Factorization                 # noqa: E402
+from phasorkv.kernels import nvfp4                           # noqa: E402
+from phasorkv.latent import PhasorKey                        # noqa: E402
+from phasorkv.rope import rope_phasors                       # noqa: E402
+from transformers.models.llama.modeling_llama import apply_rotary_pos_emb   # noqa: E402
+
+
+class _Rotary:
+    def __init__(self, inv_freq, scale=1.0):
+        self.inv_freq = inv_freq
+        self.attention_scaling = scale
+
+
+def nvfp4_cases():
+    g = torch.Generator().manual_seed(4401)
+    rows = []
+    second = torch.tensor([0.0125], dtype=torch.float32)
+    unit = float(second) * 1.0                                # block scale byte for 1.0 -> scale == second
+    # 1. exact E2M1 midpoints (ties) in a block whose scale is exactly `second` * 1.0 (amax = 6*second)
+    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    tie = torch.zeros(16)
+    tie[:7] = mids * unit
+    tie[7:14] = -mids * unit
+    tie[14] = 6.0 * unit
+    tie[15] = -6.0 * unit
+    rows.append(tie)
+    # 2. all-zero block, 3. tiny values that round to zero with a sign, 4. saturation of the block scale
+    rows.append(torch.zeros(16))
+    small = torch.zeros(16); small[0] = 6.0 * unit; small[1:] = -0.2 * unit
+    rows.append(small)
+    sat = torch.randn(16, generator=g) * 1e4
+    rows.append(sat)
+    # 5. scales in the E4M3 subnormal range and below (2^-9 steps; 2^-10 ties to zero)
+    for e in (-6, -7, -8, -9, -10, -11):
+        blk = torch.randn(16, generator=g)
+        blk = blk / blk.abs().max() * 6.0 * float(second) * 2.0 ** e
+        rows.append(blk)
+    # 6. scale ties in E4M3 (halfway between two scale codes)
+    for s in (1.0625, 1.1875, 17.0, 19.0, 0.001953125 * 1.5):
+        blk = torch.randn(16, generator=g)
+        blk = blk / blk.abs().max() * 6.0 * float(second) * s
+        rows.append(blk)
+    special = torch.stack(rows)                              # [n, 16]
+    pad = (-special.shape[0]) % 4
+    special = torch.cat([special, torch.zeros(pad, 16)])
+    special = special.reshape(-1, 64)
+    # 7. random rows over many decades
+    mag = torch.exp(torch.randn(96, 1, generator=g) * 3.0)
+    rnd = torch.randn(96, 64, generator=g) * mag * float(second)
+    x = torch.cat([special, rnd]).float()
+    codes, s, xhat = nvfp4.quantize_nv_block(x, "nvfp4", second)
+    fake = quant.block_quant(x, "nvfp4", -1, second)
+    assert torch.equal(fake, xhat)
+    out = dict(x=x.numpy(), second=second.numpy(), codes=codes.numpy(),
+               scales=s.view(torch.uint8).numpy(), xhat=xhat.numpy(),
+               packed=nvfp4.pack_nibbles(codes).numpy())
+    # dynamic second (quant.block_quant default) and the static rule
+    out["second_dynamic"] = (x.abs().amax().clamp_min(1e-30) / (448.0 * 6.0)).reshape(1).numpy()
+    var = torch.rand(64, generator=g) * 3.0
+    out["static_var"] = var.numpy()
+    out["static_second"] = quant.nv_static_second(var, "nvfp4").numpy()
+    np.savez_compressed(os.path.join(HERE, "nvfp4_cases.npz"), **out)
+    print("nvfp4_cases", x.shape)
+
+
+def inject(A, B, freq, n_q, n_kv, h, A_s=None, B_s=None, slow=None):
+    pk = object.__new__(PhasorKey)
+    pk.A, pk.B, pk.freq = A, B, freq
+    pk.A_s, pk.B_s = A_s, B_s
+    pk.slow = slow if slow is not None else torch.zeros(0, dtype=torch.long)
+    pk.n_q, pk.n_kv, pk.h = n_q, n_kv, h
+    pk.R = B.shape[0]
+    pk.R_s = 0 if B_s is None else B_s.shape[0]
+    return pk
+
+
+def phasorkey_injected():
+    """Reference PhasorKey on injected random factors (the benchmark configurations' convention)."""
+    g = torch.Generator().manual_seed(4402)
+    D, n_q, n_kv, d = 192, 8, 2, 64
+    h = d // 2
+    T, Tq = 40, 3
+    inv_freq = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -2.0 * torch.arange(h, dtype=torch.float64) / d)
+    out = {}
+    for tag, n_slow in (("freq", 0), ("band", 4)):
+        ranks = torch.randint(0, 4, (h - n_slow,), generator=g)
+        ranks[0] = 2
+        freq = torch.repeat_interleave(torch.arange(h - n_slow), ranks)
+        R = freq.numel()
+        A = torch.complex(torch.randn(n_kv, R, generator=g), torch.randn(n_kv, R, generator=g)) * 0.3
+        B = torch.complex(torch.randn(R, D, generator=g), torch.randn(R, D, generator=g)) * 0.05
+        A_s = B_s = slow = None
+        if n_slow:
+            R_s = 8
+            slow = torch.arange(h - n_slow, h)
+            A_s = torch.randn(n_kv, 2 * n_slow, R_s, generator=g) * 0.3
+            B_s = torch.randn(R_s, D, generator=g) * 0.05
+        pk = inject(A, B, freq, n_q, n_kv, h, A_s, B_s, slow)
+        pos_k = torch.tensor([0, 1, 2, 3, 5, 17, 255, 4095, 4096, 29999, 30000, 65535, 131071] + list(range(100000, 100027)))
+        pos_q = torch.tensor([4096, 30000, 131072])
+        rot = _Rotary(inv_freq, 1.0)
+        ph_k = rope_phasors(rot, pos_k)
+        ph_q = rope_phasors(rot, pos_q)
+        x = torch.randn(T, D, generator=g)
+        q = torch.randn(n_q, Tq, d, generator=g)
+        rows = pk.write(x, ph_k)
+        qa = pk.absorb(q, ph_q)
+        S = pk.scores(qa, rows)
+        out.update({f"{tag}_A": A.numpy(), f"{tag}_B": B.numpy(), f"{tag}_freq": freq.numpy(),
+                    f"{tag}_x": x.numpy(), f"{tag}_q": q.numpy(), f"{tag}_pos_k": pos_k.numpy(),
+                    f"{tag}_pos_q": pos_q.numpy(), f"{tag}_ph_k": ph_k.numpy(), f"{tag}_ph_q": ph_q.numpy(),
+                    f"{tag}_rows": rows.numpy(), f"{tag}_qabs": qa.numpy(), f"{tag}_scores": S.numpy()})
+        if n_slow:
+            out.update({f"{tag}_A_s": A_s.numpy(), f"{tag}_B_s": B_s.numpy(), f"{tag}_slow": slow.numpy()})
+    out["inv_freq"] = inv_freq.numpy()
+    out["dims"] = np.array([D, n_q, n_kv, d])
+    np.savez_compressed(os.path.join(HERE, "phasorkey_injected.npz"), **out)
+    print("phasorkey_injected")
+
+
+def phasorkey_factorized():
+    """Reference Factorization -> PhasorKey (fp64) and the W_hat + HF-rotary identity (README.md:75-77)."""
+    g = torch.Generator().manual_seed(4403)
+    D, n_q, n_kv, d = 96, 8, 2, 32
+    h = d // 2
+    T, Tq = 24, 2
+    inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(h, dtype=torch.float64) / d)
+    W = torch.randn(n_kv * d, D, generator=g, dtype=torch.float64) / D ** 0.5
+    X = torch.randn(4 * D, D, generator=g, dtype=torch.float64)
+    Cx = X.T @ X / X.shape[0]
+    q2 = torch.rand(n_q, d, generator=g, dtype=torch.float64) + 0.1
+    out = dict(inv_freq=inv_freq.numpy(), dims=np.array([D, n_q, n_kv, d]))
+    rot = _Rotary(inv_freq, 1.0)
+    pos_k = torch.arange(29976, 30000)
+    pos_q = torch.tensor([30000, 30001])
+    ph_k, ph_q = rope_phasors(rot, pos_k), rope_phasors(rot, pos_q)
+    x = torch.randn(T, D, generator=g, dtype=torch.float64)
+    q = torch.randn(n_q, Tq, d, generator=g, dtype=torch.float64)
+    for tag, structure in (("freq", "freq"), ("band", "band4")):
+        fac = Factorization(W, Cx, q2, n_kv, d, structure, "xq", device="cpu")
+        ranks = fac.ranks(fac.full_size // 2)
+        pk = PhasorKey(fac, ranks, n_q)
+        rows = pk.write(x, ph_k)
+        qa = pk.absorb(q, ph_q)
+        S = pk.scores(qa, rows)
+        W_hat = fac.reconstruct(ranks)
+        # rebuild keys with W_hat and rotate with HF's own function; slow frequencies unrotated
+        pk_, pq_ = ph_k.clone(), ph_q.clone()
+        if fac.nope.any():
+            pk_[:, fac.nope] = pk_[0, 0].abs().to(pk_.dtype)
+            pq_[:, fac.nope] = pq_[0, 0].abs().to(pq_.dtype)
+        k = (x @ W_hat.T).reshape(T, n_kv, d).transpose(0, 1)[None]               # [1, n_kv, T, d]
+        cos_k, sin_k = torch.cat([pk_.real, pk_.real], -1)[None], torch.cat([pk_.imag, pk_.imag], -1)[None]
+        cos_q, sin_q = torch.cat([pq_.real, pq_.real], -1)[None], torch.cat([pq_.imag, pq_.imag], -1)[None]
+        _, kr = apply_rotary_pos_emb(k, k, cos_k, sin_k)
+        qr, _ = apply_rotary_pos_emb(q[None], q[None], cos_q, sin_q)
+        S2 = qr[0] @ kr[0].repeat_interleave(n_q // n_kv, dim=0).transpose(1, 2)
+        rel = ((S - S2).norm() / S2.norm()).item()
+        print(tag, "ranks", ranks, "identity rel", rel)
+        assert rel < 1e-12
+        out.update({f"{tag}_A": pk.A.numpy(), f"{tag}_B": pk.B.numpy(), f"{tag}_freq": pk.freq.numpy(),
+                    f"{tag}_rows": rows.numpy(), f"{tag}_qabs": qa.numpy(), f"{tag}_scores": S.numpy(),
+                    f"{tag}_W_hat": W_hat.numpy(), f"{tag}_scores_hf": S2.numpy(),
+                    f"{tag}_slow": pk.slow.numpy()})
+        if pk.R_s:
+            out.update({f"{tag}_A_s": pk.A_s.numpy(), f"{tag}_B_s": pk.B_s.numpy()})
+    out.update(x=x.numpy(), q=q.numpy(), pos_k=pos_k.numpy(), pos_q=pos_q.numpy(),
+               ph_k=ph_k.numpy(), ph_q=ph_q.numpy())
+    np.savez_compressed(os.path.join(HERE, "phasorkey_factorized.npz"), **out)
+    print("phasorkey_factorized")
+
+
+if __name__ == "__main__":
+    torch.set_num_threads(4)
+    nvfp4_cases()
+    phasorkey_injected()
+    phasorkey_factorized()
