@@ -1,0 +1,458 @@
+#!/usr/bin/env python
+"""Decode benchmark of the B200 PhasorKey path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--algo tc|simt]
+  python bench.py --impl reference ...        # the CPU PhasorKey path on the host cores
+
+One *step* is one decode step of a whole model-depth stack: for each of 32 layers, the newest token
+of every sequence is written into the NVFP4 latent / bf16 V cache, the query is absorbed, and
+split-T attention + merge produce the output. Inputs are seeded synthetic tensors with the shapes
+of Llama-3.1-8B (the reference benchmarks its kernels on random factors and caches too,
+scripts/bench_decode.py:4-8); cache contents are real writes of seeded hidden states.
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): every rank runs its own batch (batch
+parallel, no communication, weak scaling); in addition the token-sharded 128k configuration is
+timed (`seq_sharded`), where each rank attends over its slice of the tokens and the partial
+(o, m, l) triples are exchanged by one NCCL all-gather per layer.
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LAYERS = 32
+D_MODEL = 4096
+L2_BYTES = 126 * 2 ** 20
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
+    ap.add_argument("--algo", default=os.environ.get("PKV_BENCH_ALGO", "simt"), choices=["tc", "simt"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--batch", type=int, default=0, help="override the configuration's batch (profiling)")
+    ap.add_argument("--context", type=int, default=0, help="override the configuration's context (profiling)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--splits", type=int, default=0)
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# the GPU arm
+# ------------------------------------------------------------------------------------------------
+
+class Stack:
+    """32 layers of one configuration with their caches filled by real writes of seeded hidden states."""
+
+    def __init__(self, config: str, n_layers: int, device, algo: str, seed: int, batch: int = 0, context: int = 0,
+                 n_split: int = 0):
+        from phasorkv_b200 import synth
+        from phasorkv_b200.latent import PhasorKey
+        c = synth.CONFIGS[config]
+        self.config, self.algo = config, algo
+        self.B = batch or c["batch"]
+        self.T = context or c["context"]
+        self.device = device
+        self.simt = algo == "simt"
+        self.layers, self.caches = [], []
+        g = torch.Generator(device=device).manual_seed(seed)
+        for l in range(n_layers):
+            pk = PhasorKey.from_spec(synth.make_layer(config, l), device=device)
+            self.layers.append(pk)
+        pk0 = self.layers[0]
+        self.n_q, self.n_kv, self.d = pk0.n_q, pk0.n_kv, pk0.head_dim
+        self.W = pk0.cache_width
+        # tensor scale per layer: the reference's static rule on a 4096-token calibration write
+        n_out = max(1, round(0.01 * D_MODEL))
+        self.outliers = torch.randperm(D_MODEL, generator=g, device=device)[:n_out]
+        xc = self._hidden(g, 4096)
+        pos = torch.arange(4096, dtype=torch.int32, device=device)
+        rows = torch.empty((4096, self.W), dtype=torch.float32, device=device)
+        for pk in self.layers:
+            pk.write_paged(None, xc, pos, None, latent_out=rows)
+            pk.calibrate_second(rows)
+        del rows, xc
+        for pk in self.layers:
+            self.caches.append(pk.new_cache(self.B, self.T))
+        chunk = 16384
+        for b in range(self.B):
+            for t0 in range(0, self.T, chunk):
+                n = min(chunk, self.T - t0)
+                x = self._hidden(g, n).to(torch.bfloat16)
+                lp = torch.arange(t0, t0 + n, dtype=torch.int32, device=device)
+                seq = torch.full((n,), b, dtype=torch.int32, device=device)
+                for pk, cache in zip(self.layers, self.caches):
+                    slots = cache.slots(seq, lp)
+                    pk.write_paged(cache, x, lp, slots)
+                    cache.v.view(-1, self.n_kv * self.d)[slots.long()] = torch.randn(
+                        (n, self.n_kv * self.d), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        for cache in self.caches:
+            cache.seqlens.fill_(self.T)
+        self.n_split = n_split or pk0.default_splits(self.B, self.T, self.simt)
+        self.ws = [pk0.workspace(self.B, self.n_split) for _ in range(2)]
+        # per-step inputs (all layers): newest hidden state, its V row, the query; output buffer
+        L = n_layers
+        self.x_new = torch.empty((L, self.B, D_MODEL), dtype=torch.bfloat16, device=device)
+        self.v_new = torch.empty((L, self.B, self.n_kv * self.d), dtype=torch.bfloat16, device=device)
+        self.q = torch.empty((L, self.B, self.n_q, self.d), dtype=torch.float32, device=device)
+        self.out = torch.empty((L, self.B, self.n_q, self.d), dtype=torch.float32, device=device)
+        self.x_new.copy_(self._hidden(g, L * self.B).view(L, self.B, D_MODEL))
+        self.v_new.copy_(torch.randn(self.v_new.shape, generator=g, device=device))
+        self.q.copy_(torch.randn(self.q.shape, generator=g, device=device))
+        self.qpos = torch.full((self.B,), self.T, dtype=torch.int32, device=device)
+        self.wpos = torch.full((self.B,), self.T - 1, dtype=torch.int32, device=device)
+        seq = torch.arange(self.B, dtype=torch.int32, device=device)
+        self.wslots = [c.slots(seq, self.wpos) for c in self.caches]
+        self.launches_per_layer = 0
+
+    def _hidden(self, g, n):
+        x = torch.randn((n, D_MODEL), generator=g, device=self.device, dtype=torch.float32)
+        x[:, self.outliers] *= 20.0
+        return x
+
+    def step(self, events=None, scores_only=False, write=True):
+        """One decode step over all layers. `events`: list receiving (start, end) CUDA events around
+        each attention launch."""
+        n = 0
+        for l, (pk, cache) in enumerate(zip(self.layers, self.caches)):
+            ws = self.ws[l & 1]
+            if write:
+                pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], scratch=ws.wscratch)
+                cache.write_v(self.v_new[l], self.wslots[l])
+                n += 3
+            pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only)
+            if events is not None:
+                e1.record()
+                events.append((e0, e1))
+            pk.merge_step(ws, out=self.out[l])
+            n += 3
+        self.launches_per_layer = n // len(self.layers)
+        return n
+
+    # bytes one attention launch must move (per layer): NVFP4 codes + scales, and bf16 V
+    def bytes_k(self):
+        return self.B * self.T * (self.W // 2 + self.W // 16)
+
+    def bytes_full(self):
+        return self.bytes_k() + self.B * self.T * self.n_kv * self.d * 2
+
+
+def timed(fn, steps, warmup, dist=None):
+    """W warm-up calls, then exactly K calls between barrier + synchronize; device time by CUDA events."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = a.elapsed_time(b)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t)
+    return ms / steps
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def run_b200(args):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist_.init_process_group("nccl", device_id=device)
+        dist = dist_
+    from phasorkv_b200 import _lib
+    _lib.check(_lib.load().pkv_device_check(), "pkv_device_check")
+
+    st = Stack(args.workload, args.layers, device, args.algo, seed=1234 + rank, batch=args.batch, context=args.context,
+               n_split=args.splits)
+    torch.cuda.synchronize()
+
+    # ---- device-resident timing, with per-launch events around the attention kernel
+    events = []
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches = {"n": 0}
+
+    def full_step():
+        launches["n"] += st.step(events=events)
+    ms_step = timed(full_step, args.steps, args.warmup, dist)
+    clocks = sampler.stop()
+    timed_events = events[-args.steps * args.layers:]
+    attn_ms = sum(a.elapsed_time(b) for a, b in timed_events) / len(timed_events)
+    gpu_launches = st.launches_per_layer * args.layers * args.steps
+
+    # ---- K path only (logits + log-sum-exp, V never read): the "K-path us/layer" of the metric
+    ev_k = []
+    ms_k = timed(lambda: st.step(events=ev_k, scores_only=True, write=False), max(2, args.steps // 2), 2, dist)
+    k_events = ev_k[-max(2, args.steps // 2) * args.layers:]
+    attn_k_ms = sum(a.elapsed_time(b) for a, b in k_events) / len(k_events)
+
+    # ---- end to end through the host API: pinned host inputs in, outputs back, every step
+    L = args.layers
+    hx = torch.empty(st.x_new.shape, dtype=st.x_new.dtype).pin_memory()
+    hv = torch.empty(st.v_new.shape, dtype=st.v_new.dtype).pin_memory()
+    hq = torch.empty(st.q.shape, dtype=st.q.dtype).pin_memory()
+    ho = torch.empty(st.out.shape, dtype=st.out.dtype).pin_memory()
+    hx.copy_(st.x_new); hv.copy_(st.v_new); hq.copy_(st.q)
+
+    def e2e_step():
+        st.x_new.copy_(hx, non_blocking=True)
+        st.v_new.copy_(hv, non_blocking=True)
+        st.q.copy_(hq, non_blocking=True)
+        st.step()
+        ho.copy_(st.out, non_blocking=True)
+    ms_e2e = timed(e2e_step, args.steps, args.warmup, dist)
+    h2d = hx.numel() * hx.element_size() + hv.numel() * hv.element_size() + hq.numel() * hq.element_size()
+    d2h = ho.numel() * ho.element_size()
+
+    # ---- token-sharded long context (cfg4): the same pools viewed as B=4, T=131072/world per rank
+    sharded = None
+    if not args.no_sharded and args.workload == "cfg2" and not args.batch and not args.context:
+        sharded = run_sharded(st, args, dist, world)
+
+    pk, src = peaks()
+    achieved = st.bytes_full() / (attn_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+            "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": src,
+            "kernel": "pkv_attn_%s" % args.algo, "bytes_per_launch": st.bytes_full(),
+            "us_per_launch": round(attn_ms * 1e3, 2)}
+    line = {
+        "metric": "decode tokens/s (B=%d, T=%d, %d layers; K-path us/layer and HBM GB/s beside it)" % (st.B, st.T, L),
+        "value": round(world * st.B / (ms_step * 1e-3), 2), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V",
+        "data": "synthetic",
+        "config": {"workload": "%s: Llama-3.1-8B layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers"
+                   % (args.workload, st.B, st.T, st.W, st.n_kv, st.d, L),
+                   "algo": args.algo, "n_split": st.n_split, "parallelism": "batch-parallel x%d" % world,
+                   "l2": "inputs larger than L2 (%.2f GB streamed per layer, %.1f GB per step)"
+                         % (st.bytes_full() / 1e9, L * st.bytes_full() / 1e9)},
+        "k_path_us_per_layer": round(attn_k_ms * 1e3, 2),
+        "k_path_gbs": round(st.bytes_k() / (attn_k_ms * 1e-3) / 1e9, 1),
+        "full_us_per_layer": round(ms_step * 1e3 / L, 2),
+        "hbm_gbs": round(achieved, 1),
+        "roofline": roof,
+        "e2e": {"value": round(world * st.B / (ms_e2e * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": gpu_launches,
+        "clocks": clocks,
+    }
+    if sharded is not None:
+        line["seq_sharded"] = sharded
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=15.0)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_sharded(st, args, dist, world):
+    """cfg4: B=4, T=131072 with the token axis split evenly over the ranks; one all-gather per layer."""
+    B4, T4 = 4, 131072
+    Tl = T4 // world
+    pages = Tl // 128
+    dev = st.device
+    pt = torch.arange(B4 * pages, dtype=torch.int32, device=dev).reshape(B4, pages)
+    seqlens = torch.full((B4,), Tl, dtype=torch.int32, device=dev)
+    pk0 = st.layers[0]
+    n_split = max(1, min(pages, (torch.cuda.get_device_properties(dev).multi_processor_count * (3 if st.simt else 1)) // B4))
+    ws = pk0.workspace(B4, n_split)
+    gathered = torch.empty((world, B4, st.n_q, st.d + 2), dtype=torch.float32, device=dev)
+    out = torch.empty((B4, st.n_q, st.d), dtype=torch.float32, device=dev)
+    qpos = torch.full((B4,), T4, dtype=torch.int32, device=dev)
+    saved = [(c.page_table, c.seqlens, c.max_pages) for c in st.caches]
+
+    def step():
+        for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
+            pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
+            pk.attend_step(cache, ws, simt=st.simt)
+            if world > 1:
+                pk.merge_step(ws, normalise=False, packed=True)
+                dist.all_gather_into_tensor(gathered, ws.packed)
+                pk.merge_gathered(gathered, out)
+            else:
+                pk.merge_step(ws)
+    for c in st.caches:
+        c.page_table, c.seqlens, c.max_pages = pt, seqlens, pages
+    try:
+        ms = timed(step, args.steps, args.warmup, dist)
+    finally:
+        for c, s in zip(st.caches, saved):
+            c.page_table, c.seqlens, c.max_pages = s
+    per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
+    return {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, args.layers),
+            "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
+            "scaling": "strong", "collective": "all_gather of [B,H,d+2] fp32 per layer" if world > 1 else "none",
+            "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
+            "hbm_gbs_per_gpu": round(per_gpu_bytes * args.layers / (ms * 1e-3) / 1e9, 1)}
+
+
+# ------------------------------------------------------------------------------------------------
+# the CPU arm: the reference's PhasorKey arithmetic (oracle port) on the host cores
+# ------------------------------------------------------------------------------------------------
+
+def cpu_sample(workload: str, n_seq: int = 1):
+    """One (layer, sequence) unit of the workload prepared for the CPU path; returns a closure that
+    runs absorb + scores + softmax + P.V once, and the unit's description."""
+    from oracle import phasor_oracle as po
+    from phasorkv_b200 import synth
+    c = synth.CONFIGS[workload]
+    T = c["context"]
+    spec = synth.make_layer(workload, 0)
+    pk = po.PhasorKeyOracle.from_spec(spec)
+    gen = torch.Generator().manual_seed(99)
+    rows = []
+    for t0 in range(0, T, 4096):
+        x = synth.make_hidden(gen, 4096)
+        rows.append(pk.write(x, po.rope_phasors(spec.inv_freq, torch.arange(t0, t0 + 4096))))
+    rows = torch.cat(rows)
+    second = po.nv_static_second(rows[:4096].var(0))
+    rows = po.nvfp4_quantize(rows, second)[2]                      # the dequantised latent, fp32 [T, W]
+    V = synth.make_values(gen, T, spec.n_kv, spec.head_dim)
+    q = synth.make_query(gen, 1, spec.n_q, spec.head_dim)[0]
+    ph_q = po.rope_phasors(spec.inv_freq, torch.tensor([T]))
+
+    def unit():
+        return po.decode_step(pk, q, ph_q, rows, V, spec.head_dim)
+    return unit, c
+
+
+def cpu_baseline(workload: str, budget_s: float = 15.0) -> dict:
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    unit, c = cpu_sample(workload)
+    unit(); unit()
+    ts = []
+    t_end = time.perf_counter() + budget_s
+    while len(ts) < 5 or (time.perf_counter() < t_end and len(ts) < 50):
+        t0 = time.perf_counter()
+        unit()
+        ts.append(time.perf_counter() - t0)
+    ts.sort()
+    t_unit = ts[len(ts) // 2]
+    step_s = t_unit * c["batch"] * N_LAYERS
+    return {"value": round(c["batch"] / step_s, 4), "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": "1 layer x 1 sequence of T=%d (absorb + scores + softmax + P.V, fp32 on the dequantised latent, "
+                      "bf16 V), median of %d runs = %.2f ms, scaled x%d sequences x%d layers"
+                      % (c["context"], len(ts), t_unit * 1e3, c["batch"], N_LAYERS)}
+
+
+def run_reference(args):
+    """--impl reference: the CPU path timed as the step itself; rank 0 only."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    unit, c = cpu_sample(args.workload)
+    for _ in range(max(1, min(args.warmup, 3))):
+        unit()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        unit()
+    t_unit = (time.perf_counter() - t0) / args.steps
+    step_s = t_unit * c["batch"] * N_LAYERS
+    val = round(c["batch"] / step_s, 4)
+    sample = ("each step = 1 layer x 1 sequence of T=%d through the oracle port of PhasorKey (absorb + scores + softmax + "
+              "P.V), %.2f ms; scaled x%d sequences x%d layers to a full decode step" % (c["context"], t_unit * 1e3, c["batch"], N_LAYERS))
+    line = {"impl": "reference",
+            "metric": "decode tokens/s (B=%d, T=%d, %d layers; K-path us/layer and HBM GB/s beside it)" % (c["batch"], c["context"], N_LAYERS),
+            "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(step_s * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "%s: Llama-3.1-8B layer shape, B=%d, T=%d, fp32 dequantised latent, bf16 V, %d layers"
+                       % (args.workload, c["batch"], c["context"], N_LAYERS)},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_b200(a)

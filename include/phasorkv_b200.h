@@ -1,0 +1,158 @@
+/* phasorkv_b200 -- C ABI of the B200 (sm_100a) PhasorKey decode path.
+ *
+ * One shared library, libphasorkv_b200.so, loaded with dlopen/ctypes. Every entry point
+ *   - is extern "C", takes plain pointers and sizes (no C++ or torch types),
+ *   - enqueues work on the CUDA stream it is given and returns without synchronising,
+ *   - allocates nothing: inputs, outputs and scratch are all owned by the caller,
+ *   - returns 0 on success or a negative pkv_status code (never throws, never exits).
+ * This is the convention of the reference's own FFI, which launches extern "C" kernels on torch's
+ * current stream with caller-owned buffers (phasorkv/kernels/cubin.py:34-55,
+ * phasorkv/kernels/latent_attn.py:610-629).  "file:line" citations below are paths inside the
+ * reference project and name the Python routine each entry point stands in for.
+ *
+ * Pointers named *_dev point to device memory of the current device; *_host to host memory.
+ */
+#ifndef PHASORKV_B200_H
+#define PHASORKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKV_PAGE_TOKENS 128          /* tokens per cache page */
+#define PKV_MAX_WIDTH   256          /* largest supported latent width W = 2R + R_s */
+#define PKV_QUERY_TERMS 4            /* NVFP4 residual terms of the absorbed query operand */
+#define PKV_SMALL_WRITE_TOKENS 64    /* pkv_cache_write spreads the projection over the GPU up to this n */
+
+enum pkv_status {
+    PKV_OK = 0,
+    PKV_ERR_INVALID = -1,            /* null pointer, negative size, misaligned buffer */
+    PKV_ERR_UNSUPPORTED = -2,        /* shape outside what the kernels are built for */
+    PKV_ERR_CUDA = -3,               /* a CUDA runtime call failed; see pkv_last_cuda_error */
+    PKV_ERR_ARCH = -4                /* the current device is not sm_100 */
+};
+
+enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
+
+/* flags of pkv_decode_attn */
+#define PKV_ATTN_SCORES_ONLY 1u      /* K path only: logits and log-sum-exp, V is not read */
+#define PKV_ATTN_SIMT        2u      /* CUDA-core scaffold kernel on the fp32 absorbed query */
+
+/* One layer's factors, in the attribute convention of phasorkv.latent.PhasorKey
+ * (phasorkv/latent.py:47-54).  All arrays live in device memory and belong to the caller. */
+typedef struct pkv_layer {
+    int32_t d_model;                 /* D */
+    int32_t n_q, n_kv, head_dim;     /* query heads, kv heads, d */
+    int32_t R, R_s, n_slow;          /* complex latent dims, real slow dims, slow frequencies */
+    float   attn_scale;              /* rotary attention_scaling (phasorkv/rope.py:31) */
+    float   second;                  /* fp32 tensor scale of this layer's NVFP4 latent */
+    const float*   Bw_dev;           /* [2R + R_s, D]: rows Re B | Im B | B_s */
+    const float*   A_re_dev;         /* [n_kv, R] */
+    const float*   A_im_dev;         /* [n_kv, R] */
+    const float*   A_s_dev;          /* [n_kv, 2*n_slow, R_s] or NULL */
+    const int32_t* freq_dev;         /* [R] frequency index of each complex latent dim */
+    const int32_t* slow_dev;         /* [n_slow] or NULL */
+    const double*  inv_freq_dev;     /* [head_dim/2] rotary inverse frequencies */
+} pkv_layer_t;
+
+/* The paged cache of one layer.  A page holds PKV_PAGE_TOKENS tokens.
+ *   latent page (pkv_latent_page_bytes(W) bytes, pool base 1024-byte aligned):
+ *     codes : 128 rows x RB bytes (RB = 64 if W <= 128 else 128), two E2M1 codes per byte, even
+ *             column in the low nibble (phasorkv/kernels/nvfp4.py:34-36); byte `o = row*RB + col/2`
+ *             is stored at `o ^ ((o >> 3) & (RB == 128 ? 0x70 : 0x30))`, the shared-memory swizzle
+ *             of a K-major tcgen05 operand, so a page is copied to shared memory verbatim.
+ *     scales: after the codes, one 512-byte block per 64 columns; the E4M3 scale of row r,
+ *             16-column block j sits at `(j/4)*512 + (r%32)*16 + (r/32)*4 + j%4`.
+ *   V page: [128][n_kv][head_dim] bf16, row-major.
+ * A token's place is its *slot*: page_index * 128 + row. */
+typedef struct pkv_cache {
+    uint8_t* latent_dev;
+    void*    v_dev;                  /* bf16, may be NULL when only the K path is used */
+    int32_t  n_pages;
+    int32_t  W;                      /* 2R + R_s, a multiple of 16, <= PKV_MAX_WIDTH */
+    int32_t  n_kv, head_dim;
+} pkv_cache_t;
+
+int pkv_abi_version(void);
+const char* pkv_status_string(int status);
+/* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
+int pkv_last_cuda_error(void);
+/* 0 when the current device can run the library (compute capability 10.x), else PKV_ERR_ARCH. */
+int pkv_device_check(void);
+
+int64_t pkv_latent_page_bytes(int32_t W);
+int64_t pkv_v_page_bytes(int32_t n_kv, int32_t head_dim);
+
+/* NVFP4 quantise-and-pack of given fp32 latent rows into the paged cache: the bit-exact
+ * counterpart of quantize_nv_block + pack_nibbles (phasorkv/kernels/nvfp4.py:34-55;
+ * rounding rules of phasorkv/quant.py:70-89).  rows_dev [n, W]; slots_dev [n]. */
+int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev,
+                      int32_t n_tokens, float second, void* stream);
+
+/* Fused cache write: c = x B^T (complex), rotation by e^{i theta t} * attn_scale, slow block
+ * unrotated, NVFP4 quantisation, paged store.  Replaces PhasorKey.write (phasorkv/latent.py:61-70)
+ * followed by the quantiser above.  x_dev [n, D] of x_dtype; slots_dev [n].  The phasor of token i is
+ * either computed from positions_dev[i] (angle position * inv_freq formed in double, as
+ * phasorkv/rope.py:29-32 does) or, when phasors_dev is given, read from it: [n, head_dim/2] complex64
+ * (re, im interleaved), the `ph` argument of the reference with attention_scaling already inside.
+ * latent_out_dev: optional fp32 [n, W] copy of the unquantised rows (what PhasorKey.write returns);
+ * cache may be NULL when only that copy is wanted.
+ * scratch_dev: optional fp32 scratch of n * 256 floats (16-byte aligned).  When it is given and
+ * n <= PKV_SMALL_WRITE_TOKENS (the decode-time write of one token per sequence) the projection is
+ * split by latent column over many SMs and staged through it; otherwise one CTA per 64 tokens does
+ * everything on chip and the scratch is not touched. */
+int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
+                    const int32_t* positions_dev, const float* phasors_dev, const int32_t* slots_dev,
+                    int32_t n_tokens, float* latent_out_dev, float* scratch_dev, void* stream);
+
+/* bf16 value rows v_dev [n, n_kv*head_dim] into the V pages at slots_dev [n]. */
+int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slots_dev, int32_t n_tokens,
+                void* stream);
+
+/* Read tokens back in the reference's layout (tests, debugging): any of the outputs may be NULL.
+ * rows_out [n, W] fp32 = value(code) * (scale * second) (phasorkv/kernels/nvfp4.py:55);
+ * codes_out [n, W/2] packed nibbles; scales_out [n, W/16] E4M3 bytes. */
+int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, float second,
+                   float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream);
+
+/* Query absorption, PhasorKey.absorb for one query position per sequence
+ * (phasorkv/latent.py:72-83).  q_dev [B, n_q, head_dim] fp32 pre-RoPE; positions_dev [B] or, as for
+ * pkv_cache_write, phasors_dev [B, head_dim/2] complex64 (one of the two must be given).
+ * qabs_out_dev: optional fp32 [B, n_q, W] in the reference layout [Re q' | Im q' | slow].
+ * qop_out_dev: optional tensor-core operand, pkv_query_operand_bytes(W) per sequence: the absorbed
+ * query as PKV_QUERY_TERMS NVFP4 residual terms (row = term*32 + head) in the same swizzled
+ * code / scale layout as a cache page, followed by n_q*PKV_QUERY_TERMS fp32 per-row scales. */
+int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
+               const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, void* stream);
+int64_t pkv_query_operand_bytes(int32_t W);
+
+/* Decode attention on the latent cache: scores (PhasorKey.scores, phasorkv/latent.py:85-88),
+ * softmax(S * head_dim^-0.5) and P.V with kv heads shared by n_q/n_kv query heads
+ * (phasorkv/metrics.py:23,29-35), as split-T flash decoding.
+ *   q_dev       : fp32 [B, n_q, W] (PKV_ATTN_SIMT) or the operand blob written by pkv_absorb
+ *   page_table  : [B, max_pages] page indices; seqlens [B] tokens per sequence
+ *   partials    : scratch AND result, fp32 [B, n_split, n_q, head_dim + 2]: per split the
+ *                 unnormalised output o[head_dim], the maximum m of the base-2 logits and
+ *                 l = sum 2^(s - m)
+ *   scores_out  : optional fp32 [B, n_q, scores_stride] unscaled scores (tests)
+ *   status_dev  : optional int32[4]; kernels record a give-up of a bounded wait or an index out
+ *                 of range here instead of trapping */
+int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
+                    const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
+                    int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
+                    float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, void* stream);
+
+/* Log-sum-exp merge of n_parts partial triples per (sequence, head): M = max m, w = 2^(m - M),
+ * O = sum w o / sum w l (phasorkv/kernels/dense_attn.py:72-74).  parts_dev is addressed as
+ * parts[b*stride_b + p*stride_p + head*(head_dim+2) + i].  out_dev: optional normalised
+ * [B, n_q, head_dim]; packed_out_dev: optional merged triple [B, n_q, head_dim+2] (what a rank
+ * contributes to the all-gather of a token-sharded sequence). */
+int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
+              int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PHASORKV_B200_H */

@@ -1,0 +1,102 @@
+// Shared definitions of the phasorkv_b200 CUDA library: page layout, NVFP4 arithmetic, error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/phasorkv_b200.h"
+
+#define PKV_LOG2E 1.4426950408889634f
+
+extern thread_local int g_pkv_last_cuda_error;
+
+#define PKV_CUDA_TRY(expr)                                   \
+    do {                                                     \
+        cudaError_t e__ = (expr);                            \
+        if (e__ != cudaSuccess) {                            \
+            g_pkv_last_cuda_error = (int)e__;                \
+            return PKV_ERR_CUDA;                             \
+        }                                                    \
+    } while (0)
+
+#define PKV_LAUNCH_CHECK() PKV_CUDA_TRY(cudaGetLastError())
+
+// ------------------------------------------------------------------------------------------------
+// page layout (documented in include/phasorkv_b200.h)
+// ------------------------------------------------------------------------------------------------
+
+__host__ __device__ __forceinline__ int pkv_padded_width(int W) { return W <= 128 ? 128 : 256; }
+__host__ __device__ __forceinline__ int pkv_row_bytes(int W) { return pkv_padded_width(W) / 2; }
+__host__ __device__ __forceinline__ int pkv_codes_bytes(int W) { return PKV_PAGE_TOKENS * pkv_row_bytes(W); }
+__host__ __device__ __forceinline__ int pkv_scales_bytes(int W) { return (pkv_padded_width(W) / 64) * 512; }
+__host__ __device__ __forceinline__ int pkv_page_bytes(int W) { return pkv_codes_bytes(W) + pkv_scales_bytes(W); }
+
+// byte offset inside the code region of (row, byte column) for a row pitch of RB bytes: the
+// 128-byte (RB = 128) or 64-byte (RB = 64) shared-memory swizzle applied to the linear offset
+__host__ __device__ __forceinline__ uint32_t pkv_code_offset(uint32_t row, uint32_t byte_col, uint32_t RB) {
+    uint32_t o = row * RB + byte_col;
+    return o ^ ((o >> 3) & (RB == 128 ? 0x70u : 0x30u));
+}
+
+// byte offset inside the scale region of (row, 16-column block j)
+__host__ __device__ __forceinline__ uint32_t pkv_scale_offset(uint32_t row, uint32_t j) {
+    return (j >> 2) * 512u + (row & 31u) * 16u + (row >> 5) * 4u + (j & 3u);
+}
+
+// ------------------------------------------------------------------------------------------------
+// NVFP4 arithmetic. Every step is a single correctly rounded fp32 operation in the order the
+// reference performs it (phasorkv/kernels/nvfp4.py:49-55): no reciprocal, no fused multiply-add.
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float pkv_e4m3_to_float(uint8_t b) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// round to nearest even with saturation; the input is already clamped to [0, 448]
+__device__ __forceinline__ uint8_t pkv_float_to_e4m3(float x) {
+    return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float pkv_e2m1_value(uint32_t code) {
+    // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 : code bits 0-2, sign bit 3
+    uint32_t m = code & 7u;
+    float v = (m < 2u) ? 0.5f * (float)m : (float)(2u + (m & 1u)) * (float)(1u << (m >> 1)) * 0.25f;
+    return (code & 8u) ? -v : v;
+}
+
+// E4M3 scale byte of a block with the given max magnitude
+__device__ __forceinline__ uint8_t pkv_block_scale_byte(float amax, float second) {
+    float t = __fdiv_rn(__fdiv_rn(amax, 6.0f), second);
+    t = fminf(fmaxf(t, 0.0f), 448.0f);
+    return pkv_float_to_e4m3(t);
+}
+
+// E2M1 code of x under `scale` (= e4m3 * second): midpoints are compared with ">" so that an
+// exact tie takes the lower magnitude, and a value that rounds to zero carries no sign
+__device__ __forceinline__ uint32_t pkv_e2m1_code(float x, float scale) {
+    if (!(scale > 0.0f)) return 0u;
+    float y = __fdiv_rn(x, fmaxf(scale, 1e-30f));
+    float a = fabsf(y);
+    uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+    return idx | ((idx != 0u && y < 0.0f) ? 8u : 0u);
+}
+
+// quantise 16 consecutive values; returns the 8 packed code bytes (low nibble = even column)
+__device__ __forceinline__ uint2 pkv_quantize_block16(const float (&v)[16], float second, uint8_t& scale_byte) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    scale_byte = pkv_block_scale_byte(amax, second);
+    float scale = __fmul_rn(pkv_e4m3_to_float(scale_byte), second);
+    uint32_t lo = 0u, hi = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= pkv_e2m1_code(v[i], scale) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= pkv_e2m1_code(v[8 + i], scale) << (4 * i);
+    return make_uint2(lo, hi);
+}
+
+__device__ __forceinline__ float pkv_bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }

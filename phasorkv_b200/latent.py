@@ -1,0 +1,356 @@
+"""Host side of the B200 PhasorKey path: the reference's ``phasorkv.latent.PhasorKey`` interface
+(constructor, attributes, ``write`` / ``absorb`` / ``scores``; phasorkv/latent.py:27-88) on top of
+the CUDA library, plus the batched, paged, quantised entry points a decode loop uses.
+
+All arithmetic of the path runs in libphasorkv_b200.so; torch is used for device memory, streams
+and index bookkeeping only. Nothing here falls back to a CPU or eager-torch implementation of the
+path: without the library or without a GPU the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import PAGE_TOKENS
+
+
+def rope_phasors(inv_freq: torch.Tensor, positions: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``scale * e^{i t theta_j}`` as complex128 [len(positions), h], the angle formed in float64
+    (same contract as phasorkv/rope.py:23-32, taking inv_freq instead of the rotary module)."""
+    ang = positions.to(torch.float64)[:, None] * inv_freq.to(device=positions.device, dtype=torch.float64)[None, :]
+    return torch.polar(torch.full_like(ang, float(scale)), ang)
+
+
+def _aligned_bytes(n: int, device, align: int = 1024) -> torch.Tensor:
+    """A zeroed uint8 tensor of n bytes whose address is a multiple of `align`."""
+    raw = torch.zeros(n + align, dtype=torch.uint8, device=device)
+    off = (-raw.data_ptr()) % align
+    return raw[off:off + n]
+
+
+class PagedLatentCache:
+    """Paged NVFP4 latent + bf16 V cache of one layer (layout in include/phasorkv_b200.h).
+
+    ``page_table[b, p]`` is the pool page holding tokens ``[128 p, 128 p + 128)`` of sequence b's
+    local cache; ``seqlens[b]`` counts the tokens stored. The reference has no paging: its packed
+    precedent is a dense [B, T, W/2] code tensor (phasorkv/kernels/latent_attn.py:207-212).
+    """
+
+    def __init__(self, W: int, n_kv: int, head_dim: int, batch: int, max_tokens: int, device="cuda",
+                 with_v: bool = True, n_pages: Optional[int] = None):
+        lib = _lib.load()
+        self.W, self.n_kv, self.head_dim, self.batch = W, n_kv, head_dim, batch
+        self.max_pages = (max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS
+        self.n_pages = batch * self.max_pages if n_pages is None else n_pages
+        self.page_bytes = int(lib.pkv_latent_page_bytes(W))
+        if self.page_bytes <= 0:
+            raise _lib.PhasorKVError(f"latent width {W} is not supported (multiple of 16, <= {_lib.MAX_WIDTH})")
+        self.device = torch.device(device)
+        self.latent = _aligned_bytes(self.n_pages * self.page_bytes, self.device)
+        self.v = (torch.zeros((self.n_pages * PAGE_TOKENS, n_kv, head_dim), dtype=torch.bfloat16, device=self.device)
+                  if with_v else None)
+        # contiguous default mapping: sequence b owns pages [b*max_pages, (b+1)*max_pages)
+        pt = torch.arange(batch * self.max_pages, dtype=torch.int32).reshape(batch, self.max_pages)
+        self.page_table = (pt % self.n_pages).to(self.device)
+        self.seqlens = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self.c = _lib.Cache(self.latent.data_ptr(), 0 if self.v is None else self.v.data_ptr(), self.n_pages, W,
+                            n_kv, head_dim)
+
+    def slots(self, seq: torch.Tensor, local_pos: torch.Tensor) -> torch.Tensor:
+        """Slot (page * 128 + row) of token `local_pos` of sequence `seq`; int32 tensors on the device."""
+        page = self.page_table[seq.long(), (local_pos // PAGE_TOKENS).long()]
+        return (page * PAGE_TOKENS + (local_pos % PAGE_TOKENS).to(torch.int32)).to(torch.int32)
+
+    def write_v(self, v: torch.Tensor, slots: torch.Tensor) -> None:
+        """bf16 value rows [n, n_kv, head_dim] into the V pages."""
+        v = v.to(torch.bfloat16).contiguous()
+        _lib.check(_lib.load().pkv_v_write(ctypes.byref(self.c), _lib.ptr(v), _lib.ptr(slots), v.shape[0],
+                                           _lib.current_stream()), "pkv_v_write")
+
+    def quantize_rows(self, rows: torch.Tensor, slots: torch.Tensor, second: float) -> None:
+        """Given fp32 latent rows [n, W] -> NVFP4 codes + scales in the pages (bit-exact quantiser)."""
+        rows = rows.to(torch.float32).contiguous()
+        _lib.check(_lib.load().pkv_quantize_rows(ctypes.byref(self.c), _lib.ptr(rows), _lib.ptr(slots), rows.shape[0],
+                                                 ctypes.c_float(second), _lib.current_stream()), "pkv_quantize_rows")
+
+    def read(self, slots: torch.Tensor, second: float, rows: bool = True, codes: bool = True):
+        """-> (rows fp32 [n, W] | None, packed codes uint8 [n, W/2] | None, scale bytes uint8 [n, W/16] | None)."""
+        n = slots.numel()
+        r = torch.empty((n, self.W), dtype=torch.float32, device=self.device) if rows else None
+        c = torch.empty((n, self.W // 2), dtype=torch.uint8, device=self.device) if codes else None
+        s = torch.empty((n, self.W // 16), dtype=torch.uint8, device=self.device) if codes else None
+        _lib.check(_lib.load().pkv_cache_read(ctypes.byref(self.c), _lib.ptr(slots), n, ctypes.c_float(second),
+                                              _lib.ptr(r), _lib.ptr(c), _lib.ptr(s), _lib.current_stream()),
+                   "pkv_cache_read")
+        return r, c, s
+
+
+class DecodeWorkspace:
+    """Caller-owned scratch of one decode call: absorbed query (fp32 and operand form), the split
+    partials, the output. Reused across layers and steps so that the timed path allocates nothing."""
+
+    def __init__(self, batch: int, n_q: int, head_dim: int, W: int, n_split: int, device):
+        lib = _lib.load()
+        self.batch, self.n_split = batch, n_split
+        self.qabs = torch.empty((batch, n_q, W), dtype=torch.float32, device=device)
+        self.qop_bytes = int(lib.pkv_query_operand_bytes(W))
+        self.qop = _aligned_bytes(batch * self.qop_bytes, device)
+        self.partials = torch.empty((batch, n_split, n_q, head_dim + 2), dtype=torch.float32, device=device)
+        self.packed = torch.empty((batch, n_q, head_dim + 2), dtype=torch.float32, device=device)
+        self.out = torch.empty((batch, n_q, head_dim), dtype=torch.float32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.wscratch = torch.empty((max(batch, 1), 256), dtype=torch.float32, device=device)   # decode-time write
+
+
+class PhasorKey:
+    """The phasor key cache of one layer.
+
+    Constructor and attributes follow the reference (phasorkv/latent.py:28-59): ``PhasorKey(fac,
+    ranks, n_q)`` takes a ``Factorization``-like object (``blocks`` with ``U, s2, sq, Mw, where,
+    cost``; ``nope``; ``n_kv``; ``d``; ``absorbed``) and builds ``A [n_kv, R]``, ``B [R, D]``,
+    ``freq``, ``energy``, ``slow``, ``A_s``, ``B_s`` with latent dims sorted by energy.
+    ``from_factors`` injects those arrays directly (synthetic layers).
+    """
+
+    def __init__(self, fac, ranks: Sequence[int], n_q: int, inv_freq: Optional[torch.Tensor] = None,
+                 attn_scale: float = 1.0, device="cuda"):
+        if not getattr(fac, "absorbed", False):
+            raise AssertionError("PhasorKey needs an absorbed layout ('freq' or 'bandN')")
+        a_cols, b_rows, freq, energy = [], [], [], []
+        A_s = B_s = None
+        for blk, r in zip(fac.blocks, ranks):
+            r = int(r)
+            top = blk.U[:, :r]
+            if blk.cost == 1:                                       # real slow band, scored without RoPE
+                if r:
+                    A_s = (top / blk.sq[:, None]).reshape(fac.n_kv, -1, r)
+                    B_s = top.T @ blk.Mw
+                continue
+            if r == 0:
+                continue
+            a_cols.append(top / blk.sq[:, None])
+            b_rows.append(top.conj().T @ blk.Mw)
+            freq.append(torch.full((r,), int(blk.where), dtype=torch.long))
+            energy.append(blk.s2[:r])
+        en = torch.cat(energy)
+        order = torch.argsort(en, descending=True)
+        self._init(torch.cat(a_cols, dim=1)[:, order], torch.cat(b_rows, dim=0)[order], torch.cat(freq)[order.cpu()],
+                   n_q, fac.n_kv, fac.d, inv_freq, A_s, B_s, fac.nope.nonzero().flatten(), en[order], attn_scale, device)
+
+    @classmethod
+    def from_factors(cls, A, B, freq, n_q, n_kv, head_dim, inv_freq, A_s=None, B_s=None, slow=None,
+                     energy=None, attn_scale: float = 1.0, device="cuda") -> "PhasorKey":
+        self = object.__new__(cls)
+        self._init(A, B, freq, n_q, n_kv, head_dim, inv_freq, A_s, B_s, slow, energy, attn_scale, device)
+        return self
+
+    @classmethod
+    def from_spec(cls, spec, device="cuda") -> "PhasorKey":
+        return cls.from_factors(spec.A, spec.B, spec.freq, spec.n_q, spec.n_kv, spec.head_dim, spec.inv_freq,
+                                spec.A_s, spec.B_s, spec.slow, None, spec.attn_scale, device)
+
+    def _init(self, A, B, freq, n_q, n_kv, head_dim, inv_freq, A_s, B_s, slow, energy, attn_scale, device):
+        self.A, self.B, self.freq = A, B, freq.long()
+        self.A_s, self.B_s = A_s, B_s
+        self.slow = slow.long() if slow is not None else torch.zeros(0, dtype=torch.long)
+        self.energy = energy
+        self.n_q, self.n_kv, self.h = int(n_q), int(n_kv), int(head_dim) // 2
+        self.R = int(B.shape[0])
+        self.R_s = 0 if B_s is None else int(B_s.shape[0])
+        self.head_dim, self.d_model = int(head_dim), int(B.shape[1])
+        self.inv_freq = None if inv_freq is None else inv_freq.to(torch.float64).cpu()
+        self.attn_scale = float(attn_scale)
+        self.second = 1.0
+        self.device = torch.device(device)
+        self._dev = None
+
+    # ------------------------------------------------------------------ reference surface
+    @property
+    def cache_width(self) -> int:
+        """Cached reals per token (shared by all heads)."""
+        return 2 * self.R + self.R_s
+
+    def write(self, x: torch.Tensor, ph: torch.Tensor) -> torch.Tensor:
+        """Tokens x [T, D] at phasors ph [T, d/2] -> fp32 cache rows [T, 2R + R_s] (unquantised)."""
+        L = self._layer()
+        x = self._x(x)
+        phd = self._ph(ph)
+        out = torch.empty((x.shape[0], self.cache_width), dtype=torch.float32, device=self.device)
+        _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None, _lib.ptr(x), self._xdt(x), None, _lib.ptr(phd),
+                                               None, x.shape[0], _lib.ptr(out), None, _lib.current_stream()),
+                   "pkv_cache_write")
+        return out
+
+    def absorb(self, q: torch.Tensor, ph: torch.Tensor) -> torch.Tensor:
+        """Pre-RoPE queries q [H, Tq, d] at phasors ph [Tq, d/2] -> [H, Tq, 2R + R_s]."""
+        L = self._layer()
+        qd = q.to(device=self.device, dtype=torch.float32).transpose(0, 1).contiguous()     # [Tq, H, d]
+        phd = self._ph(ph)
+        out = torch.empty((qd.shape[0], self.n_q, self.cache_width), dtype=torch.float32, device=self.device)
+        _lib.check(_lib.load().pkv_absorb(ctypes.byref(L), _lib.ptr(qd), None, _lib.ptr(phd), qd.shape[0],
+                                          _lib.ptr(out), None, _lib.current_stream()), "pkv_absorb")
+        return out.transpose(0, 1)
+
+    def scores(self, q_abs: torch.Tensor, cache) -> torch.Tensor:
+        """Unscaled logits [H, Tq, Tk] of absorbed queries against cache rows.
+
+        `cache` is either fp32 rows [Tk, W] (they are quantised with this layer's tensor scale into a
+        scratch paged cache first, so the result is the score on the NVFP4 cache) or a tuple
+        ``(PagedLatentCache, sequence index)``."""
+        if isinstance(cache, tuple):
+            pc, b = cache
+        else:
+            rows = cache.to(device=self.device, dtype=torch.float32)
+            pc, b = PagedLatentCache(self.cache_width, self.n_kv, self.head_dim, 1, rows.shape[0], self.device,
+                                     with_v=False), 0
+            n = rows.shape[0]
+            pos = torch.arange(n, dtype=torch.int32, device=self.device)
+            pc.quantize_rows(rows, pc.slots(torch.zeros_like(pos), pos), self.second)
+            pc.seqlens.fill_(n)
+        Tk = int(pc.seqlens[b])
+        qa = q_abs.to(device=self.device, dtype=torch.float32).transpose(0, 1).contiguous()        # [Tq, H, W]
+        Tq = qa.shape[0]
+        S = torch.empty((Tq, self.n_q, Tk), dtype=torch.float32, device=self.device)
+        pt = pc.page_table[b:b + 1].expand(Tq, -1).contiguous()
+        sl = pc.seqlens[b:b + 1].expand(Tq).contiguous()
+        ws = DecodeWorkspace(Tq, self.n_q, self.head_dim, self.cache_width, 1, self.device)
+        L = self._layer()
+        _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(pc.c), _lib.ptr(qa), _lib.ptr(pt),
+                                               pc.max_pages, _lib.ptr(sl), Tq, 1,
+                                               _lib.ATTN_SCORES_ONLY | _lib.ATTN_SIMT, _lib.ptr(ws.partials),
+                                               _lib.ptr(S), Tk, _lib.ptr(ws.status), _lib.current_stream()),
+                   "pkv_decode_attn")
+        return S.transpose(0, 1)
+
+    # ------------------------------------------------------------------ B200 entry points
+    def set_second(self, second: float) -> None:
+        """fp32 tensor scale of the NVFP4 latent (phasorkv/quant.py:119-124 gives the static rule)."""
+        self.second = float(second)
+        if self._dev is not None:
+            self._dev["layer"].second = self.second
+
+    def calibrate_second(self, rows: torch.Tensor) -> float:
+        """Static rule of the reference: 32 sigma of the widest latent channel over 448 * 6."""
+        var = rows.float().var(dim=0)
+        self.set_second(float(32.0 * var.max().clamp_min(1e-30).sqrt() / (448.0 * 6.0)))
+        return self.second
+
+    def new_cache(self, batch: int, max_tokens: int, with_v: bool = True) -> PagedLatentCache:
+        return PagedLatentCache(self.cache_width, self.n_kv, self.head_dim, batch, max_tokens, self.device, with_v)
+
+    def write_paged(self, cache: PagedLatentCache, x: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                    v: Optional[torch.Tensor] = None, latent_out: Optional[torch.Tensor] = None,
+                    scratch: Optional[torch.Tensor] = None) -> None:
+        """Fused write of tokens x [n, D] (fp32 or bf16) at global `positions` into `slots`; V rows too.
+        With ``cache=None`` only the unquantised rows are produced (into `latent_out`)."""
+        L = self._layer()
+        x = self._x(x)
+        _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None if cache is None else ctypes.byref(cache.c),
+                                               _lib.ptr(x), self._xdt(x),
+                                               _lib.ptr(positions), None, _lib.ptr(slots), x.shape[0],
+                                               _lib.ptr(latent_out), _lib.ptr(scratch), _lib.current_stream()),
+                   "pkv_cache_write")
+        if v is not None:
+            cache.write_v(v, slots)
+
+    def workspace(self, batch: int, n_split: int) -> DecodeWorkspace:
+        return DecodeWorkspace(batch, self.n_q, self.head_dim, self.cache_width, n_split, self.device)
+
+    def default_splits(self, batch: int, max_tokens: int, simt: bool = False) -> int:
+        """Token splits per sequence so that the grid fills the GPU a whole number of times."""
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        pages = max(1, (max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS)
+        per_sm = 3 if simt else 1
+        return max(1, min(pages, (sms * per_sm) // max(1, batch)))
+
+    def absorb_step(self, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace, operand: bool = True) -> None:
+        """q [B, H, d] fp32 at `positions` [B] -> ws.qabs (fp32) and, if asked, ws.qop (operand form)."""
+        L = self._layer()
+        _lib.check(_lib.load().pkv_absorb(ctypes.byref(L), _lib.ptr(q), _lib.ptr(positions), None, q.shape[0],
+                                          _lib.ptr(ws.qabs), _lib.ptr(ws.qop) if operand else None,
+                                          _lib.current_stream()), "pkv_absorb")
+
+    def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
+                    scores_out: Optional[torch.Tensor] = None) -> None:
+        """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials."""
+        L = self._layer()
+        flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
+        qsrc = ws.qabs if simt else ws.qop
+        stride = 0 if scores_out is None else scores_out.shape[-1]
+        _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(qsrc),
+                                               _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
+                                               ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
+                                               stride, _lib.ptr(ws.status), _lib.current_stream()), "pkv_decode_attn")
+
+    def merge_step(self, ws: DecodeWorkspace, normalise: bool = True, packed: bool = False,
+                   out: Optional[torch.Tensor] = None) -> None:
+        """Log-sum-exp merge of ws.partials -> `out` or ws.out (normalised) and / or ws.packed (o, m, l)."""
+        pw = self.head_dim + 2
+        out = ws.out if out is None else out
+        _lib.check(_lib.load().pkv_merge(_lib.ptr(ws.partials), ws.n_split * self.n_q * pw, self.n_q * pw, ws.n_split,
+                                         ws.batch, self.n_q, self.head_dim, _lib.ptr(out) if normalise else None,
+                                         _lib.ptr(ws.packed) if packed else None, _lib.current_stream()), "pkv_merge")
+
+    def merge_gathered(self, gathered: torch.Tensor, out: torch.Tensor) -> None:
+        """gathered [G, B, H, d+2] packed triples of G token shards -> out [B, H, d]."""
+        G, B = gathered.shape[0], gathered.shape[1]
+        pw = self.head_dim + 2
+        _lib.check(_lib.load().pkv_merge(_lib.ptr(gathered), self.n_q * pw, B * self.n_q * pw, G, B, self.n_q,
+                                         self.head_dim, _lib.ptr(out), None, _lib.current_stream()), "pkv_merge")
+
+    def decode(self, cache: PagedLatentCache, q: torch.Tensor, positions: torch.Tensor,
+               ws: Optional[DecodeWorkspace] = None, simt: bool = False, scores_only: bool = False) -> torch.Tensor:
+        """One decode step of this layer: absorb, split-T attention, merge -> O [B, H, d] fp32."""
+        if ws is None:
+            ws = self.workspace(q.shape[0], self.default_splits(q.shape[0], cache.max_pages * PAGE_TOKENS, simt))
+        self.absorb_step(q, positions, ws, operand=not simt)
+        self.attend_step(cache, ws, simt=simt, scores_only=scores_only)
+        self.merge_step(ws)
+        return ws.out
+
+    # ------------------------------------------------------------------ plumbing
+    def _layer(self) -> _lib.Layer:
+        """Upload the factors once and return the C struct (device pointers stay owned by this object)."""
+        if self._dev is None:
+            if not torch.cuda.is_available():
+                raise _lib.PhasorKVError("phasorkv_b200 needs a CUDA device; there is no CPU path")
+            _lib.check(_lib.load().pkv_device_check(), "pkv_device_check")
+            if self.inv_freq is None:
+                raise _lib.PhasorKVError("inv_freq was not given")
+            dev = self.device
+            B = self.B.to(torch.complex64)
+            rows = [B.real, B.imag] + ([self.B_s.to(torch.float32)] if self.R_s else [])
+            t = dict(
+                Bw=torch.cat(rows, dim=0).to(device=dev, dtype=torch.float32).contiguous(),
+                A_re=self.A.real.to(device=dev, dtype=torch.float32).contiguous(),
+                A_im=self.A.imag.to(device=dev, dtype=torch.float32).contiguous(),
+                A_s=None if not self.R_s else self.A_s.to(device=dev, dtype=torch.float32).contiguous(),
+                freq=self.freq.to(device=dev, dtype=torch.int32).contiguous(),
+                slow=None if not self.R_s else self.slow.to(device=dev, dtype=torch.int32).contiguous(),
+                inv_freq=self.inv_freq.to(device=dev, dtype=torch.float64).contiguous(),
+            )
+            L = _lib.Layer(self.d_model, self.n_q, self.n_kv, self.head_dim, self.R, self.R_s,
+                           int(self.slow.numel()) if self.R_s else 0, self.attn_scale, self.second,
+                           t["Bw"].data_ptr(), t["A_re"].data_ptr(), t["A_im"].data_ptr(),
+                           0 if t["A_s"] is None else t["A_s"].data_ptr(), t["freq"].data_ptr(),
+                           0 if t["slow"] is None else t["slow"].data_ptr(), t["inv_freq"].data_ptr())
+            t["layer"] = L
+            self._dev = t
+        return self._dev["layer"]
+
+    def _x(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.to(torch.float32)
+        return x.to(self.device).contiguous()
+
+    @staticmethod
+    def _xdt(x: torch.Tensor) -> int:
+        return _lib.BF16 if x.dtype == torch.bfloat16 else _lib.F32
+
+    def _ph(self, ph: torch.Tensor) -> torch.Tensor:
+        """complex phasors [n, h] -> interleaved float32 [n, h, 2] on the device."""
+        return torch.view_as_real(ph.to(torch.complex64)).to(self.device).contiguous()
