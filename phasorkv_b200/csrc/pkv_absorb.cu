@@ -119,7 +119,9 @@ extern "C" int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const in
                           void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
-    if (!q_dev || (!positions_dev && !phasors_dev) || batch < 0) return PKV_ERR_INVALID;
+    if (batch < 0) return PKV_ERR_INVALID;
+    if (batch == 0) return PKV_OK;
+    if (!q_dev || (!positions_dev && !phasors_dev)) return PKV_ERR_INVALID;
     if (phasors_dev && (((uintptr_t)phasors_dev) & 7u)) return PKV_ERR_INVALID;
     if (layer->head_dim / 2 > MAX_H || (layer->head_dim & 1)) return PKV_ERR_UNSUPPORTED;
     const int W = 2 * layer->R + layer->R_s, Wp = pkv_padded_width(W);

@@ -226,6 +226,7 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
     if (st) return st;
     st = pkv_check_cache(cache);
     if (st) return st;
+    if (batch == 0) return PKV_OK;
     if (!q_dev || !page_table_dev || !seqlens_dev || !partials_dev) return PKV_ERR_INVALID;
     if (batch < 0 || n_split <= 0 || max_pages <= 0 || n_split > 65535 || batch > 65535) return PKV_ERR_INVALID;
     if (cache->W != 2 * layer->R + layer->R_s || cache->n_kv != layer->n_kv || cache->head_dim != layer->head_dim)

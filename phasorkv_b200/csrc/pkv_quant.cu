@@ -76,9 +76,9 @@ extern "C" int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev
                                  int32_t n_tokens, float second, void* stream) {
     int st = pkv_check_cache(cache);
     if (st) return st;
-    if (!rows_dev || !slots_dev || n_tokens < 0 || !(second > 0.0f)) return PKV_ERR_INVALID;
-    if (((uintptr_t)rows_dev) & 15u) return PKV_ERR_INVALID;
-    if (n_tokens == 0) return PKV_OK;
+    if (n_tokens < 0 || !(second > 0.0f)) return PKV_ERR_INVALID;
+    if (n_tokens == 0) return PKV_OK;                      // nothing to do: buffers may be empty (NULL)
+    if (!rows_dev || !slots_dev || (((uintptr_t)rows_dev) & 15u)) return PKV_ERR_INVALID;
     long n = (long)n_tokens * (pkv_padded_width(cache->W) / 16);
     pkv_quantize_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         cache->latent_dev, rows_dev, slots_dev, n_tokens, cache->W, cache->n_pages, second);
@@ -99,7 +99,9 @@ __global__ void pkv_v_write_kernel(uint4* __restrict__ vpool, const uint4* __res
 
 extern "C" int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slots_dev,
                            int32_t n_tokens, void* stream) {
-    if (!cache || !cache->v_dev || !v_dev || !slots_dev || n_tokens < 0) return PKV_ERR_INVALID;
+    if (!cache || !cache->v_dev || n_tokens < 0) return PKV_ERR_INVALID;
+    if (n_tokens == 0) return PKV_OK;
+    if (!v_dev || !slots_dev) return PKV_ERR_INVALID;
     int row_bytes = cache->n_kv * cache->head_dim * 2;
     if (row_bytes <= 0 || (row_bytes % 16) || (((uintptr_t)v_dev | (uintptr_t)cache->v_dev) & 15u))
         return PKV_ERR_INVALID;
@@ -142,9 +144,10 @@ extern "C" int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev
                               float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream) {
     int st = pkv_check_cache(cache);
     if (st) return st;
-    if (!slots_dev || n_tokens < 0) return PKV_ERR_INVALID;
-    if (codes_out_dev && (((uintptr_t)codes_out_dev) & 7u)) return PKV_ERR_INVALID;
+    if (n_tokens < 0) return PKV_ERR_INVALID;
     if (n_tokens == 0) return PKV_OK;
+    if (!slots_dev) return PKV_ERR_INVALID;
+    if (codes_out_dev && (((uintptr_t)codes_out_dev) & 7u)) return PKV_ERR_INVALID;
     long n = (long)n_tokens * (cache->W / 16);
     pkv_cache_read_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         cache->latent_dev, slots_dev, n_tokens, cache->W, cache->n_pages, second, rows_out_dev, codes_out_dev,

@@ -312,6 +312,7 @@ extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cach
     int st = pkv_check_layer(layer);
     if (st) return st;
     const int W = 2 * layer->R + layer->R_s;
+    if (n_tokens == 0) return PKV_OK;
     if (cache) {
         st = pkv_check_cache(cache);
         if (st) return st;
