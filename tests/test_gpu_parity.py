@@ -253,3 +253,76 @@ def test_decode_time_write_path(config, n):
     b, cb, sb = cache2.read(slots, sc.second)
     assert (ca != cb).float().mean() < 2e-3 and (sa != sb).float().mean() < 2e-3
     assert rel(b.cpu(), a.cpu()) < 5e-3
+
+
+# ------------------------------------------------------------------------------------------------
+# tensor-core kernel (tcgen05 block-scaled NVFP4 scores, bf16 P.V): same checks, same tolerances
+# ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 127, 128, 129, 1000])
+def test_tc_decode_lengths(T):
+    _check_decode(Scenario("cfg2", seqlens=(T,), pos0=4000), n_split=3, simt=False)
+
+
+@pytest.mark.parametrize("config,gain", [("cfg2", 1.0), ("cfg2", 256.0), ("cfg3", 1.0), ("cfg3", 256.0)])
+def test_tc_decode_ragged_batch(config, gain):
+    _check_decode(Scenario(config, seqlens=(513, 0, 77, 300), gain=gain, pos0=100000), n_split=4, simt=False)
+
+
+def test_tc_decode_long_single_split():
+    """Many pages through one CTA: every pipeline stage and barrier phase wraps several times."""
+    _check_decode(Scenario("cfg2", seqlens=(4096 + 37,), gain=64.0, pos0=28000), n_split=1, simt=False)
+
+
+def test_tc_matches_simt_partials():
+    sc = Scenario("cfg2", seqlens=(700, 256), gain=32.0)
+    outs = []
+    for simt in (True, False):
+        ws = sc.pk.workspace(sc.B, 2)
+        sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=not simt)
+        sc.pk.attend_step(sc.cache, ws, simt=simt)
+        sc.pk.merge_step(ws, packed=True)
+        outs.append((ws.out.clone(), ws.packed.clone()))
+    assert rel(outs[1][0].cpu(), outs[0][0].cpu()) < OUT_TOL
+    lse = lambda p: p[..., -2].double() + torch.log2(p[..., -1].double())
+    assert torch.allclose(lse(outs[1][1]).cpu(), lse(outs[0][1]).cpu(), atol=2e-3)
+
+
+def test_tc_scores_only():
+    sc = Scenario("cfg2", seqlens=(400, 130), gain=64.0)
+    ws = sc.pk.workspace(sc.B, 2)
+    sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=True)
+    sc.pk.attend_step(sc.cache, ws, simt=False, scores_only=True)
+    sc.pk.merge_step(ws, normalise=False, packed=True)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    for b, T in enumerate(sc.seqlens):
+        _, S_ref, _ = sc.oracle_scores_and_output(b, sc.dequantised(b))
+        s2 = S_ref.double() * (po.LOG2E * sc.spec.head_dim ** -0.5)
+        lse = torch.log2(torch.exp2(s2 - s2.amax(-1, keepdim=True)).sum(-1)) + s2.amax(-1)
+        got = ws.packed[b, :, -2].double().cpu() + torch.log2(ws.packed[b, :, -1].double().cpu())
+        assert torch.allclose(got, lse, atol=2e-3)
+
+
+def test_query_operand_expansion():
+    """The operand written by the absorb kernel (four NVFP4 residual terms with per-row tensor scales)
+    sums back to the fp32 absorbed query within 2e-4."""
+    sc = Scenario("cfg3", seqlens=(16,))
+    ws = sc.pk.workspace(sc.B, 1)
+    sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=True)
+    blob = ws.qop[:ws.qop_bytes].cpu()
+    W = sc.spec.cache_width
+    lv = torch.cat([po.E2M1_LEVELS, -po.E2M1_LEVELS])
+    codes_b, scales_b = blob[:128 * 128], blob[128 * 128:128 * 128 + 2048]
+    row_scale = blob[128 * 128 + 2048:].view(torch.float32)
+    n = torch.arange(128)[:, None]
+    col = torch.arange(256)[None, :]
+    o = n * 128 + col // 2
+    o = o ^ ((o >> 3) & 0x70)
+    nib = (codes_b[o] >> ((col & 1) * 4)) & 15
+    j = col // 16
+    so = (j // 4) * 512 + (n % 32) * 16 + (n // 32) * 4 + j % 4
+    sc_f = scales_b[so].view(torch.float8_e4m3fn).float()
+    vals = lv[nib.long()] * sc_f * row_scale[:, None]                  # [128 = term*32 + head, 256]
+    recon = vals.reshape(4, 32, 256).sum(0)[:, :W]
+    assert rel(recon, ws.qabs[0].cpu()) < 2e-4
