@@ -24,6 +24,7 @@ extern "C" {
 #define PKV_PAGE_TOKENS 128          /* tokens per cache page */
 #define PKV_MAX_WIDTH   256          /* largest supported latent width W = 2R + R_s */
 #define PKV_QUERY_TERMS 4            /* NVFP4 residual terms of the absorbed query operand */
+#define PKV_NOALLOC_MAX_PARTS 320     /* pkv_decode_attn_noalloc: upper bound on batch * n_split */
 #define PKV_SMALL_WRITE_TOKENS 64    /* pkv_cache_write spreads the projection over the GPU up to this n */
 
 enum pkv_status {
@@ -151,6 +152,28 @@ int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const vo
  * contributes to the all-gather of a token-sharded sequence). */
 int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
               int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream);
+
+/* Decode attention and merge for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose callers always allocate their own scratch with torch).  It is meant for hosts that
+ * only ever receive input and output buffers -- a plugin inside another runtime's fixed memory plan, a
+ * serving loop after its allocator has been frozen -- and therefore cannot provide the `partials`
+ * scratch that pkv_decode_attn asks for.  The scratch lives inside the library instead: a fixed array
+ * of PKV_NOALLOC_MAX_PARTS * 32 * 130 floats (about 5.3 MB) in the device memory of every GPU that
+ * loads the library, held until the process exits.
+ *   - same inputs as pkv_decode_attn with the tensor-core kernel (qop_dev is the operand blob of
+ *     pkv_absorb; 32 query heads, head_dim 128, 4 or 8 query heads per kv head) and the V cache
+ *     present; the result is the normalised output out_dev [B, n_q, head_dim], as pkv_merge gives
+ *   - batch * n_split must not exceed PKV_NOALLOC_MAX_PARTS; larger requests return
+ *     PKV_ERR_UNSUPPORTED and do nothing
+ *   - the first call on each device looks up the array's address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture.  No call allocates or frees anything.
+ *   - all calls on one GPU share the one array: two calls whose kernels may overlap on the GPU
+ *     (different streams, different threads) race on it.  Issue them on one stream or serialise
+ *     them.  Nothing in the array needs clearing between calls: each call overwrites every slot it
+ *     later reads. */
+int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* qop_dev,
+                            const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
+                            int32_t batch, int32_t n_split, float* out_dev, int32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

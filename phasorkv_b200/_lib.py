@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libphasorkv_b200.so")
 PAGE_TOKENS = 128
 MAX_WIDTH = 256
 QUERY_TERMS = 4
+NOALLOC_MAX_PARTS = 320
 F32, BF16 = 0, 1
 ATTN_SCORES_ONLY, ATTN_SIMT = 1, 2
 
@@ -52,6 +53,8 @@ SIGNATURES = {
     "pkv_absorb": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                   c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
+                                          c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }
