@@ -40,7 +40,7 @@ L2_BYTES = 126 * 2 ** 20
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
@@ -69,10 +69,14 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t_end = time.time() + 5.0                       # nvidia-smi needs a moment before its first line
+            while not self.rows and time.time() < t_end:
+                time.sleep(0.02)
+            self.skip = len(self.rows)                      # samples taken before the GPU was under load
         except OSError:
             self.proc = None
 
@@ -88,6 +92,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        self.rows = self.rows[getattr(self, "skip", 0):] or self.rows
         sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -176,20 +181,18 @@ class Stack:
         for l, (pk, cache) in enumerate(zip(self.layers, self.caches)):
             ws = self.ws[l & 1]
             if write:
-                pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], scratch=ws.wscratch)
-                cache.write_v(self.v_new[l], self.wslots[l])
-                n += 3
+                pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
+                n += 2
             pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only)
+            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, out=self.out[l])
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
-            pk.merge_step(ws, out=self.out[l])
-            n += 3
+            n += 2 + (1 if self.simt else 0)
         self.launches_per_layer = n // len(self.layers)
         return n
 

@@ -100,13 +100,17 @@ int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev, const int
  * (re, im interleaved), the `ph` argument of the reference with attention_scaling already inside.
  * latent_out_dev: optional fp32 [n, W] copy of the unquantised rows (what PhasorKey.write returns);
  * cache may be NULL when only that copy is wanted.
- * scratch_dev: optional fp32 scratch of n * 256 floats (16-byte aligned).  When it is given and
- * n <= PKV_SMALL_WRITE_TOKENS (the decode-time write of one token per sequence) the projection is
- * split by latent column over many SMs and staged through it; otherwise one CTA per 64 tokens does
- * everything on chip and the scratch is not touched. */
+ * scratch_dev: optional fp32 scratch of pkv_write_scratch_floats(n, d_model) floats (16-byte
+ * aligned).  When it is given and n <= PKV_SMALL_WRITE_TOKENS (the decode-time write of one token per
+ * sequence) the projection is split by latent column and by d_model slice over many SMs and staged
+ * through it; otherwise one CTA per 64 tokens does everything on chip and the scratch is not touched.
+ * v_rows_dev: optional bf16 value rows [n, n_kv*head_dim] stored into the V pages at the same slots
+ * (the same effect as a following pkv_v_write, without a further launch on the small path). */
 int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                     const int32_t* positions_dev, const float* phasors_dev, const int32_t* slots_dev,
-                    int32_t n_tokens, float* latent_out_dev, float* scratch_dev, void* stream);
+                    int32_t n_tokens, float* latent_out_dev, float* scratch_dev, const void* v_rows_dev,
+                    void* stream);
+int64_t pkv_write_scratch_floats(int32_t n_tokens, int32_t d_model);
 
 /* bf16 value rows v_dev [n, n_kv*head_dim] into the V pages at slots_dev [n]. */
 int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slots_dev, int32_t n_tokens,
@@ -139,11 +143,17 @@ int64_t pkv_query_operand_bytes(int32_t W);
  *                 l = sum 2^(s - m)
  *   scores_out  : optional fp32 [B, n_q, scores_stride] unscaled scores (tests)
  *   status_dev  : optional int32[4]; kernels record a give-up of a bounded wait or an index out
- *                 of range here instead of trapping */
+ *                 of range here instead of trapping
+ *   out_dev     : optional fp32 [B, n_q, head_dim]; when given, the splits are also merged (the
+ *                 result of pkv_merge on `partials`) -- inside the same launch for the tensor-core
+ *                 kernel, where the last CTA of each sequence to finish does it
+ *   counters_dev: int32 [B], required with out_dev for the tensor-core kernel; zero them once when
+ *                 allocating, every launch leaves them at zero again */
 int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                     const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
                     int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
-                    float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, void* stream);
+                    float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
+                    int32_t* counters_dev, void* stream);
 
 /* Log-sum-exp merge of n_parts partial triples per (sequence, head): M = max m, w = 2^(m - M),
  * O = sum w o / sum w l (phasorkv/kernels/dense_attn.py:72-74).  parts_dev is addressed as

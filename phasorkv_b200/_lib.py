@@ -47,12 +47,13 @@ SIGNATURES = {
     "pkv_query_operand_bytes": (c_int64, [c_int32]),
     "pkv_quantize_rows": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_float, c_void_p]),
     "pkv_cache_write": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
-                                  c_int32, c_void_p, c_void_p, c_void_p]),
+                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "pkv_write_scratch_floats": (c_int64, [c_int32, c_int32]),
     "pkv_v_write": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p]),
     "pkv_cache_read": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_absorb": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
-                                  c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+                                  c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                           c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,

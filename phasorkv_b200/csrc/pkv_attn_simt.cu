@@ -3,13 +3,15 @@
 // 32-token tiles of the latent, scores all query heads against them, keeps a running base-2
 // softmax and accumulates P.V from the bf16 V pages. Also the log-sum-exp merge kernel.
 #include "pkv_common.cuh"
+#include "pkv_merge.cuh"
 
 int pkv_check_layer(const pkv_layer_t* L);
 int pkv_check_cache(const pkv_cache_t* c);
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, cudaStream_t stream);
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, int32_t* counters_dev,
+                       cudaStream_t stream);
 
 namespace {
 
@@ -174,31 +176,20 @@ __global__ void __launch_bounds__(NT) pkv_attn_simt_kernel(
     }
 }
 
-// one CTA per (sequence, head), one thread per output dim
-__global__ void pkv_merge_kernel(const float* __restrict__ parts, long stride_b, long stride_p, int n_parts, int n_q,
-                                 int head_dim, float* __restrict__ out, float* __restrict__ packed_out) {
-    const int b = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+// one warp per (sequence, head)
+__global__ void __launch_bounds__(128) pkv_merge_kernel(const float* __restrict__ parts, long stride_b, long stride_p,
+                                                        int n_parts, int n_q, int head_dim, int batch,
+                                                        float* __restrict__ out, float* __restrict__ packed_out) {
+    const int lane = threadIdx.x & 31;
+    const int idx = blockIdx.x * 4 + (threadIdx.x >> 5);
+    pkv_grid_launch_dependents();
+    pkv_grid_wait();
+    if (idx >= batch * n_q) return;
+    const int b = idx / n_q, h = idx % n_q;
     const int PW = head_dim + 2;
-    const float* base = parts + (size_t)b * stride_b + (size_t)h * PW;
-    float M = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) M = fmaxf(M, base[(size_t)p * stride_p + head_dim]);
-    float num = 0.0f, den = 0.0f;
-    if (M > -INFINITY) {
-        for (int p = 0; p < n_parts; ++p) {
-            const float* pp = base + (size_t)p * stride_p;
-            float w = exp2f(pp[head_dim] - M);          // a split that saw no token has m = -inf, w = 0
-            if (d < head_dim) num = fmaf(w, pp[d], num);
-            den = fmaf(w, pp[head_dim + 1], den);
-        }
-    }
-    if (d < head_dim) {
-        if (out) out[((size_t)b * n_q + h) * head_dim + d] = den > 0.0f ? num / den : 0.0f;
-        if (packed_out) packed_out[((size_t)b * n_q + h) * PW + d] = num;
-    }
-    if (packed_out && d == 0) {
-        packed_out[((size_t)b * n_q + h) * PW + head_dim] = M;
-        packed_out[((size_t)b * n_q + h) * PW + head_dim + 1] = den;
-    }
+    pkv_merge_warp(parts + (size_t)b * stride_b + (size_t)h * PW, stride_p, n_parts, head_dim, lane,
+                   out ? out + ((size_t)b * n_q + h) * head_dim : nullptr,
+                   packed_out ? packed_out + ((size_t)b * n_q + h) * PW : nullptr);
 }
 
 template <int WP, int REP>
@@ -221,7 +212,8 @@ int launch_simt(const pkv_layer_t* L, const pkv_cache_t* C, const float* q, cons
 extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                                const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
                                int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
-                               float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, void* stream) {
+                               float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
+                               int32_t* counters_dev, void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     st = pkv_check_cache(cache);
@@ -238,34 +230,41 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
     cudaStream_t s = (cudaStream_t)stream;
     if (!(flags & PKV_ATTN_SIMT))
         return pkv_attn_tc_launch(layer, cache, q_dev, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
-                                  partials_dev, scores_out_dev, scores_stride, status_dev, s);
+                                  partials_dev, scores_out_dev, scores_stride, status_dev, out_dev,
+                                  out_dev ? counters_dev : nullptr, s);
     if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
     const int rep = layer->n_q / layer->n_kv;
     const bool wide = pkv_padded_width(cache->W) == 256;
+    int rc = PKV_ERR_UNSUPPORTED;
 #define PKV_SIMT_CASE(R_)                                                                                          \
     case R_:                                                                                                       \
-        return wide ? launch_simt<256, R_>(layer, cache, (const float*)q_dev, page_table_dev, max_pages, seqlens_dev, \
+        rc = wide ? launch_simt<256, R_>(layer, cache, (const float*)q_dev, page_table_dev, max_pages, seqlens_dev, \
                                            batch, n_split, flags, partials_dev, scores_out_dev, scores_stride, s)  \
                     : launch_simt<128, R_>(layer, cache, (const float*)q_dev, page_table_dev, max_pages, seqlens_dev, \
-                                           batch, n_split, flags, partials_dev, scores_out_dev, scores_stride, s);
+                                           batch, n_split, flags, partials_dev, scores_out_dev, scores_stride, s); \
+        break;
     switch (rep) {
         PKV_SIMT_CASE(1)
         PKV_SIMT_CASE(2)
         PKV_SIMT_CASE(4)
         PKV_SIMT_CASE(8)
-        default: return PKV_ERR_UNSUPPORTED;
+        default: break;
     }
 #undef PKV_SIMT_CASE
+    if (rc == PKV_OK && out_dev) {                         // the CUDA-core kernel merges with a second launch
+        const int64_t pw = DH + 2;
+        rc = pkv_merge(partials_dev, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, out_dev, nullptr, stream);
+    }
+    return rc;
 }
 
 extern "C" int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
                          int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream) {
-    if (!parts_dev || n_parts <= 0 || batch < 0 || n_q <= 0 || head_dim <= 0 || head_dim > 1024) return PKV_ERR_INVALID;
+    if (!parts_dev || n_parts <= 0 || batch < 0 || n_q <= 0 || head_dim <= 0 || head_dim > 256) return PKV_ERR_INVALID;
     if (!out_dev && !packed_out_dev) return PKV_ERR_INVALID;
     if (batch == 0) return PKV_OK;
-    int threads = ((head_dim + 31) / 32) * 32;
-    pkv_merge_kernel<<<dim3(n_q, batch), threads, 0, (cudaStream_t)stream>>>(parts_dev, stride_b, stride_p, n_parts, n_q,
-                                                                             head_dim, out_dev, packed_out_dev);
-    PKV_LAUNCH_CHECK();
+    PKV_CUDA_TRY(pkv_launch_chained(pkv_merge_kernel, dim3((batch * n_q + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
+                                    parts_dev, (long)stride_b, (long)stride_p, n_parts, n_q, head_dim, batch, out_dev,
+                                    packed_out_dev));
     return PKV_OK;
 }

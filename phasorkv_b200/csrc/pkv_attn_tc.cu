@@ -12,6 +12,7 @@
 // Stages are handed over through mbarriers; every wait is bounded and a give-up is recorded in
 // `status` while all roles unwind, free TMEM and return.
 #include "pkv_common.cuh"
+#include "pkv_merge.cuh"
 #include "pkv_tcgen05.cuh"
 
 #include <cudaTypedefs.h>
@@ -88,13 +89,84 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
     return false;
 }
 
+// Fused merge: every CTA of a sequence bumps that sequence's counter once its partial is written and
+// fenced; the CTA that brings it to n_split owns the merge of all splits into `out` and puts the
+// counter back to zero, so the counters only ever need zeroing when they are allocated.
+// The merge sits on the tail of the launch, so it is built for latency: the partial blocks of the
+// sequence (16,640 contiguous bytes per split) are pulled into the now idle shared memory with one
+// bulk copy each, all in flight at once, and reduced from there. When they do not fit, the loads go
+// straight to L2 instead.
+constexpr int PART_FLOATS = NQ * (DH + 2);
+constexpr int MERGE_MAX_SMEM_SPLITS = 16;
+
+struct MergeSmem {
+    uint64_t bar;
+    int is_last;
+    float w[NQ][MERGE_MAX_SMEM_SPLITS];
+};
+
+__device__ __forceinline__ void count_and_merge(int32_t* counters, int b, int n_split, const float* partials, float* out,
+                                                MergeSmem* ms, float* big_smem, int big_smem_bytes, int32_t* status) {
+    __threadfence();                                   // this thread's partial stores are visible device-wide
+    __syncthreads();
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        const int prev = atomicAdd(&counters[b], 1);
+        ms->is_last = (prev == n_split - 1);
+        if (prev == n_split - 1) counters[b] = 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (!ms->is_last) return;
+    const long PW = DH + 2;
+    const float* base = partials + (size_t)b * n_split * PART_FLOATS;
+    const bool staged = n_split <= MERGE_MAX_SMEM_SPLITS && n_split * PART_FLOATS * 4 <= big_smem_bytes;
+    if (staged) {
+        if (tid == 0) {
+            mbar_init(&ms->bar, 1);
+            fence_barrier_init();
+            asm volatile("fence.proxy.async.global;" ::: "memory");     // other CTAs' stores before the async-proxy reads
+            mbar_arrive_expect_tx(&ms->bar, (uint32_t)(n_split * PART_FLOATS * 4));
+            for (int p = 0; p < n_split; ++p)
+                bulk_g2s(big_smem + (size_t)p * PART_FLOATS, base + (size_t)p * PART_FLOATS, PART_FLOATS * 4, &ms->bar);
+        }
+        __syncthreads();
+        bool ok = mbar_wait(&ms->bar, 0, 1u << 22);
+        if (!ok && status) { atomicExch(&status[0], 1); atomicExch(&status[1], 50); }
+        ok = __syncthreads_and(ok);
+        if (!ok) return;
+        if (tid < NQ) {
+            float M = -INFINITY, den = 0.0f;
+            for (int p = 0; p < n_split; ++p) M = fmaxf(M, big_smem[p * PART_FLOATS + tid * PW + DH]);
+            for (int p = 0; p < n_split; ++p) {
+                const float wp = M > -INFINITY ? exp2f(big_smem[p * PART_FLOATS + tid * PW + DH] - M) : 0.0f;
+                ms->w[tid][p] = wp;
+                den = fmaf(wp, big_smem[p * PART_FLOATS + tid * PW + DH + 1], den);
+            }
+            const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+            for (int p = 0; p < n_split; ++p) ms->w[tid][p] *= inv;
+        }
+        __syncthreads();
+        for (int e = tid; e < NQ * DH; e += NTHREADS) {
+            const int h = e / DH, d = e % DH;
+            float acc = 0.0f;
+            for (int p = 0; p < n_split; ++p) acc = fmaf(ms->w[h][p], big_smem[p * PART_FLOATS + h * PW + d], acc);
+            out[((size_t)b * NQ + h) * DH + d] = acc;
+        }
+        return;
+    }
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int h = warp; h < NQ; h += NTHREADS / 32)
+        pkv_merge_warp(base + (size_t)h * PW, NQ * PW, n_split, DH, lane, out + ((size_t)b * NQ + h) * DH, nullptr);
+}
+
 template <int WP, int REP>
 __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     const __grid_constant__ CUtensorMap vmap, const uint8_t* __restrict__ qop, long qop_stride,
     const uint8_t* __restrict__ latent, const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
-    int32_t* __restrict__ status) {
+    int32_t* __restrict__ status, float* __restrict__ out, int32_t* __restrict__ counters) {
     using C = Cfg<WP>;
     constexpr int NKV = NQ / REP;                 // kv heads
     constexpr int G16 = 16 / REP;                 // kv heads per 16-head group of P rows
@@ -102,22 +174,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     Extra* X = reinterpret_cast<Extra*>(smem + C::X_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
-    const int T = seqlens[b];
-    const int npages = min((T + PKV_PAGE_TOKENS - 1) / PKV_PAGE_TOKENS, max_pages);
-    const int pps = (npages + n_split - 1) / n_split;
-    const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
-    const int P = p_hi - p_lo;
-    const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
-    float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
+    __shared__ MergeSmem merge_smem;
+    pkv_grid_launch_dependents();
 
-    if (P <= 0) {                                  // this split has no token: the neutral partial
-        for (int i = tid; i < NQ * (DH + 2); i += NTHREADS) {
-            int c = i % (DH + 2);
-            part[i] = c == DH ? -INFINITY : 0.0f;
-        }
-        return;
-    }
-
+    // ---- prologue that touches no global memory: barriers, tensor memory
     if (tid == 0) {
         mbar_init(&X->q_full, 1);
         for (int s = 0; s < NK_STAGES; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
@@ -136,6 +196,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     tc_fence_after_sync();
     const uint32_t tb = X->tmem_base;
     const uint32_t sbase = smem_u32(smem);
+
+    pkv_grid_wait();                               // results of the kernels before (cache write, absorb) are complete
+
+    const int T = seqlens[b];
+    const int npages = min((T + PKV_PAGE_TOKENS - 1) / PKV_PAGE_TOKENS, max_pages);
+    const int pps = (npages + n_split - 1) / n_split;
+    const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
+    const int P = p_hi - p_lo;
+    const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
+    float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
+
+    if (P <= 0) {                                  // this split has no token: the neutral partial
+        for (int i = tid; i < NQ * (DH + 2); i += NTHREADS) {
+            int c = i % (DH + 2);
+            part[i] = c == DH ? -INFINITY : 0.0f;
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        if (warp == 2) tmem_dealloc(tb, TM_COLS);
+        if (out) count_and_merge(counters, b, n_split, partials, out, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
+        return;
+    }
 
     if (warp == 0) {
         // ================================================================== K producer
@@ -380,6 +462,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tb, TM_COLS);
+    if (out) count_and_merge(counters, b, n_split, partials, out, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
 }
 
 // ------------------------------------------------------------------------------------------------ host
@@ -408,15 +491,18 @@ int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
 template <int WP, int REP>
 int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
-              long scores_stride, int32_t* status, cudaStream_t st) {
+              long scores_stride, int32_t* status, float* out, int32_t* counters, cudaStream_t st) {
     auto kern = pkv_attn_tc_kernel<WP, REP>;
     constexpr int smem = Cfg<WP>::SMEM;
-    PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    static bool attr_done = false;                                  // once per instantiation
+    if (!attr_done) {
+        PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
     const float logit_scale = PKV_LOG2E / sqrtf((float)L->head_dim);
-    kern<<<dim3(n_split, batch), NTHREADS, smem, st>>>(vmap, qop, (long)Cfg<WP>::QBLOB, C->latent_dev, pt, max_pages, seqlens,
-                                                        n_split, C->n_pages, L->second * logit_scale, 1.0f / logit_scale,
-                                                        flags, partials, scores, scores_stride, status);
-    PKV_LAUNCH_CHECK();
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch), dim3(NTHREADS), smem, st, vmap, qop, (long)Cfg<WP>::QBLOB,
+                                    C->latent_dev, pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
+                                    1.0f / logit_scale, flags, partials, scores, scores_stride, status, out, counters));
     return PKV_OK;
 }
 
@@ -425,7 +511,9 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, cudaStream_t stream) {
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, int32_t* counters_dev,
+                       cudaStream_t stream) {
+    if (out_dev && !counters_dev) return PKV_ERR_INVALID;
     const int rep = layer->n_q / layer->n_kv;
     if (rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;          // P.V on tensor cores needs >= 4 query heads per kv head
     if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
@@ -441,7 +529,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     const uint8_t* qop = (const uint8_t*)q_dev;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
     return launch_tc<WP_, R_>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
-                              partials_dev, scores_out_dev, scores_stride, status_dev, stream)
+                              partials_dev, scores_out_dev, scores_stride, status_dev, out_dev, counters_dev, stream)
     if (rep == 4) { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }
     if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8);
 #undef PKV_TC_CASE

@@ -24,6 +24,32 @@ extern thread_local int g_pkv_last_cuda_error;
 #define PKV_LAUNCH_CHECK() PKV_CUDA_TRY(cudaGetLastError())
 
 // ------------------------------------------------------------------------------------------------
+// Programmatic dependent launch. The kernels of a decode step form a chain on one stream; each is
+// launched with the "programmatic stream serialization" attribute, tells the scheduler at its very
+// start that its successor may be brought onto the SMs, and itself waits for the complete result of
+// its predecessor (pkv_grid_wait) only after the part of its prologue that touches no global data.
+// A kernel launched without the attribute sees both calls as no-ops.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pkv_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pkv_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t pkv_launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                      Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// ------------------------------------------------------------------------------------------------
 // page layout (documented in include/phasorkv_b200.h)
 // ------------------------------------------------------------------------------------------------
 

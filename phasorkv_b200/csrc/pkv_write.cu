@@ -169,79 +169,110 @@ int launch_write(const pkv_layer_t* L, const pkv_cache_t* C, const void* x, cons
 }
 
 // ------------------------------------------------------------------------------------------------
-// Decode-time write (a handful of tokens): the projection is spread over Wp/8 CTAs so that the
-// factor matrix streams through many SMs, raw rows go to caller-provided scratch, and a second
-// kernel rotates, quantises and stores them.
+// Decode-time write (a handful of tokens). The factor matrix (W x D fp32, 4 MB for a Llama-3.1-8B layer)
+// has to stream through many SMs to be fast, so the projection is cut both by latent column (tiles of
+// 16) and by d_model (slices of 512): CTA (ct, ks) writes the partial dot products of its slice to
+// caller scratch [ks][token][WP]; a second kernel, one CTA per token, adds the slices, rotates,
+// quantises and stores the latent row, and copies the token's V row.
 // ------------------------------------------------------------------------------------------------
-constexpr int SM_TOK = 16;      // tokens per pass of the small projection
-constexpr int SM_KC = 1024;     // d_model slice staged in shared memory
+constexpr int SM_TOK = 16;      // tokens per pass
+constexpr int SM_COL = 16;      // latent columns per CTA
+constexpr int SM_KC = 512;      // d_model slice per CTA
+constexpr int SM_BP = SM_KC + 4;   // pitch of the factor tile: 16-byte reads of 8 consecutive rows hit distinct banks
 
 template <typename XT>
 __global__ void __launch_bounds__(256) pkv_project_small_kernel(const float* __restrict__ Bw, const XT* __restrict__ x,
                                                                 int n_tokens, int D, int W, int WP,
                                                                 float* __restrict__ raw) {
-    extern __shared__ __align__(16) float xs[];            // [SM_TOK][SM_KC]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * 8 + warp;
+    extern __shared__ __align__(16) float sm[];
+    float* xs = sm;                         // [SM_TOK][SM_KC]
+    float* bs = sm + SM_TOK * SM_KC;        // [SM_COL][SM_BP]
+    const int tid = threadIdx.x;
+    const int c0 = blockIdx.x * SM_COL, ks = blockIdx.y, k0 = ks * SM_KC;
+    const int kc = min(SM_KC, D - k0);
+    pkv_grid_launch_dependents();
+    pkv_grid_wait();                                     // x may be the output of the kernel before
+    constexpr int NV = SM_COL * (SM_KC / 4) / 256;          // 16-byte vectors per thread and tile (8)
+    auto load_x = [&](int t0, float4 (&xv)[NV]) {
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int i = tid + n * 256, tt = i / (SM_KC / 4), k4 = i % (SM_KC / 4);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t0 + tt < n_tokens && k4 * 4 < kc) {
+                const XT* src = x + (size_t)(t0 + tt) * D + k0 + k4 * 4;
+                if constexpr (sizeof(XT) == 4) {
+                    v = *reinterpret_cast<const float4*>(src);
+                } else {
+                    uint2 u = *reinterpret_cast<const uint2*>(src);
+                    v = make_float4(pkv_bf16_bits_to_float(u.x & 0xffffu), pkv_bf16_bits_to_float(u.x >> 16),
+                                    pkv_bf16_bits_to_float(u.y & 0xffffu), pkv_bf16_bits_to_float(u.y >> 16));
+                }
+            }
+            xv[n] = v;
+        }
+    };
+    // factor tile and the first token tile: all 16 loads of a thread are issued before any is used
+    {
+        float4 bv[NV], xv[NV];
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int i = tid + n * 256, cc = i / (SM_KC / 4), k4 = i % (SM_KC / 4);
+            bv[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 + cc < W && k4 * 4 < kc) bv[n] = *reinterpret_cast<const float4*>(Bw + (size_t)(c0 + cc) * D + k0 + k4 * 4);
+        }
+        load_x(0, xv);
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int i = tid + n * 256;
+            *reinterpret_cast<float4*>(bs + (i / (SM_KC / 4)) * SM_BP + (i % (SM_KC / 4)) * 4) = bv[n];
+            *reinterpret_cast<float4*>(xs + (i / (SM_KC / 4)) * SM_KC + (i % (SM_KC / 4)) * 4) = xv[n];
+        }
+    }
+    const int t = tid >> 4, c = tid & 15;
     for (int t0 = 0; t0 < n_tokens; t0 += SM_TOK) {
-        const int nt = min(SM_TOK, n_tokens - t0);
-        float acc[SM_TOK];
-#pragma unroll
-        for (int t = 0; t < SM_TOK; ++t) acc[t] = 0.0f;
-        for (int k0 = 0; k0 < D; k0 += SM_KC) {
-            const int kc = min(SM_KC, D - k0);
+        if (t0 > 0) {
+            float4 xv[NV];
+            load_x(t0, xv);
             __syncthreads();
-            for (int i = threadIdx.x; i < SM_TOK * (kc / 4); i += 256) {
-                int t = i / (kc / 4), k4 = i % (kc / 4);
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t < nt) {
-                    const XT* src = x + (size_t)(t0 + t) * D + k0 + k4 * 4;
-                    if constexpr (sizeof(XT) == 4) {
-                        v = *reinterpret_cast<const float4*>(src);
-                    } else {
-                        uint2 u = *reinterpret_cast<const uint2*>(src);
-                        v = make_float4(pkv_bf16_bits_to_float(u.x & 0xffffu), pkv_bf16_bits_to_float(u.x >> 16),
-                                        pkv_bf16_bits_to_float(u.y & 0xffffu), pkv_bf16_bits_to_float(u.y >> 16));
-                    }
-                }
-                *reinterpret_cast<float4*>(xs + t * SM_KC + k4 * 4) = v;
-            }
-            __syncthreads();
-            if (c < W) {
-                for (int k = lane * 4; k < kc; k += 128) {
-                    float4 b = *reinterpret_cast<const float4*>(Bw + (size_t)c * D + k0 + k);
 #pragma unroll
-                    for (int t = 0; t < SM_TOK; ++t) {
-                        float4 xv = *reinterpret_cast<const float4*>(xs + t * SM_KC + k);
-                        acc[t] = fmaf(xv.x, b.x, acc[t]); acc[t] = fmaf(xv.y, b.y, acc[t]);
-                        acc[t] = fmaf(xv.z, b.z, acc[t]); acc[t] = fmaf(xv.w, b.w, acc[t]);
-                    }
-                }
+            for (int n = 0; n < NV; ++n) {
+                const int i = tid + n * 256;
+                *reinterpret_cast<float4*>(xs + (i / (SM_KC / 4)) * SM_KC + (i % (SM_KC / 4)) * 4) = xv[n];
             }
         }
-#pragma unroll
-        for (int t = 0; t < SM_TOK; ++t) {
-            float v = acc[t];
-#pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && t < nt && c < WP) raw[(size_t)(t0 + t) * WP + c] = c < W ? v : 0.0f;
+        __syncthreads();
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        const float* xr = xs + t * SM_KC;
+        const float* br = bs + c * SM_BP;
+#pragma unroll 8
+        for (int k = 0; k < SM_KC; k += 4) {
+            float4 xv = *reinterpret_cast<const float4*>(xr + k);
+            float4 bv = *reinterpret_cast<const float4*>(br + k);
+            a0 = fmaf(xv.x, bv.x, a0); a1 = fmaf(xv.y, bv.y, a1); a2 = fmaf(xv.z, bv.z, a2); a3 = fmaf(xv.w, bv.w, a3);
         }
+        if (t0 + t < n_tokens) raw[((size_t)ks * n_tokens + t0 + t) * WP + c0 + c] = (a0 + a1) + (a2 + a3);
     }
 }
 
-// one CTA per token: rotate the complex pairs of its raw row, quantise, store
+// one CTA per token: add the d_model slices, rotate the complex pairs, quantise, store; V row too
 __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
-    const float* __restrict__ raw, const int32_t* __restrict__ positions, const float2* __restrict__ phasors, int h2,
-    const int32_t* __restrict__ slots, int W, int WP, int R, const int32_t* __restrict__ freq,
-    const double* __restrict__ inv_freq, float attn_scale, float second, uint8_t* __restrict__ latent, int n_pages,
-    float* __restrict__ latent_out) {
+    const float* __restrict__ raw, int n_slices, int n_tokens, const int32_t* __restrict__ positions,
+    const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots, int W, int WP, int R,
+    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, float second,
+    uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, const uint4* __restrict__ v_rows,
+    uint4* __restrict__ v_pool, int v_vecs) {
     __shared__ float row[PKV_MAX_WIDTH];
     const int tok = blockIdx.x, tid = threadIdx.x;
-    for (int c = tid; c < WP; c += 256) row[c] = raw[(size_t)tok * WP + c];
-    __syncthreads();
-    float re = 0.f, im = 0.f;
+    pkv_grid_launch_dependents();
+    pkv_grid_wait();
+    // the slice loads are issued first; the phasor (double-precision sincos) is computed while they fly
+    float a = 0.0f;
+    if (tid < WP) {
+#pragma unroll 8
+        for (int s = 0; s < n_slices; ++s) a += __ldcg(raw + ((size_t)s * n_tokens + tok) * WP + tid);
+    }
+    float pr = 1.0f, pi = 0.0f;
     if (tid < R) {
-        float pr, pi;
         if (phasors) {
             float2 p = phasors[(size_t)tok * h2 + freq[tid]];
             pr = p.x; pi = p.y;
@@ -250,9 +281,14 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
             sincos((double)positions[tok] * inv_freq[freq[tid]], &sn, &cs);
             pr = (float)((double)attn_scale * cs); pi = (float)((double)attn_scale * sn);
         }
-        float a = row[tid], b = row[R + tid];
-        re = __fsub_rn(__fmul_rn(a, pr), __fmul_rn(b, pi));
-        im = __fadd_rn(__fmul_rn(a, pi), __fmul_rn(b, pr));
+    }
+    if (tid < WP) row[tid] = a;                  // WP <= 256 = blockDim
+    __syncthreads();
+    float re = 0.f, im = 0.f;
+    if (tid < R) {
+        float x0 = row[tid], x1 = row[R + tid];
+        re = __fsub_rn(__fmul_rn(x0, pr), __fmul_rn(x1, pi));
+        im = __fadd_rn(__fmul_rn(x0, pi), __fmul_rn(x1, pr));
     }
     __syncthreads();
     if (tid < R) { row[tid] = re; row[R + tid] = im; }
@@ -262,6 +298,8 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
     if (!latent) return;
     const int slot = slots[tok];
     if (slot < 0 || slot >= n_pages * PKV_PAGE_TOKENS) return;
+    if (v_rows)
+        for (int i = tid; i < v_vecs; i += 256) v_pool[(size_t)slot * v_vecs + i] = v_rows[(size_t)tok * v_vecs + i];
     const int NB = WP / 16, RB = WP / 2;
     if (tid < NB) {
         float v[16];
@@ -278,17 +316,26 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
 
 template <typename XT>
 int launch_write_small(const pkv_layer_t* L, const pkv_cache_t* C, const void* x, const int32_t* pos, const float* ph,
-                       const int32_t* slots, int n, float* latent_out, float* scratch, cudaStream_t st) {
+                       const int32_t* slots, int n, float* latent_out, float* scratch, const void* v_rows,
+                       cudaStream_t st) {
     const int W = 2 * L->R + L->R_s, WP = pkv_padded_width(W);
+    const int n_slices = (L->d_model + SM_KC - 1) / SM_KC;
     auto kern = pkv_project_small_kernel<XT>;
-    constexpr int smem = SM_TOK * SM_KC * 4;
-    PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<WP / 8, 256, smem, st>>>(L->Bw_dev, (const XT*)x, n, L->d_model, W, WP, scratch);
-    PKV_LAUNCH_CHECK();
-    pkv_rotate_store_kernel<<<n, 256, 0, st>>>(scratch, pos, (const float2*)ph, L->head_dim / 2, slots, W, WP, L->R,
-                                               L->freq_dev, L->inv_freq_dev, L->attn_scale, L->second,
-                                               C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out);
-    PKV_LAUNCH_CHECK();
+    constexpr int smem = (SM_TOK * SM_KC + SM_COL * SM_BP) * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+        PKV_CUDA_TRY(cudaFuncSetAttribute(pkv_project_small_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        PKV_CUDA_TRY(cudaFuncSetAttribute(pkv_project_small_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(WP / SM_COL, n_slices), dim3(256), smem, st, L->Bw_dev, (const XT*)x, n,
+                                    L->d_model, W, WP, scratch));
+    const bool with_v = C && C->v_dev && v_rows;
+    PKV_CUDA_TRY(pkv_launch_chained(pkv_rotate_store_kernel, dim3(n), dim3(256), 0, st, scratch, n_slices, n, pos,
+                                    (const float2*)ph, L->head_dim / 2, slots, W, WP, L->R, L->freq_dev, L->inv_freq_dev,
+                                    L->attn_scale, L->second, C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out,
+                                    with_v ? (const uint4*)v_rows : nullptr, with_v ? (uint4*)C->v_dev : nullptr,
+                                    with_v ? C->n_kv * C->head_dim * 2 / 16 : 0));
     return PKV_OK;
 }
 
@@ -308,7 +355,8 @@ int pkv_check_layer(const pkv_layer_t* L) {
 
 extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                                const int32_t* positions_dev, const float* phasors_dev, const int32_t* slots_dev,
-                               int32_t n_tokens, float* latent_out_dev, float* scratch_dev, void* stream) {
+                               int32_t n_tokens, float* latent_out_dev, float* scratch_dev, const void* v_rows_dev,
+                               void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     const int W = 2 * layer->R + layer->R_s;
@@ -329,9 +377,14 @@ extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cach
     if (scratch_dev && n_tokens <= PKV_SMALL_WRITE_TOKENS) {
         if ((((uintptr_t)scratch_dev) & 15u) || (layer->d_model % 4)) return PKV_ERR_INVALID;
         return x_dtype == PKV_F32 ? launch_write_small<float>(layer, cache, x_dev, positions_dev, phasors_dev, slots_dev,
-                                                              n_tokens, latent_out_dev, scratch_dev, s)
+                                                              n_tokens, latent_out_dev, scratch_dev, v_rows_dev, s)
                                   : launch_write_small<uint16_t>(layer, cache, x_dev, positions_dev, phasors_dev,
-                                                                 slots_dev, n_tokens, latent_out_dev, scratch_dev, s);
+                                                                 slots_dev, n_tokens, latent_out_dev, scratch_dev,
+                                                                 v_rows_dev, s);
+    }
+    if (v_rows_dev && cache && cache->v_dev) {
+        int vst = pkv_v_write(cache, v_rows_dev, slots_dev, n_tokens, stream);
+        if (vst) return vst;
     }
     if (pkv_padded_width(W) == 128) {
         return x_dtype == PKV_F32
@@ -341,4 +394,9 @@ extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cach
     return x_dtype == PKV_F32
                ? launch_write<256, float>(layer, cache, x_dev, positions_dev, phasors_dev, slots_dev, n_tokens, latent_out_dev, s)
                : launch_write<256, uint16_t>(layer, cache, x_dev, positions_dev, phasors_dev, slots_dev, n_tokens, latent_out_dev, s);
+}
+
+extern "C" int64_t pkv_write_scratch_floats(int32_t n_tokens, int32_t d_model) {
+    if (n_tokens < 0 || d_model <= 0) return PKV_ERR_INVALID;
+    return (int64_t)n_tokens * PKV_MAX_WIDTH * ((d_model + 511) / 512);
 }

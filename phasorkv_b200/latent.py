@@ -103,7 +103,8 @@ class DecodeWorkspace:
         self.packed = torch.empty((batch, n_q, head_dim + 2), dtype=torch.float32, device=device)
         self.out = torch.empty((batch, n_q, head_dim), dtype=torch.float32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
-        self.wscratch = torch.empty((max(batch, 1), 256), dtype=torch.float32, device=device)   # decode-time write
+        self.counters = torch.zeros(max(batch, 1), dtype=torch.int32, device=device)   # fused merge; stay zero between calls
+        self.wscratch = None                                                  # decode-time write, see write_scratch()
 
 
 class PhasorKey:
@@ -181,7 +182,7 @@ class PhasorKey:
         phd = self._ph(ph)
         out = torch.empty((x.shape[0], self.cache_width), dtype=torch.float32, device=self.device)
         _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None, _lib.ptr(x), self._xdt(x), None, _lib.ptr(phd),
-                                               None, x.shape[0], _lib.ptr(out), None, _lib.current_stream()),
+                                               None, x.shape[0], _lib.ptr(out), None, None, _lib.current_stream()),
                    "pkv_cache_write")
         return out
 
@@ -222,8 +223,8 @@ class PhasorKey:
         _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(pc.c), _lib.ptr(qa), _lib.ptr(pt),
                                                pc.max_pages, _lib.ptr(sl), Tq, 1,
                                                _lib.ATTN_SCORES_ONLY | _lib.ATTN_SIMT, _lib.ptr(ws.partials),
-                                               _lib.ptr(S), Tk, _lib.ptr(ws.status), _lib.current_stream()),
-                   "pkv_decode_attn")
+                                               _lib.ptr(S), Tk, _lib.ptr(ws.status), None, None,
+                                               _lib.current_stream()), "pkv_decode_attn")
         return S.transpose(0, 1)
 
     # ------------------------------------------------------------------ B200 entry points
@@ -249,16 +250,23 @@ class PhasorKey:
         With ``cache=None`` only the unquantised rows are produced (into `latent_out`)."""
         L = self._layer()
         x = self._x(x)
+        if v is not None:
+            v = v.to(torch.bfloat16).contiguous()
         _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None if cache is None else ctypes.byref(cache.c),
                                                _lib.ptr(x), self._xdt(x),
                                                _lib.ptr(positions), None, _lib.ptr(slots), x.shape[0],
-                                               _lib.ptr(latent_out), _lib.ptr(scratch), _lib.current_stream()),
-                   "pkv_cache_write")
-        if v is not None:
-            cache.write_v(v, slots)
+                                               _lib.ptr(latent_out), _lib.ptr(scratch), _lib.ptr(v),
+                                               _lib.current_stream()), "pkv_cache_write")
 
     def workspace(self, batch: int, n_split: int) -> DecodeWorkspace:
-        return DecodeWorkspace(batch, self.n_q, self.head_dim, self.cache_width, n_split, self.device)
+        ws = DecodeWorkspace(batch, self.n_q, self.head_dim, self.cache_width, n_split, self.device)
+        ws.wscratch = self.write_scratch(batch)
+        return ws
+
+    def write_scratch(self, n_tokens: int) -> torch.Tensor:
+        """Scratch for the decode-time (<= 64 tokens) write path of `write_paged`."""
+        n = int(_lib.load().pkv_write_scratch_floats(max(n_tokens, 1), self.d_model))
+        return torch.empty(n, dtype=torch.float32, device=self.device)
 
     def default_splits(self, batch: int, max_tokens: int, simt: bool = False) -> int:
         """Token splits per sequence so that the grid fills the GPU a whole number of times."""
@@ -275,8 +283,9 @@ class PhasorKey:
                                           _lib.current_stream()), "pkv_absorb")
 
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
-                    scores_out: Optional[torch.Tensor] = None) -> None:
-        """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials."""
+                    scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> None:
+        """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
+        [B, H, d] the splits are merged as well (inside the same launch on the tensor-core path)."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
         qsrc = ws.qabs if simt else ws.qop
@@ -284,7 +293,9 @@ class PhasorKey:
         _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(qsrc),
                                                _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
                                                ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
-                                               stride, _lib.ptr(ws.status), _lib.current_stream()), "pkv_decode_attn")
+                                               stride, _lib.ptr(ws.status), _lib.ptr(out),
+                                               _lib.ptr(ws.counters) if out is not None else None,
+                                               _lib.current_stream()), "pkv_decode_attn")
 
     def merge_step(self, ws: DecodeWorkspace, normalise: bool = True, packed: bool = False,
                    out: Optional[torch.Tensor] = None) -> None:
@@ -308,8 +319,7 @@ class PhasorKey:
         if ws is None:
             ws = self.workspace(q.shape[0], self.default_splits(q.shape[0], cache.max_pages * PAGE_TOKENS, simt))
         self.absorb_step(q, positions, ws, operand=not simt)
-        self.attend_step(cache, ws, simt=simt, scores_only=scores_only)
-        self.merge_step(ws)
+        self.attend_step(cache, ws, simt=simt, scores_only=scores_only, out=ws.out)
         return ws.out
 
     # ------------------------------------------------------------------ plumbing

@@ -156,10 +156,13 @@ def _check_decode(sc, n_split, simt, scores_tol=LOGIT_TOL, out_tol=OUT_TOL):
     ws = sc.pk.workspace(sc.B, n_split)
     S = torch.zeros((sc.B, sc.spec.n_q, Tmax), device="cuda")
     sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=not simt)
-    sc.pk.attend_step(sc.cache, ws, simt=simt, scores_out=S)
-    sc.pk.merge_step(ws)
+    sc.pk.attend_step(sc.cache, ws, simt=simt, scores_out=S, out=ws.out)       # merge inside the attention launch
+    fused = ws.out.clone()
+    sc.pk.merge_step(ws)                                                       # the separate merge kernel
     torch.cuda.synchronize()
     assert int(ws.status.abs().sum()) == 0
+    assert int(ws.counters.abs().sum()) == 0                                   # the split counters reset themselves
+    assert rel(fused.cpu(), ws.out.cpu()) < 1e-6 or float(ws.out.abs().max()) == 0.0
     for b, T in enumerate(sc.seqlens):
         if T == 0:
             assert float(ws.out[b].abs().max()) == 0.0
@@ -244,10 +247,12 @@ def test_decode_time_write_path(config, n):
     the same cache content as the one-CTA-per-64-tokens kernel, up to summation order."""
     sc = Scenario(config, seqlens=(n,), pos0=32767)
     cache2 = sc.pk.new_cache(1, n)
-    scratch = torch.empty((n, 256), device="cuda")
+    scratch = sc.pk.write_scratch(n)
     out = torch.empty((n, sc.spec.cache_width), device="cuda")
     slots = sc.slots_of(0)
-    sc.pk.write_paged(cache2, sc.x[0].cuda(), sc.pos[0].to(torch.int32).cuda(), slots, latent_out=out, scratch=scratch)
+    sc.pk.write_paged(cache2, sc.x[0].cuda(), sc.pos[0].to(torch.int32).cuda(), slots, v=sc.v[0].cuda(), latent_out=out,
+                      scratch=scratch)
+    assert torch.equal(cache2.v[slots.long()].cpu(), sc.v[0])
     assert rel(out.cpu(), sc.rows_ref[0]) < 5e-6
     a, ca, sa = sc.cache.read(slots, sc.second)
     b, cb, sb = cache2.read(slots, sc.second)
@@ -326,3 +331,9 @@ def test_query_operand_expansion():
     vals = lv[nib.long()] * sc_f * row_scale[:, None]                  # [128 = term*32 + head, 256]
     recon = vals.reshape(4, 32, 256).sum(0)[:, :W]
     assert rel(recon, ws.qabs[0].cpu()) < 2e-4
+
+
+@pytest.mark.parametrize("n_split", [12, 13, 20])
+def test_tc_fused_merge_many_splits(n_split):
+    """More splits than the shared-memory staging of the fused merge holds: the L2 path takes over."""
+    _check_decode(Scenario("cfg2", seqlens=(3000, 129), gain=64.0, pos0=10000), n_split=n_split, simt=False)
