@@ -174,12 +174,14 @@ class Stack:
         x[:, self.outliers] *= 20.0
         return x
 
-    def step(self, events=None, scores_only=False, write=True):
+    def step(self, events=None, scores_only=False, write=True, pre=None, post=None):
         """One decode step over all layers. `events`: list receiving (start, end) CUDA events around
-        each attention launch."""
+        each attention launch. `pre(l)` / `post(l)` run on the host before / after layer l is enqueued."""
         n = 0
         for l, (pk, cache) in enumerate(zip(self.layers, self.caches)):
             ws = self.ws[l & 1]
+            if pre is not None:
+                pre(l)
             if write:
                 pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
                 n += 2
@@ -193,6 +195,8 @@ class Stack:
                 e1.record()
                 events.append((e0, e1))
             n += 2 + (1 if self.simt else 0)
+            if post is not None:
+                post(l)
         self.launches_per_layer = n // len(self.layers)
         return n
 
@@ -281,12 +285,39 @@ def run_b200(args):
     ho = torch.empty(st.out.shape, dtype=st.out.dtype).pin_memory()
     hx.copy_(st.x_new); hv.copy_(st.v_new); hq.copy_(st.q)
 
+    # Host copies ride on their own streams in groups of layers, so that the inputs of the next group
+    # arrive and the outputs of the previous one leave while a group computes; every byte still crosses
+    # inside the timed region, which ends only after the last output has landed in host memory.
+    GROUP = 4
+    groups = [(g, min(g + GROUP, L)) for g in range(0, L, GROUP)]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in groups]
+    ev_done = [torch.cuda.Event() for _ in groups]
+
     def e2e_step():
-        st.x_new.copy_(hx, non_blocking=True)
-        st.v_new.copy_(hv, non_blocking=True)
-        st.q.copy_(hq, non_blocking=True)
-        st.step()
-        ho.copy_(st.out, non_blocking=True)
+        main = torch.cuda.current_stream()
+        s_in.wait_stream(main)                      # the previous step has consumed its inputs
+        with torch.cuda.stream(s_in):
+            for gi, (a, b_) in enumerate(groups):
+                st.x_new[a:b_].copy_(hx[a:b_], non_blocking=True)
+                st.v_new[a:b_].copy_(hv[a:b_], non_blocking=True)
+                st.q[a:b_].copy_(hq[a:b_], non_blocking=True)
+                ev_in[gi].record(s_in)
+
+        def pre(l):
+            if l % GROUP == 0:
+                main.wait_event(ev_in[l // GROUP])
+
+        def post(l):
+            if (l + 1) % GROUP == 0 or l == L - 1:
+                gi = l // GROUP
+                ev_done[gi].record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[gi])
+                    a, b_ = groups[gi]
+                    ho[a:b_].copy_(st.out[a:b_], non_blocking=True)
+        st.step(pre=pre, post=post)
+        main.wait_stream(s_out)
     ms_e2e = timed(e2e_step, args.steps, args.warmup, dist)
     h2d = hx.numel() * hx.element_size() + hv.numel() * hv.element_size() + hq.numel() * hq.element_size()
     d2h = ho.numel() * ho.element_size()

@@ -23,7 +23,9 @@ extern "C" {
 
 #define PKV_PAGE_TOKENS 128          /* tokens per cache page */
 #define PKV_MAX_WIDTH   256          /* largest supported latent width W = 2R + R_s */
+#ifndef PKV_QUERY_TERMS
 #define PKV_QUERY_TERMS 4            /* NVFP4 residual terms of the absorbed query operand */
+#endif
 #define PKV_NOALLOC_MAX_PARTS 320     /* pkv_decode_attn_noalloc: upper bound on batch * n_split */
 #define PKV_SMALL_WRITE_TOKENS 64    /* pkv_cache_write spreads the projection over the GPU up to this n */
 
@@ -127,8 +129,10 @@ int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n
  * pkv_cache_write, phasors_dev [B, head_dim/2] complex64 (one of the two must be given).
  * qabs_out_dev: optional fp32 [B, n_q, W] in the reference layout [Re q' | Im q' | slow].
  * qop_out_dev: optional tensor-core operand, pkv_query_operand_bytes(W) per sequence: the absorbed
- * query as PKV_QUERY_TERMS NVFP4 residual terms (row = term*32 + head) in the same swizzled
- * code / scale layout as a cache page, followed by n_q*PKV_QUERY_TERMS fp32 per-row scales. */
+ * query as PKV_QUERY_TERMS NVFP4 residual terms that share one fp32 tensor scale per head: codes
+ * of a 128-row tile (row = term*32 + head) swizzled like a cache page; one 512-byte scale block per
+ * (term, 64-column step) whose 16-byte row `head` starts with the 4 E4M3 block scales of that step;
+ * then the 32 per-head tensor scales (padded to 512 bytes). */
 int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
                const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, void* stream);
 int64_t pkv_query_operand_bytes(int32_t W);

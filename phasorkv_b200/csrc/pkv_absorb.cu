@@ -39,7 +39,7 @@ constexpr int HG = 8;          // query heads per CTA
 //   stage 1: phasors of the query position (double angle, as the cache write does)
 //   stage 2: zq = (q[j] + i q[j + h]) * phasor, complex product in fp32
 //   stage 3: absorbed rows [Re q' | Im q' | slow] to shared memory (and to qabs_out)
-//   stage 4: PKV_QUERY_TERMS rounds of "quantise the residual to NVFP4 with a per-row tensor scale"
+//   stage 4: PKV_QUERY_TERMS rounds of "quantise the residual to NVFP4", one tensor scale per head row
 __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
     const float* __restrict__ q, const int32_t* __restrict__ positions, const float2* __restrict__ phasors, int n_q,
     int n_kv, int head_dim, int R, int R_s, int n_slow, const float* __restrict__ A_re, const float* __restrict__ A_im,
@@ -137,33 +137,42 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
     if (!qop_out) return;
     // ---- operand: row n = term * n_q + head of a 128-row tile in the cache-page layout
     const int NB = Wp / 16, RB = Wp / 2;
-    const int codes_bytes = pkv_codes_bytes(W), page_bytes = pkv_page_bytes(W);
+    // layout: codes of the 128-row tile (row = term * 32 + head, swizzled like a cache page) | one 512-byte
+    // scale block per (term, 64-column step): row `head` of 16 bytes starts with the 4 E4M3 scales of that
+    // step, the rest is zero | 32 fp32 tensor scales, one per head
+    const int codes_bytes = pkv_codes_bytes(W), KB = Wp / 64;
     uint8_t* blob = qop_out + (size_t)b * qop_bytes;
-    float* row_scale = reinterpret_cast<float*>(blob + page_bytes);
+    float* row_scale = reinterpret_cast<float*>(blob + codes_bytes + PKV_QUERY_TERMS * KB * 512);
     const bool live = tid < nh * NB;                  // <= 8 * 16 threads
     const int h = live ? tid / NB : 0, j = live ? tid % NB : 0;
     float res[16];
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < 16; ++i) res[i] = live ? row[h * Wp + j * 16 + i] : 0.0f;
-    for (int term = 0; term < PKV_QUERY_TERMS; ++term) {
-        if (tid < HG) amax_bits[tid] = 0u;
-        __syncthreads();
+    // one tensor scale per head row, shared by its residual terms: the terms then differ only in their
+    // E4M3 block scales and can be summed by the tensor core
+    if (tid < HG) amax_bits[tid] = 0u;
+    __syncthreads();
+    {
         float am = 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(res[i]));
         if (live) atomicMax(&amax_bits[h], __float_as_uint(am));      // non-negative floats order as integers
-        __syncthreads();
-        if (live) {
-            const float second = fmaxf(__uint_as_float(amax_bits[h]), 1e-30f) * (1.0f / (448.0f * 6.0f));
+    }
+    __syncthreads();
+    if (live) {
+        const float second = fmaxf(__uint_as_float(amax_bits[h]), 1e-30f) * (1.0f / (448.0f * 6.0f));
+        const float inv_second = __frcp_rn(second);
+        for (int term = 0; term < PKV_QUERY_TERMS; ++term) {
             uint8_t sb;
-            const uint2 packed = quantize_query_block16(res, second, __frcp_rn(second), sb);
-            uint32_t n = term * n_q + h0 + h;
+            const uint2 packed = quantize_query_block16(res, second, inv_second, sb);
+            const uint32_t n = term * n_q + h0 + h;
             *reinterpret_cast<uint2*>(blob + pkv_code_offset(n, j * 8, RB)) = packed;
-            blob[codes_bytes + pkv_scale_offset(n, j)] = sb;
-            if (j == 0) row_scale[n] = second;
+            uint8_t* sf = blob + codes_bytes + (term * KB + (j >> 2)) * 512 + (h0 + h) * 16;
+            sf[j & 3] = sb;
+            if (j & 3) *reinterpret_cast<uint32_t*>(sf + 4 * (j & 3)) = 0u;      // bytes 4..15 of the row stay zero
+            if (j == 0 && term == 0) row_scale[h0 + h] = second;
         }
-        __syncthreads();
     }
 }
 
@@ -171,7 +180,7 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
 
 extern "C" int64_t pkv_query_operand_bytes(int32_t W) {
     if (W <= 0 || W > PKV_MAX_WIDTH || (W % 16)) return PKV_ERR_UNSUPPORTED;
-    return pkv_page_bytes(W) + 128 * 4;
+    return pkv_codes_bytes(W) + PKV_QUERY_TERMS * (pkv_padded_width(W) / 64) * 512 + 512;
 }
 
 extern "C" int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,

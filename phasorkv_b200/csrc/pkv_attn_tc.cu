@@ -3,8 +3,9 @@
 // One CTA = one (sequence, token split). Seven warps, each with one job:
 //   warp 0     K producer : bulk-copies latent pages (codes + scales, already in operand layout) to smem
 //   warp 1     V producer : TMA tensor loads of the bf16 V page, one kv head (128 tokens x 128 dims) per stage
-//   warp 2     MMA issuer : S = C . Q'^T as block-scaled NVFP4 tcgen05.mma (tokens on M = 128, the four
-//                           NVFP4 residual terms of the 32 query heads on N = 128), scale factors copied
+//   warp 2     MMA issuer : S = C . Q'^T as block-scaled NVFP4 tcgen05.mma (tokens on M = 128, the 32 query
+//                           heads on N; the four NVFP4 residual terms of the query are four passes over
+//                           the same cache tile that accumulate in TMEM), scale factors copied
 //                           smem -> TMEM with tcgen05.cp; O^T += V^T . P^T as bf16 tcgen05.mma per kv head
 //   warps 3-6  softmax    : one token row (TMEM lane) per thread; online base-2 softmax whose reference
 //                           maximum only moves when a tile exceeds it by 2^8, P to smem as bf16, and the
@@ -25,6 +26,7 @@ using namespace pkv;
 
 constexpr int NQ = 32, DH = 128;
 constexpr int NK_STAGES = 2, NV_STAGES = 4;
+constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = PKV_PAGE_TOKENS * NQ * 2;              // bf16 P of one page, all heads
 constexpr int NTHREADS = 7 * 32;
@@ -32,10 +34,11 @@ constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logi
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // tensor memory columns
-constexpr uint32_t TM_S = 0;          // 2 x 128 : scores of two pages in flight
-constexpr uint32_t TM_O = 256;        // n_kv x 16 : O^T accumulators
-constexpr uint32_t TM_SFA = 384;      // 2 x 16 : cache scale factors
-constexpr uint32_t TM_SFB = 416;      // 16 : query scale factors
+constexpr int NSB = 4;                // score buffers: pages whose S = C.Q'^T may be in flight between MMA and softmax
+constexpr uint32_t TM_S = 0;          // NSB x 32 : scores (tokens x heads)
+constexpr uint32_t TM_O = 128;        // n_kv x 16 : O^T accumulators
+constexpr uint32_t TM_SFA = 256;      // NSB x 16 : cache scale factors, one set per score buffer
+constexpr uint32_t TM_SFB = 320;      // 4 x 16 : query scale factors, a 4-column group per (residual term, K step)
 constexpr uint32_t TM_COLS = 512;
 
 template <int WP>
@@ -44,7 +47,8 @@ struct Cfg {
     static constexpr int KB = WP / 64;                         // K = 64 MMA steps
     static constexpr int CODES = PKV_PAGE_TOKENS * RB;
     static constexpr int PAGE = CODES + KB * 512;
-    static constexpr int QBLOB = PAGE + 512;
+    static constexpr int SFQ = PKV_QUERY_TERMS * KB * 512;     // query scale blocks, one per (term, K step)
+    static constexpr int QBLOB = CODES + SFQ + 512;
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = ((QBLOB + 1023) / 1024) * 1024;
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
@@ -56,12 +60,13 @@ struct Cfg {
 };
 
 struct Extra {                       // lives at X_OFF
-    uint64_t q_full, k_full[NK_STAGES], k_empty[NK_STAGES], v_full[NV_STAGES], v_empty[NV_STAGES];
-    uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
+    uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_STAGES], v_empty[NV_STAGES];
+    uint64_t s_full[NSB], s_empty[NSB], p_full[2], pv_done[2];
     uint64_t sm_bar;                 // rendezvous of the 128 softmax threads (bounded, unlike bar.sync)
     uint32_t tmem_base;
     volatile int abort_flag;
     float wmax[2][4][NQ];
+    int wflag[2][4];
     float lsum[4][NQ];
 };
 
@@ -180,12 +185,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     // ---- prologue that touches no global memory: barriers, tensor memory
     if (tid == 0) {
         mbar_init(&X->q_full, 1);
-        for (int s = 0; s < NK_STAGES; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
+        for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
         for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128);
-            mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], 1);
-        }
+        for (int s = 0; s < NSB; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], 1); }
         mbar_init(&X->sm_bar, 128);
         X->abort_flag = 0;
         fence_barrier_init();
@@ -205,6 +208,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
     const int P = p_hi - p_lo;
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
+    const int nks = with_v ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
 
     if (P <= 0) {                                  // this split has no token: the neutral partial
@@ -226,8 +230,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
             bulk_g2s(smem + C::Q_OFF, qop + (size_t)b * qop_stride, C::QBLOB, &X->q_full);
             for (int i = 0; i < P; ++i) {
-                const int s = i % NK_STAGES;
-                if (i >= NK_STAGES && !wait_or_abort(&X->k_empty[s], ((i / NK_STAGES) - 1) & 1, X, status, 10)) break;
+                const int s = i % nks;
+                if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) break;
                 int pidx = page_table[(size_t)b * max_pages + p_lo + i];
                 if (pidx < 0 || pidx >= n_pages_pool) {              // never dereference a bad page index
                     X->abort_flag = 1;
@@ -240,8 +244,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             }
             if (X->abort_flag) {                                     // let copies in flight land before leaving
                 mbar_wait(&X->q_full, 0, 1u << 16);
-                for (int i = max(0, issued - NK_STAGES); i < issued; ++i)
-                    mbar_wait(&X->k_full[i % NK_STAGES], (i / NK_STAGES) & 1, 1u << 16);
+                for (int i = max(0, issued - nks); i < issued; ++i)
+                    mbar_wait(&X->k_full[i % nks], (i / nks) & 1, 1u << 16);
             }
         }
     } else if (warp == 1) {
@@ -270,13 +274,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     } else if (warp == 2) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_s = idesc_nvfp4(128, 128);
+            constexpr uint32_t idesc_s = idesc_nvfp4(128, NQ);
             constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
             bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
             if (ok) {
                 tc_fence_after_sync();
-                for (int k = 0; k < C::KB; ++k)
-                    tmem_cp_32x128b_warpx4(tb + TM_SFB + 4 * k, smem_desc(sbase + C::Q_OFF + C::CODES + k * 512, 0, 128, SWZ_NONE));
+                for (int blk = 0; blk < PKV_QUERY_TERMS * C::KB; ++blk)
+                    tmem_cp_32x128b_warpx4(tb + TM_SFB + 4 * blk,
+                                           smem_desc(sbase + C::Q_OFF + C::CODES + blk * 512, 0, 128, SWZ_NONE));
             }
             auto do_pv = [&](int i) -> bool {
                 const int pb = i & 1;
@@ -298,18 +303,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 return true;
             };
             for (int i = 0; i < P && ok; ++i) {
-                const int s = i % NK_STAGES, buf = i & 1;
-                ok = wait_or_abort(&X->k_full[s], (i / NK_STAGES) & 1, X, status, 33);
-                if (ok && i >= 2) ok = wait_or_abort(&X->s_empty[buf], ((i >> 1) - 1) & 1, X, status, 34);
+                const int s = i % nks, buf = i % NSB;
+                ok = wait_or_abort(&X->k_full[s], (i / nks) & 1, X, status, 33);
+                if (ok && i >= NSB) ok = wait_or_abort(&X->s_empty[buf], ((i / NSB) - 1) & 1, X, status, 34);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t ka = sbase + C::K_OFF + s * C::PAGE;
                 for (int k = 0; k < C::KB; ++k)
                     tmem_cp_32x128b_warpx4(tb + TM_SFA + 16 * buf + 4 * k, smem_desc(ka + C::CODES + k * 512, 0, 128, SWZ_NONE));
-                for (int k = 0; k < C::KB; ++k)
-                    mma_nvfp4(tb + TM_S + 128 * buf, smem_desc(ka + k * 32, 0, C::SBO, C::SWZ),
-                              smem_desc(sbase + C::Q_OFF + k * 32, 0, C::SBO, C::SWZ), idesc_s,
-                              tb + TM_SFA + 16 * buf + 4 * k, tb + TM_SFB + 4 * k, k > 0);
+                // the four residual terms of the query (rows 32 t .. 32 t + 31 of its tile) all accumulate into
+                // the same 32 columns: the tensor core adds them up, the tile of cache codes is reused as is
+                for (int t = 0; t < PKV_QUERY_TERMS; ++t)
+                    for (int k = 0; k < C::KB; ++k)
+                        mma_nvfp4(tb + TM_S + 32 * buf, smem_desc(ka + k * 32, 0, C::SBO, C::SWZ),
+                                  smem_desc(sbase + C::Q_OFF + t * NQ * C::RB + k * 32, 0, C::SBO, C::SWZ), idesc_s,
+                                  tb + TM_SFA + 16 * buf + 4 * k, tb + TM_SFB + 4 * (t * C::KB + k), (t | k) != 0);
                 tc_commit(&X->k_empty[s]);
                 tc_commit(&X->s_full[buf]);
                 if (with_v && i >= 1) ok = do_pv(i - 1);
@@ -321,11 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;
         const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
-        const float* rs = reinterpret_cast<const float*>(smem + C::Q_OFF + C::PAGE);     // [term*32 + head] tensor scales
-        float l[NQ];
-#pragma unroll
-        for (int h = 0; h < NQ; ++h) l[h] = 0.0f;
-        float m_ref = -INFINITY;                            // lane h keeps head h's reference maximum
+        const float* rs = reinterpret_cast<const float*>(smem + C::Q_OFF + C::CODES + C::SFQ);     // [head] tensor scale of the query operand
         // waits are made warp-uniform: the warp-collective instructions below need all 32 lanes
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int where) -> bool {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, X, status, where));
@@ -335,75 +339,95 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             mbar_arrive(&X->sm_bar);
             return wait_all(&X->sm_bar, (sync_phase++) & 1, 45);
         };
+        // Per head (all kept in registers, identical in every thread that shares statistics): the
+        // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
+        // this thread's share of the sum of 2^(s - m).
+        float cs[NQ], m[NQ], l[NQ];
         bool ok = wait_all(&X->q_full, 0, 40);
+#pragma unroll
+        for (int h = 0; h < NQ; ++h) { cs[h] = ok ? rs[h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
         for (int i = 0; i < P && ok; ++i) {
-            const int buf = i & 1;
-            ok = wait_all(&X->s_full[buf], (i >> 1) & 1, 41);
+            const int sb = i % NSB;                         // score buffer
+            const int buf = i & 1;                          // P buffer and exchange slots
+            ok = wait_all(&X->s_full[sb], (i / NSB) & 1, 41);
             if (!ok) break;
             tc_fence_after_sync();
             float s[NQ];
-#pragma unroll
-            for (int h = 0; h < NQ; ++h) s[h] = 0.0f;
-#pragma unroll
-            for (int term = 0; term < PKV_QUERY_TERMS; ++term) {
+            {
                 uint32_t r[32];
-                tmem_ld32(tl + TM_S + 128 * buf + 32 * term, r);
+                tmem_ld32(tl + TM_S + 32 * sb, r);
                 tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) s[h] = fmaf(__uint_as_float(r[h]), rs[term * NQ + h] * col_scale, s[h]);
+                for (int h = 0; h < NQ; ++h) s[h] = __uint_as_float(r[h]) * cs[h];
             }
-            tc_fence_before_sync();
-            mbar_arrive(&X->s_empty[buf]);                  // the MMA warp may overwrite this S buffer
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
             const bool valid = token < T;
             if (scores_out && valid) {
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) scores_out[((size_t)b * NQ + h) * scores_stride + token] = s[h] * inv_logit_scale;
             }
-            // ---- tile maximum per head: warp reduction, then across the four warps through smem
-            float wm = -INFINITY;
+            // ---- does any head of any row outgrow its reference maximum by more than the threshold?
+            float exc = -INFINITY;
 #pragma unroll
             for (int h = 0; h < NQ; ++h) {
                 if (!valid) s[h] = -INFINITY;
-                uint32_t red = __reduce_max_sync(0xffffffffu, f2ord(s[h]));
-                if (lane == h) wm = ord2f(red);
+                exc = fmaxf(exc, s[h] - m[h]);              // +inf while the head has no reference yet
             }
-            X->wmax[buf][quad][lane] = wm;
-            ok = softmax_sync();
-            if (!ok) break;
-            const float tm = fmaxf(fmaxf(X->wmax[buf][0][lane], X->wmax[buf][1][lane]),
-                                   fmaxf(X->wmax[buf][2][lane], X->wmax[buf][3][lane]));
-            // ---- move the reference maximum only when some head outgrew it by the threshold
-            const bool grow = (i == 0) || (tm > m_ref + RESCALE_THRESHOLD);
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_new = fmaxf(m_ref, tm);
-                const float corr = (i == 0) ? 1.0f : exp2f(m_ref - m_new);
-                m_ref = m_new;
-                if (i > 0) {
-                    if (with_v) {
+            bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
+            if (with_v) {                                   // P.V needs one reference per head for all 128 rows
+                if (lane == 0) X->wflag[buf][quad] = grow ? 1 : 0;
+                ok = softmax_sync();
+                if (!ok) break;
+                grow = (X->wflag[buf][0] | X->wflag[buf][1] | X->wflag[buf][2] | X->wflag[buf][3]) != 0;
+            }                                               // scores only: every warp keeps its own statistics
+            if (grow) {
+                // exact tile maximum per head: warp reduction, then (with V) across the four warps
+                float wm = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    const uint32_t red = __reduce_max_sync(0xffffffffu, f2ord(s[h]));
+                    if (lane == h) wm = ord2f(red);
+                }
+                float tm = wm;
+                if (with_v) {
+                    X->wmax[buf][quad][lane] = wm;
+                    ok = softmax_sync();
+                    if (!ok) break;
+                    tm = fmaxf(fmaxf(X->wmax[buf][0][lane], X->wmax[buf][1][lane]),
+                               fmaxf(X->wmax[buf][2][lane], X->wmax[buf][3][lane]));
+                    if (i > 0) {                            // the accumulators must be at rest before they are rescaled
                         ok = wait_all(&X->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, 42);
                         if (!ok) break;
                         tc_fence_after_sync();
-#pragma unroll
-                        for (int g = 0; g < NKV; ++g) {
-                            uint32_t r[4];
-                            const uint32_t a = tl + TM_O + 16 * g + (g % G16) * REP;
-                            // REP query heads of kv head g: columns (g % G16) * REP .. + REP - 1
-#pragma unroll
-                            for (int c0 = 0; c0 < REP; c0 += 4) {
-                                tmem_ld4(a + c0, r);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int c = 0; c < 4; ++c)
-                                    r[c] = __float_as_uint(__uint_as_float(r[c]) * __shfl_sync(0xffffffffu, corr, g * REP + c0 + c));
-                                tmem_st4(a + c0, r);
-                            }
-                        }
-                        tmem_st_wait();
-                        tc_fence_before_sync();
                     }
+                }
+                float corr[NQ];
 #pragma unroll
-                    for (int h = 0; h < NQ; ++h) l[h] *= __shfl_sync(0xffffffffu, corr, h);
+                for (int h = 0; h < NQ; ++h) {
+                    const float m_new = fmaxf(m[h], __shfl_sync(0xffffffffu, tm, h));
+                    corr[h] = m[h] > -INFINITY ? exp2f(m[h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
+                    m[h] = m_new;
+                    l[h] *= corr[h];
+                }
+                if (with_v && i > 0) {
+#pragma unroll
+                    for (int g = 0; g < NKV; ++g) {
+                        // REP query heads of kv head g: columns (g % G16) * REP .. + REP - 1 of its 16
+                        const uint32_t a = tl + TM_O + 16 * g + (g % G16) * REP;
+#pragma unroll
+                        for (int c0 = 0; c0 < REP; c0 += 4) {
+                            uint32_t r[4];
+                            tmem_ld4(a + c0, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[g * REP + c0 + c]);
+                            tmem_st4(a + c0, r);
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before_sync();
                 }
             }
             // ---- probabilities relative to the reference maximum; row sums stay per thread
@@ -414,7 +438,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * 512 + (row & 7) * 2;
 #pragma unroll
             for (int h = 0; h < NQ; ++h) {
-                const float p = exp2f(s[h] - __shfl_sync(0xffffffffu, m_ref, h));     // exp2(-inf) = 0 for masked rows
+                const float p = exp2f(s[h] - (m[h] > -INFINITY ? m[h] : 0.0f));       // exp2(-inf) = 0 for masked rows
                 l[h] += p;
                 if (with_v)
                     *reinterpret_cast<__nv_bfloat16*>(pbuf + (h >> 3) * 128 + (h & 7) * 16) = __float2bfloat16(p);
@@ -443,18 +467,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             } else {
                 for (int h = 0; h < NQ; ++h) part[h * (DH + 2) + row] = 0.0f;
             }
-            float lw = 0.0f;
+            float lw = 0.0f, mw = -INFINITY;
 #pragma unroll
             for (int h = 0; h < NQ; ++h) {
                 float v = l[h];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == h) lw = v;
+                if (lane == h) { lw = v; mw = m[h]; }
             }
             X->lsum[quad][lane] = lw;
+            X->wmax[0][quad][lane] = mw;                    // per warp in scores-only mode, identical otherwise
             if (softmax_sync() && quad == 0) {
-                part[lane * (DH + 2) + DH] = m_ref;
-                part[lane * (DH + 2) + DH + 1] = X->lsum[0][lane] + X->lsum[1][lane] + X->lsum[2][lane] + X->lsum[3][lane];
+                float M = -INFINITY, lt = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) M = fmaxf(M, X->wmax[0][w][lane]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                    if (X->wmax[0][w][lane] > -INFINITY) lt = fmaf(X->lsum[w][lane], exp2f(X->wmax[0][w][lane] - M), lt);
+                part[lane * (DH + 2) + DH] = M;
+                part[lane * (DH + 2) + DH + 1] = lt;
             }
         }
     }
