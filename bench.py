@@ -50,6 +50,7 @@ def parse():
     ap.add_argument("--context", type=int, default=0, help="override the configuration's context (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the token-sharded step eagerly instead of as a CUDA graph")
     ap.add_argument("--splits", type=int, default=0)
     return ap.parse_args()
 
@@ -246,6 +247,11 @@ def run_b200(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     dist = None
+    # stdout carries the one JSON line and nothing else: libraries that greet on file descriptor 1
+    # (NCCL prints its version there) are pointed at stderr until the line is written
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist_
         dist_.init_process_group("nccl", device_id=device)
@@ -358,6 +364,8 @@ def run_b200(args):
         line["seq_sharded"] = sharded
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=15.0)
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -383,24 +391,44 @@ def run_sharded(st, args, dist, world):
     def step():
         for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
             pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
-            pk.attend_step(cache, ws, simt=st.simt)
             if world > 1:
-                pk.merge_step(ws, normalise=False, packed=True)
+                pk.attend_step(cache, ws, simt=st.simt, packed_out=ws.packed)     # local splits merged in the same launch
                 dist.all_gather_into_tensor(gathered, ws.packed)
                 pk.merge_gathered(gathered, out)
             else:
-                pk.merge_step(ws)
+                pk.attend_step(cache, ws, simt=st.simt, out=out)
     for c in st.caches:
         c.page_table, c.seqlens, c.max_pages = pt, seqlens, pages
+    graphed = False
     try:
-        ms = timed(step, args.steps, args.warmup, dist)
+        fn = step
+        if not args.no_graph:
+            # at 1/8 of the tokens per GPU a layer lasts tens of microseconds: the step is replayed as one
+            # CUDA graph (kernels, all-gather and all) so that the host is out of the loop, as the
+            # reference times its kernels (scripts/bench_decode.py:29-49)
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step()
+                    step()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    step()
+                fn, graphed = g.replay, True
+            except Exception as e:                                  # capture refused: time the eager step
+                sys.stderr.write("graph capture of the sharded step failed: %r\n" % (e,))
+                torch.cuda.synchronize()
+        ms = timed(fn, args.steps, args.warmup, dist)
     finally:
         for c, s in zip(st.caches, saved):
             c.page_table, c.seqlens, c.max_pages = s
     per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
     return {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, args.layers),
             "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
-            "scaling": "strong", "collective": "all_gather of [B,H,d+2] fp32 per layer" if world > 1 else "none",
+            "scaling": "strong", "cuda_graph": graphed, "collective": "all_gather of [B,H,d+2] fp32 per layer" if world > 1 else "none",
             "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
             "hbm_gbs_per_gpu": round(per_gpu_bytes * args.layers / (ms * 1e-3) / 1e9, 1)}
 

@@ -42,6 +42,7 @@ enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
 /* flags of pkv_decode_attn */
 #define PKV_ATTN_SCORES_ONLY 1u      /* K path only: logits and log-sum-exp, V is not read */
 #define PKV_ATTN_SIMT        2u      /* CUDA-core scaffold kernel on the fp32 absorbed query */
+#define PKV_ATTN_PACKED_OUT  4u      /* out_dev receives the merged triple [B, n_q, head_dim+2] (o, m, l), not normalised */
 
 /* One layer's factors, in the attribute convention of phasorkv.latent.PhasorKey
  * (phasorkv/latent.py:47-54).  All arrays live in device memory and belong to the caller. */
@@ -148,7 +149,8 @@ int64_t pkv_query_operand_bytes(int32_t W);
  *   scores_out  : optional fp32 [B, n_q, scores_stride] unscaled scores (tests)
  *   status_dev  : optional int32[4]; kernels record a give-up of a bounded wait or an index out
  *                 of range here instead of trapping
- *   out_dev     : optional fp32 [B, n_q, head_dim]; when given, the splits are also merged (the
+ *   out_dev     : optional fp32 [B, n_q, head_dim] (with PKV_ATTN_PACKED_OUT: [B, n_q, head_dim+2], what
+ *                 a rank of a token-sharded sequence hands to the all-gather); when given, the splits are also merged (the
  *                 result of pkv_merge on `partials`) -- inside the same launch for the tensor-core
  *                 kernel, where the last CTA of each sequence to finish does it
  *   counters_dev: int32 [B], required with out_dev for the tensor-core kernel; zero them once when

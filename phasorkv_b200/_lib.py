@@ -16,7 +16,7 @@ MAX_WIDTH = 256
 QUERY_TERMS = 4
 NOALLOC_MAX_PARTS = 320
 F32, BF16 = 0, 1
-ATTN_SCORES_ONLY, ATTN_SIMT = 1, 2
+ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT = 1, 2, 4
 
 
 class PhasorKVError(RuntimeError):

@@ -253,7 +253,9 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
 #undef PKV_SIMT_CASE
     if (rc == PKV_OK && out_dev) {                         // the CUDA-core kernel merges with a second launch
         const int64_t pw = DH + 2;
-        rc = pkv_merge(partials_dev, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, out_dev, nullptr, stream);
+        const bool packed = (flags & PKV_ATTN_PACKED_OUT) != 0;
+        rc = pkv_merge(partials_dev, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, packed ? nullptr : out_dev,
+                       packed ? out_dev : nullptr, stream);
     }
     return rc;
 }

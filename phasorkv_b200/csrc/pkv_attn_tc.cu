@@ -111,7 +111,8 @@ struct MergeSmem {
 };
 
 __device__ __forceinline__ void count_and_merge(int32_t* counters, int b, int n_split, const float* partials, float* out,
-                                                MergeSmem* ms, float* big_smem, int big_smem_bytes, int32_t* status) {
+                                                bool packed, MergeSmem* ms, float* big_smem, int big_smem_bytes,
+                                                int32_t* status) {
     __threadfence();                                   // this thread's partial stores are visible device-wide
     __syncthreads();
     const int tid = threadIdx.x;
@@ -148,21 +149,29 @@ __device__ __forceinline__ void count_and_merge(int32_t* counters, int b, int n_
                 ms->w[tid][p] = wp;
                 den = fmaf(wp, big_smem[p * PART_FLOATS + tid * PW + DH + 1], den);
             }
-            const float inv = den > 0.0f ? 1.0f / den : 0.0f;
-            for (int p = 0; p < n_split; ++p) ms->w[tid][p] *= inv;
+            if (packed) {                              // the merged triple (o, m, l) of this sequence, not normalised
+                out[((size_t)b * NQ + tid) * PW + DH] = M;
+                out[((size_t)b * NQ + tid) * PW + DH + 1] = den;
+            } else {
+                const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+                for (int p = 0; p < n_split; ++p) ms->w[tid][p] *= inv;
+            }
         }
         __syncthreads();
+        const long ow = packed ? PW : DH;
         for (int e = tid; e < NQ * DH; e += NTHREADS) {
             const int h = e / DH, d = e % DH;
             float acc = 0.0f;
             for (int p = 0; p < n_split; ++p) acc = fmaf(ms->w[h][p], big_smem[p * PART_FLOATS + h * PW + d], acc);
-            out[((size_t)b * NQ + h) * DH + d] = acc;
+            out[((size_t)b * NQ + h) * ow + d] = acc;
         }
         return;
     }
     const int warp = tid >> 5, lane = tid & 31;
     for (int h = warp; h < NQ; h += NTHREADS / 32)
-        pkv_merge_warp(base + (size_t)h * PW, NQ * PW, n_split, DH, lane, out + ((size_t)b * NQ + h) * DH, nullptr);
+        pkv_merge_warp(base + (size_t)h * PW, NQ * PW, n_split, DH, lane,
+                       packed ? nullptr : out + ((size_t)b * NQ + h) * DH,
+                       packed ? out + ((size_t)b * NQ + h) * PW : nullptr);
 }
 
 template <int WP, int REP>
@@ -219,7 +228,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         tc_fence_before_sync();
         __syncthreads();
         if (warp == 2) tmem_dealloc(tb, TM_COLS);
-        if (out) count_and_merge(counters, b, n_split, partials, out, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
+        if (out) count_and_merge(counters, b, n_split, partials, out, (flags & PKV_ATTN_PACKED_OUT) != 0, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
         return;
     }
 
@@ -493,7 +502,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tb, TM_COLS);
-    if (out) count_and_merge(counters, b, n_split, partials, out, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
+    if (out) count_and_merge(counters, b, n_split, partials, out, (flags & PKV_ATTN_PACKED_OUT) != 0, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
 }
 
 // ------------------------------------------------------------------------------------------------ host
@@ -558,10 +567,23 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     }
     const bool wide = pkv_padded_width(cache->W) == 256;
     const uint8_t* qop = (const uint8_t*)q_dev;
+    // The merge inside the launch stages all splits of a sequence in shared memory at once; with more
+    // splits than fit there, a separate merge launch (128 CTAs wide) is the faster way.
+    const bool fuse = out_dev && n_split <= MERGE_MAX_SMEM_SPLITS &&
+                      (size_t)n_split * PART_FLOATS * 4 <= (size_t)(wide ? Cfg<256>::X_OFF : Cfg<128>::X_OFF);
+    float* fused_out = fuse ? out_dev : nullptr;
+    int rc;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
-    return launch_tc<WP_, R_>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
-                              partials_dev, scores_out_dev, scores_stride, status_dev, out_dev, counters_dev, stream)
+    rc = launch_tc<WP_, R_>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
+                            partials_dev, scores_out_dev, scores_stride, status_dev, fused_out, counters_dev, stream)
     if (rep == 4) { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }
-    if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8);
+    else { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
 #undef PKV_TC_CASE
+    if (rc == PKV_OK && out_dev && !fuse) {
+        const int64_t pw = DH + 2;
+        const bool packed = (flags & PKV_ATTN_PACKED_OUT) != 0;
+        rc = pkv_merge(partials_dev, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, packed ? nullptr : out_dev,
+                       packed ? out_dev : nullptr, stream);
+    }
+    return rc;
 }

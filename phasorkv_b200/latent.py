@@ -283,11 +283,14 @@ class PhasorKey:
                                           _lib.current_stream()), "pkv_absorb")
 
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
-                    scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> None:
+                    scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    packed_out: Optional[torch.Tensor] = None) -> None:
         """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
         [B, H, d] the splits are merged as well (inside the same launch on the tensor-core path)."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
+        if packed_out is not None:                      # merged (o, m, l) triple [B, H, d+2] instead of the normalised output
+            out, flags = packed_out, flags | _lib.ATTN_PACKED_OUT
         qsrc = ws.qabs if simt else ws.qop
         stride = 0 if scores_out is None else scores_out.shape[-1]
         _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(qsrc),

@@ -338,3 +338,22 @@ def test_query_operand_expansion():
 def test_tc_fused_merge_many_splits(n_split):
     """More splits than the shared-memory staging of the fused merge holds: the L2 path takes over."""
     _check_decode(Scenario("cfg2", seqlens=(3000, 129), gain=64.0, pos0=10000), n_split=n_split, simt=False)
+
+
+def test_tc_packed_output_for_sharding():
+    """The merged, not normalised triple a rank contributes to the all-gather, written by the attention
+    launch itself, equals what the separate merge kernel packs."""
+    sc = Scenario("cfg2", seqlens=(700, 0, 256), gain=32.0)
+    ws = sc.pk.workspace(sc.B, 3)
+    sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=True)
+    fused = torch.zeros_like(ws.packed)
+    sc.pk.attend_step(sc.cache, ws, packed_out=fused)
+    sc.pk.merge_step(ws, normalise=False, packed=True)
+    torch.cuda.synchronize()
+    assert torch.equal(fused[..., -2], ws.packed[..., -2])                       # maxima
+    assert torch.allclose(fused, ws.packed, rtol=1e-5, atol=1e-6)
+    gathered = torch.stack([fused, fused])                                       # two identical shards
+    out = torch.empty_like(ws.out)
+    sc.pk.merge_gathered(gathered, out)
+    sc.pk.merge_step(ws)
+    assert rel(out[0].cpu(), ws.out[0].cpu()) < 1e-5
