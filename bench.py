@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--context", type=int, default=0, help="override the configuration's context (profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
+                    help="token-sharded exchange: own peer-memory kernel, or NCCL all-gather + merge")
     ap.add_argument("--no-graph", action="store_true", help="time the token-sharded step eagerly instead of as a CUDA graph")
     ap.add_argument("--splits", type=int, default=0)
     return ap.parse_args()
@@ -387,14 +389,21 @@ def run_sharded(st, args, dist, world):
     out = torch.empty((B4, st.n_q, st.d), dtype=torch.float32, device=dev)
     qpos = torch.full((B4,), T4, dtype=torch.int32, device=dev)
     saved = [(c.page_table, c.seqlens, c.max_pages) for c in st.caches]
+    ex = None
+    if world > 1 and args.collective == "p2p":
+        from phasorkv_b200.sharded import ShardExchange
+        ex = ShardExchange.from_process_group(dist.group.WORLD, B4, st.n_q, st.d, dev)
 
     def step():
         for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
             pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
             if world > 1:
                 pk.attend_step(cache, ws, simt=st.simt, packed_out=ws.packed)     # local splits merged in the same launch
-                dist.all_gather_into_tensor(gathered, ws.packed)
-                pk.merge_gathered(gathered, out)
+                if ex is not None:
+                    ex.run(ws.packed, out)                  # peer stores + flags + merge, one kernel
+                else:
+                    dist.all_gather_into_tensor(gathered, ws.packed)
+                    pk.merge_gathered(gathered, out)
             else:
                 pk.attend_step(cache, ws, simt=st.simt, out=out)
     for c in st.caches:
@@ -428,7 +437,9 @@ def run_sharded(st, args, dist, world):
     per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
     return {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, args.layers),
             "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
-            "scaling": "strong", "cuda_graph": graphed, "collective": "all_gather of [B,H,d+2] fp32 per layer" if world > 1 else "none",
+            "scaling": "strong", "cuda_graph": graphed,
+            "collective": "none" if world == 1 else ("fused exchange+merge kernel over NVLink peer memory, [B,H,d+2] fp32 per layer"
+                                                     if ex is not None else "NCCL all_gather of [B,H,d+2] fp32 per layer + merge"),
             "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
             "hbm_gbs_per_gpu": round(per_gpu_bytes * args.layers / (ms * 1e-3) / 1e9, 1)}
 

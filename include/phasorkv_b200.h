@@ -169,6 +169,31 @@ int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const vo
 int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
               int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream);
 
+/* Token-sharded sequences (the token axis of every sequence split over the GPUs of one box; no
+ * counterpart in the reference, which is single-GPU): exchange of the per-rank merged triples
+ * [B, n_q, head_dim+2] over NVLink peer memory and their merge, in one launch per rank.
+ * The caller provides, on every rank, memory that all ranks can address (CUDA IPC, or
+ * torch.distributed._symmetric_memory): a gather buffer of 8-byte words
+ *   data : uint64 [2][world][B*n_q*(head_dim+2)], zero at start, 8-byte aligned
+ * (low half: a float of a triple; high half: the number of the exchange it belongs to, so that a
+ * value and its "arrived" mark travel in one store) and passes a device array with the addresses of
+ * all ranks' copies.  epoch_dev is local, uint32 [n_cta], zero at start.  All ranks must call with the
+ * same shapes, the same n_cta and the same number of calls.  A rank waits for its peers' words with a
+ * bounded poll; when it gives up, status[0] = 3 and out is left incomplete.  phases = PUSH | MERGE in
+ * production; the two phases can be launched separately (all pushes, then all merges) to drive
+ * several ranks' buffers from one GPU in tests. */
+#define PKV_EXCHANGE_PUSH  1u
+#define PKV_EXCHANGE_MERGE 2u
+typedef struct pkv_exchange {
+    int32_t world, rank;
+    int32_t batch, n_q, head_dim;
+    int32_t n_cta;                       /* CTAs of the launch; the rows = batch*n_q are split evenly over them */
+    void* const*     peer_data_dev;      /* device array [world]: address of rank r's gather buffer */
+    uint32_t*        epoch_dev;          /* local, [n_cta] */
+} pkv_exchange_t;
+int pkv_exchange_merge(const pkv_exchange_t* x, const float* packed_dev, float* out_dev, uint32_t phases,
+                       int32_t* status_dev, void* stream);
+
 /* Decode attention and merge for callers that cannot allocate device memory (no counterpart in the
  * reference, whose callers always allocate their own scratch with torch).  It is meant for hosts that
  * only ever receive input and output buffers -- a plugin inside another runtime's fixed memory plan, a

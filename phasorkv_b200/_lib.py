@@ -17,6 +17,7 @@ QUERY_TERMS = 4
 NOALLOC_MAX_PARTS = 320
 F32, BF16 = 0, 1
 ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT = 1, 2, 4
+EXCHANGE_PUSH, EXCHANGE_MERGE = 1, 2
 
 
 class PhasorKVError(RuntimeError):
@@ -29,6 +30,11 @@ class Layer(ctypes.Structure):
                 ("attn_scale", c_float), ("second", c_float),
                 ("Bw_dev", c_void_p), ("A_re_dev", c_void_p), ("A_im_dev", c_void_p), ("A_s_dev", c_void_p),
                 ("freq_dev", c_void_p), ("slow_dev", c_void_p), ("inv_freq_dev", c_void_p)]
+
+
+class Exchange(ctypes.Structure):
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("batch", c_int32), ("n_q", c_int32), ("head_dim", c_int32),
+                ("n_cta", c_int32), ("peer_data_dev", c_void_p), ("epoch_dev", c_void_p)]
 
 
 class Cache(ctypes.Structure):
@@ -56,6 +62,7 @@ SIGNATURES = {
                                   c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                           c_int32, c_void_p, c_void_p, c_void_p]),
+    "pkv_exchange_merge": (c_int32, [POINTER(Exchange), c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }

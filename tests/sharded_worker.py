@@ -1,0 +1,61 @@
+"""Child process of tests/test_gpu_multi.py: one rank of a token-sharded decode on its own GPU."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    from helpers import Scenario, rel
+    from phasorkv_b200.sharded import ShardExchange
+    T = 2048
+    full = Scenario("cfg2", seqlens=(T, T // 2), gain=64.0, pos0=50000)          # same seeds on every rank
+    ws_full = full.pk.workspace(full.B, 2)
+    full.pk.absorb_step(full.q.cuda(), full.qpos.cuda(), ws_full)
+    full.pk.attend_step(full.cache, ws_full, out=ws_full.out)
+    # this rank's token range of every sequence in its own cache
+    lens = [(rank + 1) * Tb // world - rank * Tb // world for Tb in full.seqlens]
+    cache = full.pk.new_cache(full.B, max(lens))
+    for b, Tb in enumerate(full.seqlens):
+        lo, hi = rank * Tb // world, (rank + 1) * Tb // world
+        n = hi - lo
+        seq = torch.full((n,), b, dtype=torch.int32, device=dev)
+        slots = cache.slots(seq, torch.arange(n, dtype=torch.int32, device=dev))
+        full.pk.write_paged(cache, full.x[b][lo:hi].cuda(), full.pos[b][lo:hi].to(torch.int32).cuda(), slots,
+                            v=full.v[b][lo:hi].cuda())
+    cache.seqlens.copy_(torch.tensor(lens, dtype=torch.int32))
+    ex = ShardExchange.from_process_group(dist.group.WORLD, full.B, full.spec.n_q, full.spec.head_dim, dev)
+    ws = full.pk.workspace(full.B, 2)
+    out = torch.empty_like(ws.out)
+    errs = []
+    for rnd in range(3):
+        full.pk.absorb_step(full.q.cuda(), full.qpos.cuda(), ws)
+        full.pk.attend_step(cache, ws, packed_out=ws.packed)
+        ex.run(ws.packed, out)
+        torch.cuda.synchronize()
+        errs.append(rel(out.cpu(), ws_full.out.cpu()))
+        assert int(ex.status.abs().sum()) == 0
+    # the NCCL route gives the same answer
+    gathered = torch.empty((world,) + tuple(ws.packed.shape), device=dev)
+    dist.all_gather_into_tensor(gathered, ws.packed)
+    out2 = torch.empty_like(out)
+    full.pk.merge_gathered(gathered, out2)
+    torch.cuda.synchronize()
+    errs.append(rel(out2.cpu(), out.cpu()))
+    print(f"rank {rank}: rel errors {errs}", flush=True)
+    assert max(errs[:3]) < 2e-3 and errs[3] < 1e-5
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -357,3 +357,52 @@ def test_tc_packed_output_for_sharding():
     sc.pk.merge_gathered(gathered, out)
     sc.pk.merge_step(ws)
     assert rel(out[0].cpu(), ws.out[0].cpu()) < 1e-5
+
+
+def test_exchange_merge_emulated_ranks():
+    """The fused exchange-and-merge kernel with 4 ranks' buffers on one GPU, driven phase by phase
+    (all pushes, then all merges: kernels that wait on one another never share a GPU). Three rounds,
+    so both slots and the epoch bookkeeping are exercised; every rank must obtain the merge of all
+    ranks' triples."""
+    from phasorkv_b200.sharded import ShardExchange
+    from phasorkv_b200 import _lib
+    G, B, H, d = 4, 3, 32, 128
+    ranks = ShardExchange.local_group(G, B, H, d)
+    pk = PhasorKey.from_spec(synth.make_layer("cfg2", 0))
+    gen = torch.Generator().manual_seed(5)
+    for rnd in range(3):
+        packed = torch.randn((G, B, H, d + 2), generator=gen)
+        packed[..., -2] *= 20.0                                        # maxima far apart
+        packed[..., -1] = packed[..., -1].abs() + 0.1                  # positive sums
+        packed[1, 2] = 0.0
+        packed[1, 2, :, -2] = float("-inf")                            # a rank that saw no token of sequence 2
+        dev = packed.cuda()
+        want = torch.empty((B, H, d), device="cuda")
+        pk.merge_gathered(dev, want)
+        outs = [torch.full((B, H, d), float("nan"), device="cuda") for _ in range(G)]
+        for r in range(G):
+            ranks[r].run(dev[r], None, _lib.EXCHANGE_PUSH)
+        for r in range(G):
+            ranks[r].run(None, outs[r], _lib.EXCHANGE_MERGE)
+        torch.cuda.synchronize()
+        for r in range(G):
+            assert int(ranks[r].status.abs().sum()) == 0
+            assert torch.allclose(outs[r], want, rtol=1e-5, atol=1e-6), (rnd, r)
+            assert int(ranks[r]._epoch[0]) == rnd + 1
+
+
+def test_exchange_gives_up_when_a_rank_never_pushes():
+    """A peer that never delivers: the merge phase runs out of its bounded wait, reports it in the
+    status word and leaves the output untouched; the context stays usable."""
+    from phasorkv_b200.sharded import ShardExchange
+    from phasorkv_b200 import _lib
+    G, B, H, d = 2, 1, 32, 128
+    ranks = ShardExchange.local_group(G, B, H, d, n_cta=4)
+    packed = torch.ones((B, H, d + 2), device="cuda")
+    out = torch.full((B, H, d), 7.0, device="cuda")
+    ranks[0].run(packed, None, _lib.EXCHANGE_PUSH)                     # rank 1 stays silent
+    ranks[0].run(None, out, _lib.EXCHANGE_MERGE)
+    torch.cuda.synchronize()
+    assert ranks[0].status[0].item() == 3
+    assert float(out.min()) == 7.0 and int(ranks[0]._epoch.sum()) == 0
+    assert float((packed * 2).sum()) > 0                               # the device still answers
