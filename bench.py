@@ -193,11 +193,12 @@ class Stack:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, out=self.out[l])
+            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
-            n += 2 + (1 if self.simt else 0)
+            pk.merge_step(ws, out=self.out[l])
+            n += 3
             if post is not None:
                 post(l)
         self.launches_per_layer = n // len(self.layers)

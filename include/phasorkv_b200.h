@@ -149,17 +149,15 @@ int64_t pkv_query_operand_bytes(int32_t W);
  *   scores_out  : optional fp32 [B, n_q, scores_stride] unscaled scores (tests)
  *   status_dev  : optional int32[4]; kernels record a give-up of a bounded wait or an index out
  *                 of range here instead of trapping
- *   out_dev     : optional fp32 [B, n_q, head_dim] (with PKV_ATTN_PACKED_OUT: [B, n_q, head_dim+2], what
- *                 a rank of a token-sharded sequence hands to the all-gather); when given, the splits are also merged (the
- *                 result of pkv_merge on `partials`) -- inside the same launch for the tensor-core
- *                 kernel, where the last CTA of each sequence to finish does it
- *   counters_dev: int32 [B], required with out_dev for the tensor-core kernel; zero them once when
- *                 allocating, every launch leaves them at zero again */
+ *   out_dev     : optional fp32 [B, n_q, head_dim] (with PKV_ATTN_PACKED_OUT: [B, n_q, head_dim+2], the
+ *                 not normalised triple a rank of a token-sharded sequence hands to the exchange);
+ *                 when given, the splits are merged as well (pkv_merge on `partials`, enqueued
+ *                 right behind the attention kernel) */
 int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                     const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
                     int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
                     float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
-                    int32_t* counters_dev, void* stream);
+                    void* stream);
 
 /* Log-sum-exp merge of n_parts partial triples per (sequence, head): M = max m, w = 2^(m - M),
  * O = sum w o / sum w l (phasorkv/kernels/dense_attn.py:72-74).  parts_dev is addressed as

@@ -59,7 +59,7 @@ SIGNATURES = {
     "pkv_cache_read": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_absorb": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
-                                  c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                  c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                           c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_exchange_merge": (c_int32, [POINTER(Exchange), c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),

@@ -13,10 +13,10 @@
 // Stages are handed over through mbarriers; every wait is bounded and a give-up is recorded in
 // `status` while all roles unwind, free TMEM and return.
 #include "pkv_common.cuh"
-#include "pkv_merge.cuh"
 #include "pkv_tcgen05.cuh"
 
 #include <cudaTypedefs.h>
+#include <cstdlib>
 
 int pkv_check_layer(const pkv_layer_t* L);
 
@@ -94,93 +94,13 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
     return false;
 }
 
-// Fused merge: every CTA of a sequence bumps that sequence's counter once its partial is written and
-// fenced; the CTA that brings it to n_split owns the merge of all splits into `out` and puts the
-// counter back to zero, so the counters only ever need zeroing when they are allocated.
-// The merge sits on the tail of the launch, so it is built for latency: the partial blocks of the
-// sequence (16,640 contiguous bytes per split) are pulled into the now idle shared memory with one
-// bulk copy each, all in flight at once, and reduced from there. When they do not fit, the loads go
-// straight to L2 instead.
-constexpr int PART_FLOATS = NQ * (DH + 2);
-constexpr int MERGE_MAX_SMEM_SPLITS = 16;
-
-struct MergeSmem {
-    uint64_t bar;
-    int is_last;
-    float w[NQ][MERGE_MAX_SMEM_SPLITS];
-};
-
-__device__ __forceinline__ void count_and_merge(int32_t* counters, int b, int n_split, const float* partials, float* out,
-                                                bool packed, MergeSmem* ms, float* big_smem, int big_smem_bytes,
-                                                int32_t* status) {
-    __threadfence();                                   // this thread's partial stores are visible device-wide
-    __syncthreads();
-    const int tid = threadIdx.x;
-    if (tid == 0) {
-        const int prev = atomicAdd(&counters[b], 1);
-        ms->is_last = (prev == n_split - 1);
-        if (prev == n_split - 1) counters[b] = 0;
-        __threadfence();
-    }
-    __syncthreads();
-    if (!ms->is_last) return;
-    const long PW = DH + 2;
-    const float* base = partials + (size_t)b * n_split * PART_FLOATS;
-    const bool staged = n_split <= MERGE_MAX_SMEM_SPLITS && n_split * PART_FLOATS * 4 <= big_smem_bytes;
-    if (staged) {
-        if (tid == 0) {
-            mbar_init(&ms->bar, 1);
-            fence_barrier_init();
-            asm volatile("fence.proxy.async.global;" ::: "memory");     // other CTAs' stores before the async-proxy reads
-            mbar_arrive_expect_tx(&ms->bar, (uint32_t)(n_split * PART_FLOATS * 4));
-            for (int p = 0; p < n_split; ++p)
-                bulk_g2s(big_smem + (size_t)p * PART_FLOATS, base + (size_t)p * PART_FLOATS, PART_FLOATS * 4, &ms->bar);
-        }
-        __syncthreads();
-        bool ok = mbar_wait(&ms->bar, 0, 1u << 22);
-        if (!ok && status) { atomicExch(&status[0], 1); atomicExch(&status[1], 50); }
-        ok = __syncthreads_and(ok);
-        if (!ok) return;
-        if (tid < NQ) {
-            float M = -INFINITY, den = 0.0f;
-            for (int p = 0; p < n_split; ++p) M = fmaxf(M, big_smem[p * PART_FLOATS + tid * PW + DH]);
-            for (int p = 0; p < n_split; ++p) {
-                const float wp = M > -INFINITY ? exp2f(big_smem[p * PART_FLOATS + tid * PW + DH] - M) : 0.0f;
-                ms->w[tid][p] = wp;
-                den = fmaf(wp, big_smem[p * PART_FLOATS + tid * PW + DH + 1], den);
-            }
-            if (packed) {                              // the merged triple (o, m, l) of this sequence, not normalised
-                out[((size_t)b * NQ + tid) * PW + DH] = M;
-                out[((size_t)b * NQ + tid) * PW + DH + 1] = den;
-            } else {
-                const float inv = den > 0.0f ? 1.0f / den : 0.0f;
-                for (int p = 0; p < n_split; ++p) ms->w[tid][p] *= inv;
-            }
-        }
-        __syncthreads();
-        const long ow = packed ? PW : DH;
-        for (int e = tid; e < NQ * DH; e += NTHREADS) {
-            const int h = e / DH, d = e % DH;
-            float acc = 0.0f;
-            for (int p = 0; p < n_split; ++p) acc = fmaf(ms->w[h][p], big_smem[p * PART_FLOATS + h * PW + d], acc);
-            out[((size_t)b * NQ + h) * ow + d] = acc;
-        }
-        return;
-    }
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int h = warp; h < NQ; h += NTHREADS / 32)
-        pkv_merge_warp(base + (size_t)h * PW, NQ * PW, n_split, DH, lane,
-                       packed ? nullptr : out + ((size_t)b * NQ + h) * DH,
-                       packed ? out + ((size_t)b * NQ + h) * PW : nullptr);
-}
-
 template <int WP, int REP>
 __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     const __grid_constant__ CUtensorMap vmap, const uint8_t* __restrict__ qop, long qop_stride,
     const uint8_t* __restrict__ latent, const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
-    int32_t* __restrict__ status, float* __restrict__ out, int32_t* __restrict__ counters) {
+    int32_t* __restrict__ status) {
     using C = Cfg<WP>;
     constexpr int NKV = NQ / REP;                 // kv heads
     constexpr int G16 = 16 / REP;                 // kv heads per 16-head group of P rows
@@ -188,7 +108,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     Extra* X = reinterpret_cast<Extra*>(smem + C::X_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
-    __shared__ MergeSmem merge_smem;
     pkv_grid_launch_dependents();
 
     // ---- prologue that touches no global memory: barriers, tensor memory
@@ -228,7 +147,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         tc_fence_before_sync();
         __syncthreads();
         if (warp == 2) tmem_dealloc(tb, TM_COLS);
-        if (out) count_and_merge(counters, b, n_split, partials, out, (flags & PKV_ATTN_PACKED_OUT) != 0, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
         return;
     }
 
@@ -502,7 +420,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tb, TM_COLS);
-    if (out) count_and_merge(counters, b, n_split, partials, out, (flags & PKV_ATTN_PACKED_OUT) != 0, &merge_smem, reinterpret_cast<float*>(smem), C::X_OFF, status);
 }
 
 // ------------------------------------------------------------------------------------------------ host
@@ -531,7 +448,7 @@ int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
 template <int WP, int REP>
 int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
-              long scores_stride, int32_t* status, float* out, int32_t* counters, cudaStream_t st) {
+              long scores_stride, int32_t* status, cudaStream_t st) {
     auto kern = pkv_attn_tc_kernel<WP, REP>;
     constexpr int smem = Cfg<WP>::SMEM;
     static bool attr_done = false;                                  // once per instantiation
@@ -542,7 +459,7 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
     const float logit_scale = PKV_LOG2E / sqrtf((float)L->head_dim);
     PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch), dim3(NTHREADS), smem, st, vmap, qop, (long)Cfg<WP>::QBLOB,
                                     C->latent_dev, pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
-                                    1.0f / logit_scale, flags, partials, scores, scores_stride, status, out, counters));
+                                    1.0f / logit_scale, flags, partials, scores, scores_stride, status));
     return PKV_OK;
 }
 
@@ -551,9 +468,7 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, float* out_dev, int32_t* counters_dev,
-                       cudaStream_t stream) {
-    if (out_dev && !counters_dev) return PKV_ERR_INVALID;
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream) {
     const int rep = layer->n_q / layer->n_kv;
     if (rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;          // P.V on tensor cores needs >= 4 query heads per kv head
     if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
@@ -567,19 +482,14 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     }
     const bool wide = pkv_padded_width(cache->W) == 256;
     const uint8_t* qop = (const uint8_t*)q_dev;
-    // The merge inside the launch stages all splits of a sequence in shared memory at once; with more
-    // splits than fit there, a separate merge launch (128 CTAs wide) is the faster way.
-    const bool fuse = out_dev && n_split <= MERGE_MAX_SMEM_SPLITS &&
-                      (size_t)n_split * PART_FLOATS * 4 <= (size_t)(wide ? Cfg<256>::X_OFF : Cfg<128>::X_OFF);
-    float* fused_out = fuse ? out_dev : nullptr;
     int rc;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
     rc = launch_tc<WP_, R_>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
-                            partials_dev, scores_out_dev, scores_stride, status_dev, fused_out, counters_dev, stream)
+                            partials_dev, scores_out_dev, scores_stride, status_dev, stream)
     if (rep == 4) { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }
     else { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
 #undef PKV_TC_CASE
-    if (rc == PKV_OK && out_dev && !fuse) {
+    if (rc == PKV_OK && out_dev) {                  // the merge of the splits: a second, latency-tuned launch
         const int64_t pw = DH + 2;
         const bool packed = (flags & PKV_ATTN_PACKED_OUT) != 0;
         rc = pkv_merge(partials_dev, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, packed ? nullptr : out_dev,

@@ -14,8 +14,7 @@ int pkv_check_cache(const pkv_cache_t* c);
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, float* out_dev, int32_t* counters_dev,
-                       cudaStream_t stream);
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream);
 
 namespace {
 
@@ -67,7 +66,7 @@ extern "C" int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache
     // every (sequence, split) slot of the scratch is written in full by the attention kernel before
     // the merge reads it, so nothing left over from an earlier call can leak into this one
     st = pkv_attn_tc_launch(layer, cache, qop_dev, page_table_dev, max_pages, seqlens_dev, batch, n_split, 0u, scratch,
-                            nullptr, 0, status_dev, nullptr, nullptr, (cudaStream_t)stream);
+                            nullptr, 0, status_dev, nullptr, (cudaStream_t)stream);
     if (st) return st;
     const int64_t pw = DH + 2;
     return pkv_merge(scratch, (int64_t)n_split * NQ * pw, NQ * pw, n_split, batch, NQ, DH, out_dev, nullptr, stream);

@@ -103,7 +103,6 @@ class DecodeWorkspace:
         self.packed = torch.empty((batch, n_q, head_dim + 2), dtype=torch.float32, device=device)
         self.out = torch.empty((batch, n_q, head_dim), dtype=torch.float32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
-        self.counters = torch.zeros(max(batch, 1), dtype=torch.int32, device=device)   # fused merge; stay zero between calls
         self.wscratch = None                                                  # decode-time write, see write_scratch()
 
 
@@ -223,7 +222,7 @@ class PhasorKey:
         _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(pc.c), _lib.ptr(qa), _lib.ptr(pt),
                                                pc.max_pages, _lib.ptr(sl), Tq, 1,
                                                _lib.ATTN_SCORES_ONLY | _lib.ATTN_SIMT, _lib.ptr(ws.partials),
-                                               _lib.ptr(S), Tk, _lib.ptr(ws.status), None, None,
+                                               _lib.ptr(S), Tk, _lib.ptr(ws.status), None,
                                                _lib.current_stream()), "pkv_decode_attn")
         return S.transpose(0, 1)
 
@@ -286,7 +285,7 @@ class PhasorKey:
                     scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                     packed_out: Optional[torch.Tensor] = None) -> None:
         """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
-        [B, H, d] the splits are merged as well (inside the same launch on the tensor-core path)."""
+        [B, H, d] the splits are merged as well (a merge launch enqueued right behind)."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
         if packed_out is not None:                      # merged (o, m, l) triple [B, H, d+2] instead of the normalised output
@@ -297,7 +296,6 @@ class PhasorKey:
                                                _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
                                                ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
                                                stride, _lib.ptr(ws.status), _lib.ptr(out),
-                                               _lib.ptr(ws.counters) if out is not None else None,
                                                _lib.current_stream()), "pkv_decode_attn")
 
     def merge_step(self, ws: DecodeWorkspace, normalise: bool = True, packed: bool = False,
