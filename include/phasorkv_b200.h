@@ -42,6 +42,9 @@ enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
 /* flags of pkv_decode_attn */
 #define PKV_ATTN_SCORES_ONLY 1u      /* K path only: logits and log-sum-exp, V is not read */
 #define PKV_ATTN_SIMT        2u      /* CUDA-core scaffold kernel on the fp32 absorbed query */
+#define PKV_ATTN_EARLY_STREAM 8u     /* the launch directly before this one on the stream is pkv_absorb (it writes
+                                        neither cache nor page table nor lengths): cache pages are streamed
+                                        while it still runs, only the query operand is waited for */
 #define PKV_ATTN_PACKED_OUT  4u      /* out_dev receives the merged triple [B, n_q, head_dim+2] (o, m, l), not normalised */
 
 /* One layer's factors, in the attribute convention of phasorkv.latent.PhasorKey
@@ -59,6 +62,9 @@ typedef struct pkv_layer {
     const int32_t* freq_dev;         /* [R] frequency index of each complex latent dim */
     const int32_t* slow_dev;         /* [n_slow] or NULL */
     const double*  inv_freq_dev;     /* [head_dim/2] rotary inverse frequencies */
+    const void*    Bw_bf16x3_dev;    /* optional bf16 [3][Wp][D], Wp = 128 if 2R+R_s <= 128 else 256: Bw as the sum of
+                                        three bf16 matrices (hi, mid, lo; rows past 2R+R_s zero).  Enables the
+                                        tensor-core cache write for bf16 x; NULL selects the CUDA-core kernels */
 } pkv_layer_t;
 
 /* The paged cache of one layer.  A page holds PKV_PAGE_TOKENS tokens.
@@ -108,11 +114,14 @@ int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev, const int
  * sequence) the projection is split by latent column and by d_model slice over many SMs and staged
  * through it; otherwise one CTA per 64 tokens does everything on chip and the scratch is not touched.
  * v_rows_dev: optional bf16 value rows [n, n_kv*head_dim] stored into the V pages at the same slots
- * (the same effect as a following pkv_v_write, without a further launch on the small path). */
+ * (the same effect as a following pkv_v_write, without a further launch on the small path).
+ * Larger n with bf16 x and layer->Bw_bf16x3_dev set run on the tensor cores (128 tokens per CTA,
+ * three bf16 passes that reproduce the fp32 factors to 2^-24); status_dev (optional int32[4]) receives
+ * a give-up of one of that kernel's bounded waits. */
 int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                     const int32_t* positions_dev, const float* phasors_dev, const int32_t* slots_dev,
                     int32_t n_tokens, float* latent_out_dev, float* scratch_dev, const void* v_rows_dev,
-                    void* stream);
+                    int32_t* status_dev, void* stream);
 int64_t pkv_write_scratch_floats(int32_t n_tokens, int32_t d_model);
 
 /* bf16 value rows v_dev [n, n_kv*head_dim] into the V pages at slots_dev [n]. */

@@ -16,7 +16,7 @@ MAX_WIDTH = 256
 QUERY_TERMS = 4
 NOALLOC_MAX_PARTS = 320
 F32, BF16 = 0, 1
-ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT = 1, 2, 4
+ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT, ATTN_EARLY_STREAM = 1, 2, 4, 8
 EXCHANGE_PUSH, EXCHANGE_MERGE = 1, 2
 
 
@@ -29,7 +29,7 @@ class Layer(ctypes.Structure):
                 ("R", c_int32), ("R_s", c_int32), ("n_slow", c_int32),
                 ("attn_scale", c_float), ("second", c_float),
                 ("Bw_dev", c_void_p), ("A_re_dev", c_void_p), ("A_im_dev", c_void_p), ("A_s_dev", c_void_p),
-                ("freq_dev", c_void_p), ("slow_dev", c_void_p), ("inv_freq_dev", c_void_p)]
+                ("freq_dev", c_void_p), ("slow_dev", c_void_p), ("inv_freq_dev", c_void_p), ("Bw_bf16x3_dev", c_void_p)]
 
 
 class Exchange(ctypes.Structure):
@@ -53,7 +53,7 @@ SIGNATURES = {
     "pkv_query_operand_bytes": (c_int64, [c_int32]),
     "pkv_quantize_rows": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_float, c_void_p]),
     "pkv_cache_write": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
-                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                  c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_write_scratch_floats": (c_int64, [c_int32, c_int32]),
     "pkv_v_write": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p]),
     "pkv_cache_read": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),

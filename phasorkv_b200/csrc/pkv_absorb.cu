@@ -55,8 +55,8 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
     const int b = blockIdx.x, h0 = blockIdx.y * HG, tid = threadIdx.x;
     const int nh = min(HG, n_q - h0);
     const float* qb = q + ((size_t)b * n_q + h0) * head_dim;
-    pkv_grid_launch_dependents();
     pkv_grid_wait();
+    pkv_grid_launch_dependents();
 
     // start the global loads of the query and of this thread's factor column before the trigonometry
     constexpr int QPF = 4;                                          // (head, frequency) pairs per thread, head_dim <= 256

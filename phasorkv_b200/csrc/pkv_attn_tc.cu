@@ -28,7 +28,7 @@ constexpr int NQ = 32, DH = 128;
 constexpr int NK_STAGES = 2, NV_STAGES = 4;
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
-constexpr int P_BYTES = PKV_PAGE_TOKENS * NQ * 2;              // bf16 P of one page, all heads
+constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
 constexpr int NTHREADS = 7 * 32;
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -36,9 +36,9 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 // tensor memory columns
 constexpr int NSB = 4;                // score buffers: pages whose S = C.Q'^T may be in flight between MMA and softmax
 constexpr uint32_t TM_S = 0;          // NSB x 32 : scores (tokens x heads)
-constexpr uint32_t TM_O = 128;        // n_kv x 16 : O^T accumulators
-constexpr uint32_t TM_SFA = 256;      // NSB x 16 : cache scale factors, one set per score buffer
-constexpr uint32_t TM_SFB = 320;      // 4 x 16 : query scale factors, a 4-column group per (residual term, K step)
+constexpr uint32_t TM_O = 128;        // n_kv x 32 : O^T accumulators, 16 columns for the hi and 16 for the lo weights
+constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set per score buffer
+constexpr uint32_t TM_SFB = 448;      // 4 x 16 : query scale factors, a 4-column group per (residual term, K step)
 constexpr uint32_t TM_COLS = 512;
 
 template <int WP>
@@ -128,7 +128,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     const uint32_t tb = X->tmem_base;
     const uint32_t sbase = smem_u32(smem);
 
-    pkv_grid_wait();                               // results of the kernels before (cache write, absorb) are complete
+    // Normally everything waits here for the kernel launched before this one. With PKV_ATTN_EARLY_STREAM the
+    // caller vouches that that kernel only produces the query operand (it is pkv_absorb): the cache, the
+    // page table and the lengths are then already final, the producers start streaming pages at once and
+    // only the load of the query operand waits.
+    const bool early = (flags & PKV_ATTN_EARLY_STREAM) != 0;
+    if (!early) pkv_grid_wait();
 
     const int T = seqlens[b];
     const int npages = min((T + PKV_PAGE_TOKENS - 1) / PKV_PAGE_TOKENS, max_pages);
@@ -154,9 +159,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         // ================================================================== K producer
         if (lane == 0) {
             int issued = 0;
-            mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
-            bulk_g2s(smem + C::Q_OFF, qop + (size_t)b * qop_stride, C::QBLOB, &X->q_full);
-            for (int i = 0; i < P; ++i) {
+            bool q_sent = false;
+            for (int i = 0; i <= P; ++i) {
+                if (!q_sent && (!early || i == min(P, nks))) {       // early mode: first fill the latent stages
+                    if (early) pkv_grid_wait();
+                    mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
+                    bulk_g2s(smem + C::Q_OFF, qop + (size_t)b * qop_stride, C::QBLOB, &X->q_full);
+                    q_sent = true;
+                }
+                if (i == P) break;
                 const int s = i % nks;
                 if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) break;
                 int pidx = page_table[(size_t)b * max_pages + p_lo + i];
@@ -202,7 +213,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         // ================================================================== MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_nvfp4(128, NQ);
-            constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
+            constexpr uint32_t idesc_o = idesc_bf16(128, 32, true, false);
             bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
             if (ok) {
                 tc_fence_after_sync();
@@ -219,11 +230,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                     if (!wait_or_abort(&X->v_full[s], (j / NV_STAGES) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
                     const uint32_t va = sbase + C::V_OFF + s * V_STAGE_BYTES;
-                    const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + (g / G16) * 256;
+                    // B operand: 32 rows = the hi weights of this kv head's 16-head group, then their lo parts
+                    const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + (g / G16) * 512;
 #pragma unroll
                     for (int k = 0; k < PKV_PAGE_TOKENS / 16; ++k)
-                        mma_bf16(tb + TM_O + 16 * g, smem_desc(va + k * 2048, V_STAGE_BYTES / 2, 1024, SWZ_128B),
-                                 smem_desc(pa + k * 1024, 512, 128, SWZ_NONE), idesc_o, !(i == 0 && k == 0));
+                        mma_bf16(tb + TM_O + 32 * g, smem_desc(va + k * 2048, V_STAGE_BYTES / 2, 1024, SWZ_128B),
+                                 smem_desc(pa + k * 2048, 1024, 128, SWZ_NONE), idesc_o, !(i == 0 && k == 0));
                     tc_commit(&X->v_empty[s]);
                 }
                 tc_commit(&X->pv_done[pb]);
@@ -342,16 +354,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
                         // REP query heads of kv head g: columns (g % G16) * REP .. + REP - 1 of its 16
-                        const uint32_t a = tl + TM_O + 16 * g + (g % G16) * REP;
+                        const uint32_t a = tl + TM_O + 32 * g + (g % G16) * REP;
 #pragma unroll
-                        for (int c0 = 0; c0 < REP; c0 += 4) {
-                            uint32_t r[4];
-                            tmem_ld4(a + c0, r);
-                            tmem_ld_wait();
+                        for (int half = 0; half < 2; ++half)                     // hi columns, then lo columns
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[g * REP + c0 + c]);
-                            tmem_st4(a + c0, r);
-                        }
+                            for (int c0 = 0; c0 < REP; c0 += 4) {
+                                uint32_t r[4];
+                                tmem_ld4(a + 16 * half + c0, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[g * REP + c0 + c]);
+                                tmem_st4(a + 16 * half + c0, r);
+                            }
                     }
                     tmem_st_wait();
                     tc_fence_before_sync();
@@ -362,13 +376,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 ok = wait_all(&X->pv_done[buf], ((i >> 1) - 1) & 1, 43);      // P buffer free again
                 if (!ok) break;
             }
-            uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * 512 + (row & 7) * 2;
+            // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 16-head group
+            // [hi heads 0-7 | hi 8-15 | lo 0-7 | lo 8-15] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
+            uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * 1024 + (row & 7) * 2;
 #pragma unroll
             for (int h = 0; h < NQ; ++h) {
-                const float p = exp2f(s[h] - (m[h] > -INFINITY ? m[h] : 0.0f));       // exp2(-inf) = 0 for masked rows
+                float p = exp2f(s[h] - (m[h] > -INFINITY ? m[h] : 0.0f));             // exp2(-inf) = 0 for masked rows
+                if (with_v) {
+                    // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
+                    // that value, so numerator and denominator of softmax . V carry the same rounding
+                    const __nv_bfloat16 hi = __float2bfloat16(p);
+                    const __nv_bfloat16 lo = __float2bfloat16(p - __bfloat162float(hi));
+                    uint8_t* dst = pbuf + (h >> 4) * 512 + ((h >> 3) & 1) * 128 + (h & 7) * 16;
+                    *reinterpret_cast<__nv_bfloat16*>(dst) = hi;
+                    *reinterpret_cast<__nv_bfloat16*>(dst + 256) = lo;
+                    p = __bfloat162float(hi) + __bfloat162float(lo);
+                }
                 l[h] += p;
-                if (with_v)
-                    *reinterpret_cast<__nv_bfloat16*>(pbuf + (h >> 3) * 128 + (h & 7) * 16) = __float2bfloat16(p);
             }
             if (with_v) {
                 fence_proxy_async_smem();                   // generic-proxy writes -> visible to the tensor core
@@ -384,11 +408,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 for (int g = 0; g < NKV; ++g) {
 #pragma unroll
                     for (int c0 = 0; c0 < REP; c0 += 4) {
-                        uint32_t r[4];
-                        tmem_ld4(tl + TM_O + 16 * g + (g % G16) * REP + c0, r);
+                        uint32_t r[4], r2[4];
+                        tmem_ld4(tl + TM_O + 32 * g + (g % G16) * REP + c0, r);
+                        tmem_ld4(tl + TM_O + 32 * g + 16 + (g % G16) * REP + c0, r2);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) part[(g * REP + c0 + c) * (DH + 2) + row] = __uint_as_float(r[c]);
+                        for (int c = 0; c < 4; ++c)
+                            part[(g * REP + c0 + c) * (DH + 2) + row] = __uint_as_float(r[c]) + __uint_as_float(r2[c]);
                     }
                 }
             } else {

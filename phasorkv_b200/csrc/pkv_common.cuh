@@ -25,9 +25,11 @@ extern thread_local int g_pkv_last_cuda_error;
 
 // ------------------------------------------------------------------------------------------------
 // Programmatic dependent launch. The kernels of a decode step form a chain on one stream; each is
-// launched with the "programmatic stream serialization" attribute, tells the scheduler at its very
-// start that its successor may be brought onto the SMs, and itself waits for the complete result of
-// its predecessor (pkv_grid_wait) only after the part of its prologue that touches no global data.
+// launched with the "programmatic stream serialization" attribute, lets its successor come onto the
+// SMs early (pkv_grid_launch_dependents) and waits for the complete result of its predecessor
+// (pkv_grid_wait) before it touches global data. One kernel, pkv_absorb, triggers only AFTER its own
+// wait: the attention kernel behind it may then stream cache pages before waiting, knowing that every
+// kernel up to absorb's predecessor (the cache writers) has completed.
 // A kernel launched without the attribute sees both calls as no-ops.
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pkv_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -5,6 +5,9 @@
 #include "pkv_common.cuh"
 
 int pkv_check_cache(const pkv_cache_t* c);
+bool pkv_write_tc_usable(const pkv_layer_t* L, int32_t x_dtype, const void* x_dev);
+int pkv_write_tc_launch(const pkv_layer_t* L, const pkv_cache_t* C, const void* x_dev, const int32_t* pos, const float* ph,
+                        const int32_t* slots, int n, float* latent_out, int32_t* status, cudaStream_t st);
 
 namespace {
 
@@ -356,7 +359,7 @@ int pkv_check_layer(const pkv_layer_t* L) {
 extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                                const int32_t* positions_dev, const float* phasors_dev, const int32_t* slots_dev,
                                int32_t n_tokens, float* latent_out_dev, float* scratch_dev, const void* v_rows_dev,
-                               void* stream) {
+                               int32_t* status_dev, void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     const int W = 2 * layer->R + layer->R_s;
@@ -386,6 +389,9 @@ extern "C" int pkv_cache_write(const pkv_layer_t* layer, const pkv_cache_t* cach
         int vst = pkv_v_write(cache, v_rows_dev, slots_dev, n_tokens, stream);
         if (vst) return vst;
     }
+    if (pkv_write_tc_usable(layer, x_dtype, x_dev))
+        return pkv_write_tc_launch(layer, cache, x_dev, positions_dev, phasors_dev, slots_dev, n_tokens, latent_out_dev,
+                                   status_dev, s);
     if (pkv_padded_width(W) == 128) {
         return x_dtype == PKV_F32
                    ? launch_write<128, float>(layer, cache, x_dev, positions_dev, phasors_dev, slots_dev, n_tokens, latent_out_dev, s)

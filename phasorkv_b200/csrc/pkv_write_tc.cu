@@ -1,0 +1,243 @@
+// Fused cache write on tensor cores (prefill / chunk write of bf16 hidden states).
+//
+//   latent[t, :] = x[t, :] . Bw^T   as tcgen05.mma kind::f16 with fp32 accumulation in tensor memory.
+// x is bf16 and therefore exact; the fp32 factor matrix enters as the sum of three bf16 matrices
+// (hi + mid + lo, exact to 2^-24 relative), i.e. three passes over the same x tile that accumulate in
+// the same 128 x W accumulator. One CTA owns 128 tokens and the whole latent row of each:
+//   warp 0     producer: TMA tensor loads of the x tile [128 tokens x 64] and of the three factor
+//              tiles [W x 64] per 64-wide slice of d_model, through a ring of shared-memory stages
+//   warp 1     MMA issuer
+//   warps 2-5  epilogue, one token (TMEM lane) per thread: accumulator row -> shared memory, rotation
+//              of the pairs (k, R + k) by the token's phasors, NVFP4 quantisation with the reference's
+//              rounding, store into the token's cache page
+// Every wait is bounded; a give-up is recorded in `status` and the roles unwind.
+#include "pkv_common.cuh"
+#include "pkv_tcgen05.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace {
+
+using namespace pkv;
+
+constexpr int TM_TOK = 128;                  // tokens per CTA
+constexpr int KT = 64;                       // d_model slice per stage: 128-byte rows, 128-byte swizzle
+constexpr int X_TILE = TM_TOK * KT * 2;      // 16 KB
+constexpr int NTHREADS = 6 * 32;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+template <int WP>
+struct WCfg {
+    static constexpr int B_TILE = WP * KT * 2;                     // one bf16 term of the factor slice
+    static constexpr int STAGE = X_TILE + 3 * B_TILE;
+    static constexpr int NST = WP == 256 ? 2 : 3;
+    static constexpr int ROWS = TM_TOK * (WP + 1) * 4;              // epilogue rows, reusing the stages
+    static constexpr int BODY = NST * STAGE > ROWS ? NST * STAGE : ROWS;
+    static constexpr int SMEM = BODY + 256;
+};
+
+struct WExtra {
+    uint64_t full[3], empty[3], done;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool wwait(uint64_t* bar, uint32_t parity, WExtra* X, int32_t* status, int where) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && X->abort_flag) return false;
+    }
+    X->abort_flag = 1;
+    if (status) { atomicExch(&status[0], 1); atomicExch(&status[1], where); }
+    return false;
+}
+
+template <int WP>
+__global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
+    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap bmap, int n_tokens, int D, int W, int R,
+    const int32_t* __restrict__ positions, const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots,
+    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, float second,
+    uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, int32_t* __restrict__ status) {
+    using C = WCfg<WP>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    WExtra* X = reinterpret_cast<WExtra*>(smem + C::BODY);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tok0 = blockIdx.x * TM_TOK;
+    const int n_kt = D / KT;
+    pkv_grid_launch_dependents();
+    if (tid == 0) {
+        for (int s = 0; s < 3; ++s) { mbar_init(&X->full[s], 1); mbar_init(&X->empty[s], 1); }
+        mbar_init(&X->done, 1);
+        X->abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(&X->tmem_base, 256);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tb = X->tmem_base;
+    const uint32_t sbase = smem_u32(smem);
+    pkv_grid_wait();                               // x may be the output of the kernel before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&xmap);
+            tma_prefetch_desc(&bmap);
+            int issued = 0;
+            for (int kt = 0; kt < n_kt; ++kt) {
+                const int s = kt % C::NST;
+                if (kt >= C::NST && !wwait(&X->empty[s], ((kt / C::NST) - 1) & 1, X, status, 60)) break;
+                uint8_t* st = smem + s * C::STAGE;
+                mbar_arrive_expect_tx(&X->full[s], C::STAGE);
+                tma_load_2d(st, &xmap, kt * KT, tok0, &X->full[s]);               // rows past n_tokens arrive as zeros
+                for (int t = 0; t < 3; ++t) tma_load_2d(st + X_TILE + t * C::B_TILE, &bmap, kt * KT, t * WP, &X->full[s]);
+                issued = kt + 1;
+            }
+            if (X->abort_flag)                                                     // let copies in flight land before leaving
+                for (int kt = max(0, issued - C::NST); kt < issued; ++kt) mbar_wait(&X->full[kt % C::NST], (kt / C::NST) & 1, 1u << 16);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(TM_TOK, WP, false, false);
+            bool ok = true;
+            for (int kt = 0; kt < n_kt && ok; ++kt) {
+                const int s = kt % C::NST;
+                ok = wwait(&X->full[s], (kt / C::NST) & 1, X, status, 61);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t xa = sbase + s * C::STAGE;
+#pragma unroll
+                for (int t = 0; t < 3; ++t)
+#pragma unroll
+                    for (int k = 0; k < KT / 16; ++k)
+                        mma_bf16(tb, smem_desc(xa + k * 32, 0, 1024, SWZ_128B),
+                                 smem_desc(xa + X_TILE + t * C::B_TILE + k * 32, 0, 1024, SWZ_128B), idesc, (kt | t | k) != 0);
+                tc_commit(&X->empty[s]);
+            }
+            if (ok) tc_commit(&X->done);
+        }
+    } else {
+        // ================================================================== epilogue: one token per thread
+        const int quad = warp & 3;
+        const int rowi = quad * 32 + lane;
+        const int tok = tok0 + rowi;
+        bool ok = __all_sync(0xffffffffu, wwait(&X->done, 0, X, status, 62));
+        if (ok) {
+            tc_fence_after_sync();
+            float* row = reinterpret_cast<float*>(smem) + (size_t)rowi * (WP + 1);     // the stages are idle now
+            const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < WP; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tl + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) row[c0 + i] = __uint_as_float(r[i]);
+            }
+            if (tok < n_tokens) {
+                // rotation of (column k, column R + k) by attn_scale * e^{i * position * inv_freq[freq[k]]}
+                const double pos = phasors ? 0.0 : (double)positions[tok];
+                int f_prev = -1;
+                float pr = 1.0f, pi = 0.0f;
+                for (int k = 0; k < R; ++k) {
+                    const int f = freq[k];
+                    if (f != f_prev) {
+                        if (phasors) {
+                            const float2 p = phasors[(size_t)tok * h2 + f];
+                            pr = p.x; pi = p.y;
+                        } else {
+                            double sn, cs;
+                            sincos(pos * inv_freq[f], &sn, &cs);
+                            pr = (float)((double)attn_scale * cs); pi = (float)((double)attn_scale * sn);
+                        }
+                        f_prev = f;
+                    }
+                    const float a = row[k], b = row[R + k];
+                    row[k] = __fsub_rn(__fmul_rn(a, pr), __fmul_rn(b, pi));
+                    row[R + k] = __fadd_rn(__fmul_rn(a, pi), __fmul_rn(b, pr));
+                }
+                if (latent_out)
+                    for (int c = 0; c < W; ++c) latent_out[(size_t)tok * W + c] = row[c];
+                const int slot = latent ? slots[tok] : -1;
+                if (slot >= 0 && slot < n_pages * PKV_PAGE_TOKENS) {
+                    constexpr int RB = WP / 2, NB = WP / 16;
+                    uint8_t* page = latent + (size_t)(slot / PKV_PAGE_TOKENS) * pkv_page_bytes(W);
+                    const uint32_t pr_row = slot % PKV_PAGE_TOKENS;
+                    const int codes_bytes = pkv_codes_bytes(W);
+#pragma unroll 1
+                    for (int j = 0; j < NB; ++j) {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = row[j * 16 + i];
+                        uint8_t sb;
+                        const uint2 packed = pkv_quantize_block16(v, second, sb);
+                        *reinterpret_cast<uint2*>(page + pkv_code_offset(pr_row, j * 8, RB)) = packed;
+                        page[codes_bytes + pkv_scale_offset(pr_row, j)] = sb;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tb, 256);
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 g_encode_w = nullptr;
+
+int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    if (!g_encode_w) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        PKV_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return PKV_ERR_CUDA;
+        g_encode_w = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {KT, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_w(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { g_pkv_last_cuda_error = (int)r; return PKV_ERR_CUDA; }
+    return PKV_OK;
+}
+
+template <int WP>
+int launch_write_tc(const CUtensorMap& xmap, const CUtensorMap& bmap, const pkv_layer_t* L, const pkv_cache_t* C,
+                    const int32_t* pos, const float* ph, const int32_t* slots, int n, float* latent_out, int32_t* status,
+                    cudaStream_t st) {
+    auto kern = pkv_cache_write_tc_kernel<WP>;
+    constexpr int smem = WCfg<WP>::SMEM;
+    static bool attr_done = false;
+    if (!attr_done) {
+        PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3((n + TM_TOK - 1) / TM_TOK), dim3(NTHREADS), smem, st, xmap, bmap, n, L->d_model,
+                                    2 * L->R + L->R_s, L->R, pos, (const float2*)ph, L->head_dim / 2, slots, L->freq_dev,
+                                    L->inv_freq_dev, L->attn_scale, L->second, C ? C->latent_dev : nullptr,
+                                    C ? C->n_pages : 0, latent_out, status));
+    return PKV_OK;
+}
+
+}  // namespace
+
+// bf16 x, three-term bf16 factors present, d_model a multiple of 64: the tensor-core write can run
+bool pkv_write_tc_usable(const pkv_layer_t* L, int32_t x_dtype, const void* x_dev) {
+    return x_dtype == PKV_BF16 && L->Bw_bf16x3_dev && (L->d_model % KT) == 0 && !(((uintptr_t)x_dev) & 15u) &&
+           !(((uintptr_t)L->Bw_bf16x3_dev) & 15u);
+}
+
+int pkv_write_tc_launch(const pkv_layer_t* L, const pkv_cache_t* C, const void* x_dev, const int32_t* pos, const float* ph,
+                        const int32_t* slots, int n, float* latent_out, int32_t* status, cudaStream_t st) {
+    const int W = 2 * L->R + L->R_s, WP = pkv_padded_width(W);
+    CUtensorMap xmap, bmap;
+    int rc = encode_2d_bf16(&xmap, x_dev, (uint64_t)n, (uint64_t)L->d_model, TM_TOK);
+    if (rc) return rc;
+    rc = encode_2d_bf16(&bmap, L->Bw_bf16x3_dev, (uint64_t)3 * WP, (uint64_t)L->d_model, (uint32_t)WP);
+    if (rc) return rc;
+    return WP == 128 ? launch_write_tc<128>(xmap, bmap, L, C, pos, ph, slots, n, latent_out, status, st)
+                     : launch_write_tc<256>(xmap, bmap, L, C, pos, ph, slots, n, latent_out, status, st);
+}

@@ -181,7 +181,7 @@ class PhasorKey:
         phd = self._ph(ph)
         out = torch.empty((x.shape[0], self.cache_width), dtype=torch.float32, device=self.device)
         _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None, _lib.ptr(x), self._xdt(x), None, _lib.ptr(phd),
-                                               None, x.shape[0], _lib.ptr(out), None, None, _lib.current_stream()),
+                                               None, x.shape[0], _lib.ptr(out), None, None, None, _lib.current_stream()),
                    "pkv_cache_write")
         return out
 
@@ -255,7 +255,7 @@ class PhasorKey:
                                                _lib.ptr(x), self._xdt(x),
                                                _lib.ptr(positions), None, _lib.ptr(slots), x.shape[0],
                                                _lib.ptr(latent_out), _lib.ptr(scratch), _lib.ptr(v),
-                                               _lib.current_stream()), "pkv_cache_write")
+                                               _lib.ptr(self._dev["status"]), _lib.current_stream()), "pkv_cache_write")
 
     def workspace(self, batch: int, n_split: int) -> DecodeWorkspace:
         ws = DecodeWorkspace(batch, self.n_q, self.head_dim, self.cache_width, n_split, self.device)
@@ -283,11 +283,13 @@ class PhasorKey:
 
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
                     scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    packed_out: Optional[torch.Tensor] = None) -> None:
+                    packed_out: Optional[torch.Tensor] = None, after_absorb: bool = False) -> None:
         """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
         [B, H, d] the splits are merged as well (a merge launch enqueued right behind)."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
+        if after_absorb and not simt:                   # the launch enqueued just before was absorb_step: stream pages early
+            flags |= _lib.ATTN_EARLY_STREAM
         if packed_out is not None:                      # merged (o, m, l) triple [B, H, d+2] instead of the normalised output
             out, flags = packed_out, flags | _lib.ATTN_PACKED_OUT
         qsrc = ws.qabs if simt else ws.qop
@@ -320,7 +322,7 @@ class PhasorKey:
         if ws is None:
             ws = self.workspace(q.shape[0], self.default_splits(q.shape[0], cache.max_pages * PAGE_TOKENS, simt))
         self.absorb_step(q, positions, ws, operand=not simt)
-        self.attend_step(cache, ws, simt=simt, scores_only=scores_only, out=ws.out)
+        self.attend_step(cache, ws, simt=simt, scores_only=scores_only, out=ws.out, after_absorb=True)
         return ws.out
 
     # ------------------------------------------------------------------ plumbing
@@ -335,8 +337,16 @@ class PhasorKey:
             dev = self.device
             B = self.B.to(torch.complex64)
             rows = [B.real, B.imag] + ([self.B_s.to(torch.float32)] if self.R_s else [])
+            Bw = torch.cat(rows, dim=0).to(device=dev, dtype=torch.float32).contiguous()
+            # the factors once more as three bf16 matrices whose sum is Bw to 2^-24 (tensor-core cache write)
+            Wp = 128 if Bw.shape[0] <= 128 else 256
+            Bp = torch.zeros((Wp, Bw.shape[1]), dtype=torch.float32, device=dev)
+            Bp[:Bw.shape[0]] = Bw
+            hi = Bp.to(torch.bfloat16)
+            mid = (Bp - hi.float()).to(torch.bfloat16)
+            lo = (Bp - hi.float() - mid.float()).to(torch.bfloat16)
             t = dict(
-                Bw=torch.cat(rows, dim=0).to(device=dev, dtype=torch.float32).contiguous(),
+                Bw=Bw, Bw3=torch.stack([hi, mid, lo]).contiguous(), status=torch.zeros(4, dtype=torch.int32, device=dev),
                 A_re=self.A.real.to(device=dev, dtype=torch.float32).contiguous(),
                 A_im=self.A.imag.to(device=dev, dtype=torch.float32).contiguous(),
                 A_s=None if not self.R_s else self.A_s.to(device=dev, dtype=torch.float32).contiguous(),
@@ -348,7 +358,8 @@ class PhasorKey:
                            int(self.slow.numel()) if self.R_s else 0, self.attn_scale, self.second,
                            t["Bw"].data_ptr(), t["A_re"].data_ptr(), t["A_im"].data_ptr(),
                            0 if t["A_s"] is None else t["A_s"].data_ptr(), t["freq"].data_ptr(),
-                           0 if t["slow"] is None else t["slow"].data_ptr(), t["inv_freq"].data_ptr())
+                           0 if t["slow"] is None else t["slow"].data_ptr(), t["inv_freq"].data_ptr(),
+                           t["Bw3"].data_ptr() if Bw.shape[0] <= 256 else 0)
             t["layer"] = L
             self._dev = t
         return self._dev["layer"]

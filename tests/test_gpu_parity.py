@@ -134,7 +134,8 @@ def test_fused_write_against_oracle(config, x_dtype):
         assert rel(xhat.cpu(), ref_hat) < 5e-3
         out = torch.empty((sc.seqlens[b], sc.spec.cache_width), device="cuda")
         sc.pk.write_paged(sc.cache, sc.x[b].cuda(), sc.pos[b].to(torch.int32).cuda(), sc.slots_of(b), latent_out=out)
-        assert rel(out.cpu(), sc.rows_ref[b]) < 5e-6
+        # fp32 x: CUDA-core FMA chain; bf16 x: tensor cores, factors as three bf16 terms, fp32 accumulation in TMEM
+        assert rel(out.cpu(), sc.rows_ref[b]) < (5e-6 if x_dtype == torch.float32 else 3e-5)
 
 
 def test_absorb_batch_against_oracle():
@@ -156,7 +157,7 @@ def _check_decode(sc, n_split, simt, scores_tol=LOGIT_TOL, out_tol=OUT_TOL):
     ws = sc.pk.workspace(sc.B, n_split)
     S = torch.zeros((sc.B, sc.spec.n_q, Tmax), device="cuda")
     sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=not simt)
-    sc.pk.attend_step(sc.cache, ws, simt=simt, scores_out=S, out=ws.out)       # attention + merge through one call
+    sc.pk.attend_step(sc.cache, ws, simt=simt, scores_out=S, out=ws.out, after_absorb=True)   # attention + merge, one call
     fused = ws.out.clone()
     sc.pk.merge_step(ws)                                                       # the separate merge kernel
     torch.cuda.synchronize()
