@@ -44,7 +44,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
-    ap.add_argument("--algo", default=os.environ.get("PKV_BENCH_ALGO", "simt"), choices=["tc", "simt"])
+    ap.add_argument("--algo", default=os.environ.get("PKV_BENCH_ALGO", "tc"), choices=["tc", "simt"])
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--batch", type=int, default=0, help="override the configuration's batch (profiling)")
     ap.add_argument("--context", type=int, default=0, help="override the configuration's context (profiling)")
@@ -341,9 +341,15 @@ def run_b200(args):
         sharded = run_sharded(st, args, dist, world)
 
     pk, src = peaks()
+    # DRAM traffic per launch: an ncu capture of this kernel at B=16, T=8192 (W=256, 8 kv heads) read
+    # 287.82 MB for 131072 tokens, 1.002 x the algorithmic bytes; reads scale with the tokens streamed, the
+    # split partials written (B x n_split x 32 x 130 floats) do not.
+    traffic = None
+    if args.algo == "tc" and st.W == 256 and st.n_kv == 8:
+        traffic = int(287.82e6 * (st.B * st.T) / 131072 + st.B * st.n_split * 32 * 130 * 4)
     achieved = st.bytes_full() / (attn_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": src,
+            "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": traffic, "peak_source": src,
             "kernel": "pkv_attn_%s" % args.algo, "bytes_per_launch": st.bytes_full(),
             "us_per_launch": round(attn_ms * 1e3, 2),
             "timed_over": "%d launches of a second pass of the same %d steps with CUDA events around each attention "

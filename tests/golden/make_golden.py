@@ -177,6 +177,18 @@ def phasorkey_factorized():
         rel = ((S - S2).norm() / S2.norm()).item()
         print(tag, "ranks", ranks, "identity rel", rel)
         assert rel < 1e-12
+        # the block data PhasorKey.__init__ consumes (factorize.Block fields), for the constructor check
+        out[f"{tag}_ranks"] = np.array(ranks)
+        out[f"{tag}_nope"] = fac.nope.numpy()
+        for bi, blk in enumerate(fac.blocks):
+            out[f"{tag}_blk{bi}_U"] = blk.U.numpy()
+            out[f"{tag}_blk{bi}_s2"] = blk.s2.numpy()
+            out[f"{tag}_blk{bi}_sq"] = blk.sq.numpy()
+            out[f"{tag}_blk{bi}_Mw"] = blk.Mw.numpy()
+            out[f"{tag}_blk{bi}_cost"] = np.array(blk.cost)
+            out[f"{tag}_blk{bi}_where"] = np.array(blk.where if blk.cost == 2 else -1)
+        out[f"{tag}_nblocks"] = np.array(len(fac.blocks))
+        out[f"{tag}_energy"] = pk.energy.numpy()
         out.update({f"{tag}_A": pk.A.numpy(), f"{tag}_B": pk.B.numpy(), f"{tag}_freq": pk.freq.numpy(),
                     f"{tag}_rows": rows.numpy(), f"{tag}_qabs": qa.numpy(), f"{tag}_scores": S.numpy(),
                     f"{tag}_W_hat": W_hat.numpy(), f"{tag}_scores_hf": S2.numpy(),

@@ -74,14 +74,38 @@ class _Blk(types.SimpleNamespace):
     pass
 
 
-def test_constructor_matches_reference_attribute_arrays():
-    """PhasorKey(fac, ranks, n_q) on the block data of a reference Factorization reproduces the
-    reference's A, B, freq, A_s, B_s (stored in the golden file) up to the phase of eigenvectors,
-    which the blocks fix."""
+def _fac_from_golden(g, tag):
+    blocks = []
+    for bi in range(int(g[f"{tag}_nblocks"])):
+        t = lambda k: torch.from_numpy(g[f"{tag}_blk{bi}_{k}"])
+        blocks.append(_Blk(U=t("U"), s2=t("s2"), sq=t("sq"), Mw=t("Mw"), cost=int(g[f"{tag}_blk{bi}_cost"]),
+                           where=int(g[f"{tag}_blk{bi}_where"])))
+    D, n_q, n_kv, d = (int(v) for v in g["dims"])
+    return types.SimpleNamespace(blocks=blocks, n_kv=n_kv, d=d, absorbed=True, nope=torch.from_numpy(g[f"{tag}_nope"])), n_q
+
+
+@pytest.mark.parametrize("tag", ["freq", "band"])
+def test_constructor_matches_reference_attribute_arrays(tag):
+    """PhasorKey(fac, ranks, n_q) fed with the block data of a reference Factorization (eigenvectors,
+    energies, row weights, weighted rows; stored in the golden file) reproduces the arrays the
+    reference's own constructor built from them: A, B, freq, energy, slow, A_s, B_s."""
     g = np.load(os.path.join(GOLDEN, "phasorkey_factorized.npz"))
-    # Rebuild fake blocks from A, B: U = A*sq with sq = 1, Mw = pinv-free choice B = U^H Mw when U has
-    # orthonormal columns is not available from A, B alone; instead check the energy ordering logic
-    # on a synthetic factorization-like object.
+    fac, n_q = _fac_from_golden(g, tag)
+    pk = PhasorKey(fac, g[f"{tag}_ranks"].tolist(), n_q, inv_freq=torch.from_numpy(g["inv_freq"]), device="cpu")
+    assert torch.equal(pk.freq, torch.from_numpy(g[f"{tag}_freq"]))
+    for name in ("A", "B", "energy"):
+        ref = torch.from_numpy(g[f"{tag}_{name}"])
+        assert torch.allclose(getattr(pk, name), ref, rtol=1e-13, atol=1e-15), name
+    assert torch.equal(pk.slow, torch.from_numpy(g[f"{tag}_slow"]))
+    assert pk.cache_width == g[f"{tag}_rows"].shape[1]
+    if f"{tag}_A_s" in g:
+        assert torch.allclose(pk.A_s, torch.from_numpy(g[f"{tag}_A_s"]), rtol=1e-13, atol=1e-15)
+        assert torch.allclose(pk.B_s, torch.from_numpy(g[f"{tag}_B_s"]), rtol=1e-13, atol=1e-15)
+    else:
+        assert pk.A_s is None and pk.R_s == 0
+
+
+def test_constructor_orders_latent_dims_by_energy():
     gen = torch.Generator().manual_seed(3)
     n_kv, D, h = 2, 12, 4
     blocks, ranks = [], [2, 0, 1, 2]
@@ -94,12 +118,9 @@ def test_constructor_matches_reference_attribute_arrays():
     pk = PhasorKey(fac, ranks, 4, inv_freq=torch.ones(h, dtype=torch.float64), device="cpu")
     assert pk.R == 5 and pk.cache_width == 10 and pk.R_s == 0
     assert list(pk.energy) == sorted(pk.energy.tolist(), reverse=True)
-    # dims of frequency 3 carry energies 1.5 and 4.0; frequency 0: 3.0 and 1.0; frequency 2: 2.0
     assert pk.freq.tolist() == [3, 0, 2, 3, 0]
-    k = 0                                              # the first latent dim is component 1 of block 3
-    assert torch.allclose(pk.A[:, k], blocks[3].U[:, 1] / blocks[3].sq)
-    assert torch.allclose(pk.B[k], blocks[3].U[:, 1].conj() @ blocks[3].Mw)
-    del g
+    assert torch.allclose(pk.A[:, 0], blocks[3].U[:, 1] / blocks[3].sq)
+    assert torch.allclose(pk.B[0], blocks[3].U[:, 1].conj() @ blocks[3].Mw)
 
 
 def test_patch_protocol_install_and_undo():
