@@ -406,3 +406,25 @@ def test_exchange_gives_up_when_a_rank_never_pushes():
     assert ranks[0].status[0].item() == 3
     assert float(out.min()) == 7.0 and int(ranks[0]._epoch.sum()) == 0
     assert float((packed * 2).sum()) > 0                               # the device still answers
+
+
+def test_tc_reports_page_index_outside_the_pool():
+    """A corrupt page-table entry is reported through the status word and never dereferenced; the other
+    sequences of the batch are unaffected and the context stays usable."""
+    sc = Scenario("cfg2", seqlens=(300, 200))
+    good = sc.cache.page_table.clone()
+    ws = sc.pk.workspace(sc.B, 1)
+    sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws)
+    sc.pk.attend_step(sc.cache, ws, out=ws.out)
+    want = ws.out.clone()
+    sc.cache.page_table[0, 1] = 10 ** 6
+    ws.out.zero_()
+    sc.pk.attend_step(sc.cache, ws, out=ws.out)
+    torch.cuda.synchronize()
+    assert ws.status[0].item() == 2 and ws.status[1].item() == 1
+    assert rel(ws.out[1].cpu(), want[1].cpu()) < 1e-6
+    sc.cache.page_table.copy_(good)
+    ws.status.zero_()
+    sc.pk.attend_step(sc.cache, ws, out=ws.out)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0 and rel(ws.out.cpu(), want.cpu()) < 1e-6
