@@ -139,10 +139,9 @@ int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n
  * pkv_cache_write, phasors_dev [B, head_dim/2] complex64 (one of the two must be given).
  * qabs_out_dev: optional fp32 [B, n_q, W] in the reference layout [Re q' | Im q' | slow].
  * qop_out_dev: optional tensor-core operand, pkv_query_operand_bytes(W) per sequence: the absorbed
- * query as PKV_QUERY_TERMS NVFP4 residual terms that share one fp32 tensor scale per head: codes
- * of a 128-row tile (row = term*32 + head) swizzled like a cache page; one 512-byte scale block per
- * (term, 64-column step) whose 16-byte row `head` starts with the 4 E4M3 block scales of that step;
- * then the 32 per-head tensor scales (padded to 512 bytes). */
+ * query as PKV_QUERY_TERMS NVFP4 residual terms that share one fp32 tensor scale per head: a
+ * 128-row tile (row = term*32 + head) in exactly the layout of a cache page, then the 32 per-head
+ * tensor scales (padded to 512 bytes). */
 int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
                const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, void* stream);
 int64_t pkv_query_operand_bytes(int32_t W);

@@ -137,12 +137,11 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
     if (!qop_out) return;
     // ---- operand: row n = term * n_q + head of a 128-row tile in the cache-page layout
     const int NB = Wp / 16, RB = Wp / 2;
-    // layout: codes of the 128-row tile (row = term * 32 + head, swizzled like a cache page) | one 512-byte
-    // scale block per (term, 64-column step): row `head` of 16 bytes starts with the 4 E4M3 scales of that
-    // step, the rest is zero | 32 fp32 tensor scales, one per head
-    const int codes_bytes = pkv_codes_bytes(W), KB = Wp / 64;
+    // layout: a 128-row tile (row = term * 32 + head) exactly like a cache page (swizzled codes, then the E4M3
+    // block scales in scale-factor order) | 32 fp32 tensor scales, one per head, shared by its residual terms
+    const int codes_bytes = pkv_codes_bytes(W), page_bytes = pkv_page_bytes(W);
     uint8_t* blob = qop_out + (size_t)b * qop_bytes;
-    float* row_scale = reinterpret_cast<float*>(blob + codes_bytes + PKV_QUERY_TERMS * KB * 512);
+    float* row_scale = reinterpret_cast<float*>(blob + page_bytes);
     const bool live = tid < nh * NB;                  // <= 8 * 16 threads
     const int h = live ? tid / NB : 0, j = live ? tid % NB : 0;
     float res[16];
@@ -168,9 +167,7 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
             const uint2 packed = quantize_query_block16(res, second, inv_second, sb);
             const uint32_t n = term * n_q + h0 + h;
             *reinterpret_cast<uint2*>(blob + pkv_code_offset(n, j * 8, RB)) = packed;
-            uint8_t* sf = blob + codes_bytes + (term * KB + (j >> 2)) * 512 + (h0 + h) * 16;
-            sf[j & 3] = sb;
-            if (j & 3) *reinterpret_cast<uint32_t*>(sf + 4 * (j & 3)) = 0u;      // bytes 4..15 of the row stay zero
+            blob[codes_bytes + pkv_scale_offset(n, j)] = sb;
             if (j == 0 && term == 0) row_scale[h0 + h] = second;
         }
     }
@@ -180,7 +177,7 @@ __global__ void __launch_bounds__(NT) pkv_absorb_kernel(
 
 extern "C" int64_t pkv_query_operand_bytes(int32_t W) {
     if (W <= 0 || W > PKV_MAX_WIDTH || (W % 16)) return PKV_ERR_UNSUPPORTED;
-    return pkv_codes_bytes(W) + PKV_QUERY_TERMS * (pkv_padded_width(W) / 64) * 512 + 512;
+    return pkv_page_bytes(W) + 512;
 }
 
 extern "C" int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,

@@ -29,16 +29,17 @@ constexpr int NK_STAGES = 2, NV_STAGES = 4;
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
-constexpr int NTHREADS = 7 * 32;
+constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
+constexpr int NTHREADS_SCORES = 11 * 32;      // scores only: two softmax groups that take alternate pages
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // tensor memory columns
-constexpr int NSB = 4;                // score buffers: pages whose S = C.Q'^T may be in flight between MMA and softmax
-constexpr uint32_t TM_S = 0;          // NSB x 32 : scores (tokens x heads)
-constexpr uint32_t TM_O = 128;        // n_kv x 32 : O^T accumulators, 16 columns for the hi and 16 for the lo weights
+constexpr int NSB_V = 2, NSB_S = 3;   // score buffers (pages in flight between MMA and softmax): with V / scores only
+constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residual terms x 32 heads); 384 columns reserved
+constexpr uint32_t TM_O = 256;        // with V only (then NSB = 2): n_kv x 16 O^T accumulators, 8 hi + 8 lo weight columns
 constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set per score buffer
-constexpr uint32_t TM_SFB = 448;      // 4 x 16 : query scale factors, a 4-column group per (residual term, K step)
+constexpr uint32_t TM_SFB = 432;      // 16 : query scale factors, a 4-column group per K step
 constexpr uint32_t TM_COLS = 512;
 
 template <int WP>
@@ -47,28 +48,30 @@ struct Cfg {
     static constexpr int KB = WP / 64;                         // K = 64 MMA steps
     static constexpr int CODES = PKV_PAGE_TOKENS * RB;
     static constexpr int PAGE = CODES + KB * 512;
-    static constexpr int SFQ = PKV_QUERY_TERMS * KB * 512;     // query scale blocks, one per (term, K step)
-    static constexpr int QBLOB = CODES + SFQ + 512;
+    static constexpr int QBLOB = PAGE + 512;                   // query operand: a 128-row tile like a page + 32 head scales
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = ((QBLOB + 1023) / 1024) * 1024;
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
     static constexpr int P_OFF = V_OFF + NV_STAGES * V_STAGE_BYTES;
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
-    static constexpr int SMEM = X_OFF + 2048;
+    static constexpr int SMEM = X_OFF + 4096;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
     static constexpr uint32_t SBO = 8 * RB;
 };
 
 struct Extra {                       // lives at X_OFF
     uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_STAGES], v_empty[NV_STAGES];
-    uint64_t s_full[NSB], s_empty[NSB], p_full[2], pv_done[2];
+    uint64_t s_full[NSB_S], s_empty[NSB_S], p_full[2], pv_done[2];
     uint64_t sm_bar;                 // rendezvous of the 128 softmax threads (bounded, unlike bar.sync)
     uint32_t tmem_base;
     volatile int abort_flag;
     float wmax[2][4][NQ];
     int wflag[2][4];
-    float lsum[4][NQ];
+    float lsum[2][4][NQ];            // [softmax group][warp][head]
+    float mfin[2][4][NQ];
 };
+
+static_assert(sizeof(Extra) <= 4096, "barriers and exchange arrays must fit behind the stages");
 
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
@@ -94,16 +97,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
     return false;
 }
 
-template <int WP, int REP>
-__global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
-    const __grid_constant__ CUtensorMap vmap, const uint8_t* __restrict__ qop, long qop_stride,
-    const uint8_t* __restrict__ latent, const int32_t* __restrict__ page_table, int max_pages,
+
+template <int WP, int REP, bool WV>
+__global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_tc_kernel(
+    const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap kmap,
+    const __grid_constant__ CUtensorMap qmap, const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
     int32_t* __restrict__ status) {
     using C = Cfg<WP>;
     constexpr int NKV = NQ / REP;                 // kv heads
-    constexpr int G16 = 16 / REP;                 // kv heads per 16-head group of P rows
     extern __shared__ __align__(1024) uint8_t smem[];
     Extra* X = reinterpret_cast<Extra*>(smem + C::X_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -115,9 +118,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         mbar_init(&X->q_full, 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
         for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
-        for (int s = 0; s < NSB; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
+        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], 1); }
-        mbar_init(&X->sm_bar, 128);
+        mbar_init(&X->sm_bar, WV ? 128 : 256);
         X->abort_flag = 0;
         fence_barrier_init();
     }
@@ -140,12 +143,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     const int pps = (npages + n_split - 1) / n_split;
     const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
     const int P = p_hi - p_lo;
-    const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
+    constexpr bool with_v = WV;                      // scores-only launches are a separate instantiation
+    constexpr int SG = WV ? 1 : 2;                   // softmax groups
+    constexpr int NSB = WV ? NSB_V : NSB_S;
     const int nks = with_v ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
 
     if (P <= 0) {                                  // this split has no token: the neutral partial
-        for (int i = tid; i < NQ * (DH + 2); i += NTHREADS) {
+        for (int i = tid; i < NQ * (DH + 2); i += blockDim.x) {
             int c = i % (DH + 2);
             part[i] = c == DH ? -INFINITY : 0.0f;
         }
@@ -157,70 +162,93 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
 
     if (warp == 0) {
         // ================================================================== K producer
-        if (lane == 0) {
-            int issued = 0;
-            bool q_sent = false;
-            for (int i = 0; i <= P; ++i) {
-                if (!q_sent && (!early || i == min(P, nks))) {       // early mode: first fill the latent stages
-                    if (early) pkv_grid_wait();
-                    mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
-                    bulk_g2s(smem + C::Q_OFF, qop + (size_t)b * qop_stride, C::QBLOB, &X->q_full);
-                    q_sent = true;
+        // The page indices are fetched 32 at a time by the whole warp (one coalesced load, one round trip per
+        // 32 pages) and handed to lane 0 by shuffle: a dependent global load per page would cap the producer
+        // at one page per memory latency.
+        if (lane == 0) { tma_prefetch_desc(&kmap); tma_prefetch_desc(&qmap); }
+        int issued = 0;
+        bool q_sent = false, stop = false;
+        for (int base = 0; base <= P && !stop; base += 32) {
+            const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
+            for (int jj = 0; jj < 32 && base + jj <= P && !stop; ++jj) {
+                const int i = base + jj;
+                const int pidx = __shfl_sync(0xffffffffu, mine, jj);
+                if (lane == 0) {
+                    if (!q_sent && (!early || i == min(P, nks))) {       // early mode: first fill the latent stages
+                        if (early) pkv_grid_wait();
+                        mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
+                        tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
+                        q_sent = true;
+                    }
+                    if (i < P) {
+                        const int s = i % nks;
+                        if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) {
+                            stop = true;
+                        } else if (pidx < 0 || pidx >= n_pages_pool) {   // never dereference a bad page index
+                            X->abort_flag = 1;
+                            if (status) { atomicExch(&status[0], 2); atomicExch(&status[1], p_lo + i); }
+                            stop = true;
+                        } else {
+                            mbar_arrive_expect_tx(&X->k_full[s], C::PAGE);
+                            // one tensor tile of PAGE/128 rows x 128 bytes (plain bulk copies of this size were
+                            // measured at ~16 GB/s per SM, tiled loads are not limited that way)
+                            tma_load_2d(smem + C::K_OFF + s * C::PAGE, &kmap, 0, pidx * (C::PAGE / 128), &X->k_full[s]);
+                            issued = i + 1;
+                        }
+                    }
                 }
-                if (i == P) break;
-                const int s = i % nks;
-                if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) break;
-                int pidx = page_table[(size_t)b * max_pages + p_lo + i];
-                if (pidx < 0 || pidx >= n_pages_pool) {              // never dereference a bad page index
-                    X->abort_flag = 1;
-                    if (status) { atomicExch(&status[0], 2); atomicExch(&status[1], p_lo + i); }
-                    break;
-                }
-                mbar_arrive_expect_tx(&X->k_full[s], C::PAGE);
-                bulk_g2s(smem + C::K_OFF + s * C::PAGE, latent + (size_t)pidx * C::PAGE, C::PAGE, &X->k_full[s]);
-                issued = i + 1;
+                stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
             }
-            if (X->abort_flag) {                                     // let copies in flight land before leaving
-                mbar_wait(&X->q_full, 0, 1u << 16);
-                for (int i = max(0, issued - nks); i < issued; ++i)
-                    mbar_wait(&X->k_full[i % nks], (i / nks) & 1, 1u << 16);
-            }
+        }
+        if (lane == 0 && X->abort_flag) {                            // let copies in flight land before leaving
+            if (q_sent) mbar_wait(&X->q_full, 0, 1u << 16);
+            for (int i = max(0, issued - nks); i < issued; ++i) mbar_wait(&X->k_full[i % nks], (i / nks) & 1, 1u << 16);
         }
     } else if (warp == 1) {
         // ================================================================== V producer
-        if (lane == 0 && with_v) {
-            tma_prefetch_desc(&vmap);
+        if (with_v) {
+            if (lane == 0) tma_prefetch_desc(&vmap);
             int issued = 0;
-            bool ok = true;
-            for (int i = 0; i < P && ok; ++i) {
-                int pidx = page_table[(size_t)b * max_pages + p_lo + i];
-                if (pidx < 0 || pidx >= n_pages_pool) break;         // the K producer reports it
-                for (int g = 0; g < NKV; ++g) {
-                    const int j = i * NKV + g, s = j % NV_STAGES;
-                    if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { ok = false; break; }
-                    uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
-                    mbar_arrive_expect_tx(&X->v_full[s], V_STAGE_BYTES);
-                    tma_load_2d(dst, &vmap, g * DH, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
-                    tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, g * DH + 64, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
-                    issued = j + 1;
+            bool stop = false;
+            for (int base = 0; base < P && !stop; base += 32) {
+                const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
+                for (int jj = 0; jj < 32 && base + jj < P && !stop; ++jj) {
+                    const int i = base + jj;
+                    const int pidx = __shfl_sync(0xffffffffu, mine, jj);
+                    if (lane == 0) {
+                        if (pidx < 0 || pidx >= n_pages_pool) {
+                            stop = true;                             // the K producer reports it
+                        } else {
+                            for (int g = 0; g < NKV; ++g) {
+                                const int j = i * NKV + g, s = j % NV_STAGES;
+                                if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }
+                                uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
+                                mbar_arrive_expect_tx(&X->v_full[s], V_STAGE_BYTES);
+                                tma_load_2d(dst, &vmap, g * DH, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, g * DH + 64, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                issued = j + 1;
+                            }
+                        }
+                    }
+                    stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
                 }
             }
-            if (X->abort_flag)
+            if (lane == 0 && X->abort_flag)
                 for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
                     mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
         }
     } else if (warp == 2) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_s = idesc_nvfp4(128, NQ);
-            constexpr uint32_t idesc_o = idesc_bf16(128, 32, true, false);
+            constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
+            constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
             bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
             if (ok) {
                 tc_fence_after_sync();
-                for (int blk = 0; blk < PKV_QUERY_TERMS * C::KB; ++blk)
-                    tmem_cp_32x128b_warpx4(tb + TM_SFB + 4 * blk,
-                                           smem_desc(sbase + C::Q_OFF + C::CODES + blk * 512, 0, 128, SWZ_NONE));
+                for (int k = 0; k < C::KB; ++k)
+                    tmem_cp_32x128b_warpx4(tb + TM_SFB + 4 * k, smem_desc(sbase + C::Q_OFF + C::CODES + k * 512, 0, 128, SWZ_NONE));
             }
+            const uint64_t q_desc = smem_desc(sbase + C::Q_OFF, 0, C::SBO, C::SWZ);
             auto do_pv = [&](int i) -> bool {
                 const int pb = i & 1;
                 if (!wait_or_abort(&X->p_full[pb], (i >> 1) & 1, X, status, 31)) return false;
@@ -230,12 +258,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                     if (!wait_or_abort(&X->v_full[s], (j / NV_STAGES) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
                     const uint32_t va = sbase + C::V_OFF + s * V_STAGE_BYTES;
-                    // B operand: 32 rows = the hi weights of this kv head's 16-head group, then their lo parts
-                    const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + (g / G16) * 512;
+                    // B operand: 16 rows = the hi weights of the 8-head group holding this kv head's heads, then their lo parts
+                    const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + ((g * REP) >> 3) * 256;
+                    const uint64_t v_desc = smem_desc(va, V_STAGE_BYTES / 2, 1024, SWZ_128B);
+                    const uint64_t p_desc = smem_desc(pa, 1024, 128, SWZ_NONE);
 #pragma unroll
                     for (int k = 0; k < PKV_PAGE_TOKENS / 16; ++k)
-                        mma_bf16(tb + TM_O + 32 * g, smem_desc(va + k * 2048, V_STAGE_BYTES / 2, 1024, SWZ_128B),
-                                 smem_desc(pa + k * 2048, 1024, 128, SWZ_NONE), idesc_o, !(i == 0 && k == 0));
+                        mma_bf16(tb + TM_O + 16 * g, v_desc + (uint64_t)(k * 2048 / 16), p_desc + (uint64_t)(k * 2048 / 16), idesc_o,
+                                 !(i == 0 && k == 0));
                     tc_commit(&X->v_empty[s]);
                 }
                 tc_commit(&X->pv_done[pb]);
@@ -248,15 +278,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t ka = sbase + C::K_OFF + s * C::PAGE;
+                // descriptors differ from page to page only in the start-address field (units of 16 bytes): the
+                // constant parts are formed once, the loops below are fully unrolled
+                const uint64_t sf_desc = smem_desc(ka + C::CODES, 0, 128, SWZ_NONE);
+                const uint64_t a_desc = smem_desc(ka, 0, C::SBO, C::SWZ);
+                const uint32_t s_tm = tb + TM_S + 128 * buf, sfa_tm = tb + TM_SFA + 16 * buf;
+#pragma unroll
+                for (int k = 0; k < C::KB; ++k) tmem_cp_32x128b_warpx4(sfa_tm + 4 * k, sf_desc + (uint64_t)(k * 512 / 16));
+                // the four residual terms of the query are the four 32-row blocks of its tile: one pass with N = 128,
+                // the softmax warps add the four column blocks (an MMA costs ~75 cycles whatever its N)
+#pragma unroll
                 for (int k = 0; k < C::KB; ++k)
-                    tmem_cp_32x128b_warpx4(tb + TM_SFA + 16 * buf + 4 * k, smem_desc(ka + C::CODES + k * 512, 0, 128, SWZ_NONE));
-                // the four residual terms of the query (rows 32 t .. 32 t + 31 of its tile) all accumulate into
-                // the same 32 columns: the tensor core adds them up, the tile of cache codes is reused as is
-                for (int t = 0; t < PKV_QUERY_TERMS; ++t)
-                    for (int k = 0; k < C::KB; ++k)
-                        mma_nvfp4(tb + TM_S + 32 * buf, smem_desc(ka + k * 32, 0, C::SBO, C::SWZ),
-                                  smem_desc(sbase + C::Q_OFF + t * NQ * C::RB + k * 32, 0, C::SBO, C::SWZ), idesc_s,
-                                  tb + TM_SFA + 16 * buf + 4 * k, tb + TM_SFB + 4 * (t * C::KB + k), (t | k) != 0);
+                    mma_nvfp4(s_tm, a_desc + (uint64_t)(k * 32 / 16), q_desc + (uint64_t)(k * 32 / 16), idesc_s, sfa_tm + 4 * k,
+                              tb + TM_SFB + 4 * k, k != 0);
                 tc_commit(&X->k_empty[s]);
                 tc_commit(&X->s_full[buf]);
                 if (with_v && i >= 1) ok = do_pv(i - 1);
@@ -266,9 +300,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
     } else {
         // ================================================================== softmax (128 threads, one token row each)
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
+        const int sg = (warp - 3) >> 2;                     // softmax group: pages sg, sg + SG, ...
         const int row = quad * 32 + lane;
         const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
-        const float* rs = reinterpret_cast<const float*>(smem + C::Q_OFF + C::CODES + C::SFQ);     // [head] tensor scale of the query operand
+        const float* rs = reinterpret_cast<const float*>(smem + C::Q_OFF + C::PAGE);     // [head] tensor scale of the query operand
         // waits are made warp-uniform: the warp-collective instructions below need all 32 lanes
         auto wait_all = [&](uint64_t* bar, uint32_t parity, int where) -> bool {
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, X, status, where));
@@ -285,7 +320,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
         bool ok = wait_all(&X->q_full, 0, 40);
 #pragma unroll
         for (int h = 0; h < NQ; ++h) { cs[h] = ok ? rs[h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
-        for (int i = 0; i < P && ok; ++i) {
+        for (int i = sg; i < P && ok; i += SG) {
             const int sb = i % NSB;                         // score buffer
             const int buf = i & 1;                          // P buffer and exchange slots
             ok = wait_all(&X->s_full[sb], (i / NSB) & 1, 41);
@@ -293,13 +328,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
             tc_fence_after_sync();
             float s[NQ];
             {
-                uint32_t r[32];
-                tmem_ld32(tl + TM_S + 32 * sb, r);
-                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < PKV_QUERY_TERMS; ++t) {     // the terms share the head's tensor scale: plain sum
+                    uint32_t r[32];
+                    tmem_ld32(tl + TM_S + 128 * sb + 32 * t, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h) s[h] = t == 0 ? __uint_as_float(r[h]) : s[h] + __uint_as_float(r[h]);
+                }
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) s[h] = __uint_as_float(r[h]) * cs[h];
+                for (int h = 0; h < NQ; ++h) s[h] *= cs[h];
             }
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
             const bool valid = token < T;
@@ -353,18 +393,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 if (with_v && i > 0) {
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
-                        // REP query heads of kv head g: columns (g % G16) * REP .. + REP - 1 of its 16
-                        const uint32_t a = tl + TM_O + 32 * g + (g % G16) * REP;
+                        // REP query heads of kv head g: hi columns (g * REP) % 8 .. + REP - 1 of its 16, lo columns 8 further
+                        const uint32_t a = tl + TM_O + 16 * g + ((g * REP) & 7);
 #pragma unroll
                         for (int half = 0; half < 2; ++half)                     // hi columns, then lo columns
 #pragma unroll
                             for (int c0 = 0; c0 < REP; c0 += 4) {
                                 uint32_t r[4];
-                                tmem_ld4(a + 16 * half + c0, r);
+                                tmem_ld4(a + 8 * half + c0, r);
                                 tmem_ld_wait();
 #pragma unroll
                                 for (int c = 0; c < 4; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[g * REP + c0 + c]);
-                                tmem_st4(a + 16 * half + c0, r);
+                                tmem_st4(a + 8 * half + c0, r);
                             }
                     }
                     tmem_st_wait();
@@ -376,8 +416,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 ok = wait_all(&X->pv_done[buf], ((i >> 1) - 1) & 1, 43);      // P buffer free again
                 if (!ok) break;
             }
-            // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 16-head group
-            // [hi heads 0-7 | hi 8-15 | lo 0-7 | lo 8-15] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
+            // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 8-head group
+            // [hi | lo] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
             uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * 1024 + (row & 7) * 2;
 #pragma unroll
             for (int h = 0; h < NQ; ++h) {
@@ -387,9 +427,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                     // that value, so numerator and denominator of softmax . V carry the same rounding
                     const __nv_bfloat16 hi = __float2bfloat16(p);
                     const __nv_bfloat16 lo = __float2bfloat16(p - __bfloat162float(hi));
-                    uint8_t* dst = pbuf + (h >> 4) * 512 + ((h >> 3) & 1) * 128 + (h & 7) * 16;
+                    uint8_t* dst = pbuf + (h >> 3) * 256 + (h & 7) * 16;
                     *reinterpret_cast<__nv_bfloat16*>(dst) = hi;
-                    *reinterpret_cast<__nv_bfloat16*>(dst + 256) = lo;
+                    *reinterpret_cast<__nv_bfloat16*>(dst + 128) = lo;
                     p = __bfloat162float(hi) + __bfloat162float(lo);
                 }
                 l[h] += p;
@@ -409,8 +449,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
 #pragma unroll
                     for (int c0 = 0; c0 < REP; c0 += 4) {
                         uint32_t r[4], r2[4];
-                        tmem_ld4(tl + TM_O + 32 * g + (g % G16) * REP + c0, r);
-                        tmem_ld4(tl + TM_O + 32 * g + 16 + (g % G16) * REP + c0, r2);
+                        tmem_ld4(tl + TM_O + 16 * g + ((g * REP) & 7) + c0, r);
+                        tmem_ld4(tl + TM_O + 16 * g + 8 + ((g * REP) & 7) + c0, r2);
                         tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
@@ -418,7 +458,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                     }
                 }
             } else {
-                for (int h = 0; h < NQ; ++h) part[h * (DH + 2) + row] = 0.0f;
+                if (sg == 0)
+                    for (int h = 0; h < NQ; ++h) part[h * (DH + 2) + row] = 0.0f;
             }
             float lw = 0.0f, mw = -INFINITY;
 #pragma unroll
@@ -428,18 +469,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if (lane == h) { lw = v; mw = m[h]; }
             }
-            X->lsum[quad][lane] = lw;
-            X->wmax[0][quad][lane] = mw;                    // per warp in scores-only mode, identical otherwise
-            if (softmax_sync() && quad == 0) {
+            X->lsum[sg][quad][lane] = lw;
+            X->mfin[sg][quad][lane] = mw;                   // per warp in scores-only mode, identical otherwise
+            if (softmax_sync() && quad == 0 && sg == 0) {
                 float M = -INFINITY, lt = 0.0f;
 #pragma unroll
-                for (int w = 0; w < 4; ++w) M = fmaxf(M, X->wmax[0][w][lane]);
+                for (int w = 0; w < 4 * SG; ++w) M = fmaxf(M, X->mfin[w >> 2][w & 3][lane]);
 #pragma unroll
-                for (int w = 0; w < 4; ++w)
-                    if (X->wmax[0][w][lane] > -INFINITY) lt = fmaf(X->lsum[w][lane], exp2f(X->wmax[0][w][lane] - M), lt);
+                for (int w = 0; w < 4 * SG; ++w) {
+                    const float mw2 = X->mfin[w >> 2][w & 3][lane];
+                    if (mw2 > -INFINITY) lt = fmaf(X->lsum[w >> 2][w & 3][lane], exp2f(mw2 - M), lt);
+                }
                 part[lane * (DH + 2) + DH] = M;
                 part[lane * (DH + 2) + DH + 1] = lt;
             }
+        } else {
+            softmax_sync();                                 // keep the rendezvous count whole when a group gave up
         }
     }
     // ---- teardown: everyone meets, tensor memory goes back
@@ -451,7 +496,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_attn_tc_kernel(
 // ------------------------------------------------------------------------------------------------ host
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 
-int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
+int init_encoder() {
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -459,6 +504,10 @@ int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
         if (!fn || qres != cudaDriverEntryPointSuccess) return PKV_ERR_CUDA;
         g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
     }
+    return PKV_OK;
+}
+
+int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
     // V pool as a 2-D bf16 tensor [n_pages * 128 tokens, n_kv * head_dim]; box = 64 dims x 128 tokens, 128-byte swizzle
     cuuint64_t dims[2] = {(cuuint64_t)C->n_kv * C->head_dim, (cuuint64_t)C->n_pages * PKV_PAGE_TOKENS};
     cuuint64_t strides[1] = {(cuuint64_t)C->n_kv * C->head_dim * 2};
@@ -471,11 +520,25 @@ int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
     return PKV_OK;
 }
 
-template <int WP, int REP>
+// a buffer of `rows` 128-byte rows as a 2-D uint8 tensor; box = box_rows whole rows, no swizzle (the latent
+// pages and the query operand are stored in their shared-memory layout already)
+int encode_rows128_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+    cuuint64_t dims[2] = {128, rows};
+    cuuint64_t strides[1] = {128};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { g_pkv_last_cuda_error = (int)r; return PKV_ERR_CUDA; }
+    return PKV_OK;
+}
+
+template <int WP, int REP, bool WV>
 int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
               long scores_stride, int32_t* status, cudaStream_t st) {
-    auto kern = pkv_attn_tc_kernel<WP, REP>;
+    auto kern = pkv_attn_tc_kernel<WP, REP, WV>;
     constexpr int smem = Cfg<WP>::SMEM;
     static bool attr_done = false;                                  // once per instantiation
     if (!attr_done) {
@@ -483,8 +546,13 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
         attr_done = true;
     }
     const float logit_scale = PKV_LOG2E / sqrtf((float)L->head_dim);
-    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch), dim3(NTHREADS), smem, st, vmap, qop, (long)Cfg<WP>::QBLOB,
-                                    C->latent_dev, pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
+    CUtensorMap kmap, qmap;
+    int rc = encode_rows128_map(&kmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::PAGE / 128);
+    if (rc) return rc;
+    rc = encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
+    if (rc) return rc;
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch), dim3(WV ? NTHREADS : NTHREADS_SCORES), smem, st, vmap, kmap, qmap,
+                                    pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
                                     1.0f / logit_scale, flags, partials, scores, scores_stride, status));
     return PKV_OK;
 }
@@ -501,6 +569,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
     CUtensorMap vmap;
     memset(&vmap, 0, sizeof(vmap));
+    {
+        int st = init_encoder();
+        if (st) return st;
+    }
     if (with_v) {
         if (((uintptr_t)cache->v_dev) & 15u) return PKV_ERR_INVALID;
         int st = encode_v_map(&vmap, cache);
@@ -510,8 +582,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     const uint8_t* qop = (const uint8_t*)q_dev;
     int rc;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
-    rc = launch_tc<WP_, R_>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
-                            partials_dev, scores_out_dev, scores_stride, status_dev, stream)
+    rc = with_v ? launch_tc<WP_, R_, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
+                                           flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)       \
+                : launch_tc<WP_, R_, false>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
+                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)
     if (rep == 4) { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }
     else { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
 #undef PKV_TC_CASE

@@ -318,18 +318,17 @@ def test_query_operand_expansion():
     blob = ws.qop[:ws.qop_bytes].cpu()
     W = sc.spec.cache_width
     lv = torch.cat([po.E2M1_LEVELS, -po.E2M1_LEVELS])
-    codes_b, scales_b = blob[:128 * 128], blob[128 * 128:128 * 128 + 16 * 512]
-    head_scale = blob[128 * 128 + 16 * 512:128 * 128 + 16 * 512 + 128].view(torch.float32)      # [32]
+    codes_b, scales_b = blob[:128 * 128], blob[128 * 128:128 * 128 + 2048]
+    head_scale = blob[128 * 128 + 2048:128 * 128 + 2048 + 128].view(torch.float32)              # [32]
     n = torch.arange(128)[:, None]
     col = torch.arange(256)[None, :]
     o = n * 128 + col // 2
     o = o ^ ((o >> 3) & 0x70)
     nib = (codes_b[o] >> ((col & 1) * 4)) & 15
     j = col // 16
-    term, head = n // 32, n % 32
-    so = (term * 4 + j // 4) * 512 + head * 16 + j % 4
+    so = (j // 4) * 512 + (n % 32) * 16 + (n // 32) * 4 + j % 4
     sc_f = scales_b[so].view(torch.float8_e4m3fn).float()
-    vals = lv[nib.long()] * sc_f * head_scale[head.squeeze(1)][:, None]           # [128 = term*32 + head, 256]
+    vals = lv[nib.long()] * sc_f * head_scale[(n % 32).squeeze(1)][:, None]                   # [128 = term*32 + head, 256]
     recon = vals.reshape(4, 32, 256).sum(0)[:, :W]
     assert rel(recon, ws.qabs[0].cpu()) < 3e-4
 

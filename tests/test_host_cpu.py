@@ -40,8 +40,8 @@ def test_sizes_and_status_strings(lib):
     assert lib.pkv_latent_page_bytes(240) == lib.pkv_latent_page_bytes(256)
     assert lib.pkv_latent_page_bytes(272) == -2 and lib.pkv_latent_page_bytes(100) == -2
     assert lib.pkv_v_page_bytes(8, 128) == 128 * 8 * 128 * 2
-    assert lib.pkv_query_operand_bytes(256) == 16384 + 16 * 512 + 512
-    assert lib.pkv_query_operand_bytes(128) == 8192 + 8 * 512 + 512
+    assert lib.pkv_query_operand_bytes(256) == 18432 + 512
+    assert lib.pkv_query_operand_bytes(128) == 9216 + 512
     assert lib.pkv_status_string(0) == b"ok" and lib.pkv_status_string(-2) == b"unsupported shape"
 
 
