@@ -121,6 +121,7 @@ class Stack:
         self.T = context or c["context"]
         self.device = device
         self.simt = algo == "simt"
+        self.fused_prologue = os.environ.get("PKV_BENCH_SEPARATE_PROLOGUE", "0") != "1"
         self.layers, self.caches = [], []
         g = torch.Generator(device=device).manual_seed(seed)
         for l in range(n_layers):
@@ -185,20 +186,27 @@ class Stack:
             ws = self.ws[l & 1]
             if pre is not None:
                 pre(l)
-            if write:
-                pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
-                n += 2
-            pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
+            fused = write and not self.simt and self.fused_prologue
+            if fused:                                                 # newest token's write + absorb: one launch
+                pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l])
+                n += 1
+            else:
+                if write:
+                    pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
+                    n += 2
+                pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
+                n += 1
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=events is None and not self.simt)
+            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=events is None and not fused,
+                           after_prologue=events is None and fused)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
             pk.merge_step(ws, out=self.out[l])
-            n += 3
+            n += 2
             if post is not None:
                 post(l)
         self.launches_per_layer = n // len(self.layers)

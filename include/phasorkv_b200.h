@@ -45,6 +45,9 @@ enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
 #define PKV_ATTN_EARLY_STREAM 8u     /* the launch directly before this one on the stream is pkv_absorb (it writes
                                         neither cache nor page table nor lengths): cache pages are streamed
                                         while it still runs, only the query operand is waited for */
+#define PKV_ATTN_TAIL_WRITTEN 16u    /* with PKV_ATTN_EARLY_STREAM: the launch before is pkv_decode_prologue, which also
+                                        writes the newest token (position seqlen-1) of each sequence: the last page
+                                        of a sequence is fetched only after that launch has completed */
 #define PKV_ATTN_PACKED_OUT  4u      /* out_dev receives the merged triple [B, n_q, head_dim+2] (o, m, l), not normalised */
 
 /* One layer's factors, in the attribute convention of phasorkv.latent.PhasorKey
@@ -145,6 +148,21 @@ int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n
 int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
                const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, void* stream);
 int64_t pkv_query_operand_bytes(int32_t W);
+
+/* The two calls a decode step makes before it attends -- pkv_cache_write of the newest token of each
+ * of the `batch` sequences (x_dev [batch, d_model], write_positions_dev / slots_dev / v_rows_dev
+ * [batch]) and pkv_absorb of the step's queries (q_dev at query_positions_dev [batch]) -- as ONE
+ * launch: the reference's per-layer patch makes them back to back (PhasorKey.write, then
+ * PhasorKey.absorb: phasorkv/latent.py:57-83) and neither depends on the other. The bits written are
+ * those of the two separate calls. The single launch needs batch <= PKV_SMALL_WRITE_TOKENS, R a
+ * multiple of 16 and d_model a multiple of 32 and at most 16384; otherwise the two separate launches
+ * are made (scratch_dev, optional, is only used then). latent_out_dev, qabs_out_dev, qop_out_dev,
+ * v_rows_dev are optional as in the separate calls. */
+int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
+                        const int32_t* write_positions_dev, const int32_t* slots_dev, const void* v_rows_dev,
+                        const float* q_dev, const int32_t* query_positions_dev, int32_t batch,
+                        float* latent_out_dev, float* scratch_dev, float* qabs_out_dev, uint8_t* qop_out_dev,
+                        int32_t* status_dev, void* stream);
 
 /* Decode attention on the latent cache: scores (PhasorKey.scores, phasorkv/latent.py:85-88),
  * softmax(S * head_dim^-0.5) and P.V with kv heads shared by n_q/n_kv query heads

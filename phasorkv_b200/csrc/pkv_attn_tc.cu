@@ -135,7 +135,10 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     // caller vouches that that kernel only produces the query operand (it is pkv_absorb): the cache, the
     // page table and the lengths are then already final, the producers start streaming pages at once and
     // only the load of the query operand waits.
+    // PKV_ATTN_TAIL_WRITTEN on top: that kernel also writes rows of the LAST page of a sequence (the newest
+    // token: pkv_decode_prologue), so the last page is only fetched after the wait.
     const bool early = (flags & PKV_ATTN_EARLY_STREAM) != 0;
+    const bool tail_written = (flags & PKV_ATTN_TAIL_WRITTEN) != 0;
     if (!early) pkv_grid_wait();
 
     const int T = seqlens[b];
@@ -174,7 +177,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 const int i = base + jj;
                 const int pidx = __shfl_sync(0xffffffffu, mine, jj);
                 if (lane == 0) {
-                    if (!q_sent && (!early || i == min(P, nks))) {       // early mode: first fill the latent stages
+                    // early mode: first fill the latent stages (but never with a page that is still being written)
+                    if (!q_sent && (!early || i == min(P, nks) || (tail_written && p_lo + i == npages - 1))) {
                         if (early) pkv_grid_wait();
                         mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
                         tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         if (with_v) {
             if (lane == 0) tma_prefetch_desc(&vmap);
             int issued = 0;
-            bool stop = false;
+            bool stop = false, waited = !(early && tail_written);
             for (int base = 0; base < P && !stop; base += 32) {
                 const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
                 for (int jj = 0; jj < 32 && base + jj < P && !stop; ++jj) {
@@ -219,6 +223,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                         if (pidx < 0 || pidx >= n_pages_pool) {
                             stop = true;                             // the K producer reports it
                         } else {
+                            if (!waited && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                             for (int g = 0; g < NKV; ++g) {
                                 const int j = i * NKV + g, s = j % NV_STAGES;
                                 if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }

@@ -281,15 +281,35 @@ class PhasorKey:
                                           _lib.ptr(ws.qabs), _lib.ptr(ws.qop) if operand else None,
                                           _lib.current_stream()), "pkv_absorb")
 
+    def prologue_step(self, cache: PagedLatentCache, x: torch.Tensor, write_positions: torch.Tensor, slots: torch.Tensor,
+                      q: torch.Tensor, query_positions: torch.Tensor, ws: DecodeWorkspace,
+                      v: Optional[torch.Tensor] = None, latent_out: Optional[torch.Tensor] = None,
+                      operand: bool = True) -> None:
+        """`write_paged` of the newest token of every sequence and `absorb_step` of the step's queries
+        as one launch (same bits as the two calls)."""
+        L = self._layer()
+        x = self._x(x)
+        if v is not None:
+            v = v.to(torch.bfloat16).contiguous()
+        _lib.check(_lib.load().pkv_decode_prologue(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(x), self._xdt(x),
+                                                   _lib.ptr(write_positions), _lib.ptr(slots), _lib.ptr(v), _lib.ptr(q),
+                                                   _lib.ptr(query_positions), x.shape[0], _lib.ptr(latent_out),
+                                                   _lib.ptr(getattr(ws, "wscratch", None)), _lib.ptr(ws.qabs),
+                                                   _lib.ptr(ws.qop) if operand else None, _lib.ptr(self._dev["status"]),
+                                                   _lib.current_stream()), "pkv_decode_prologue")
+
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
                     scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    packed_out: Optional[torch.Tensor] = None, after_absorb: bool = False) -> None:
+                    packed_out: Optional[torch.Tensor] = None, after_absorb: bool = False,
+                    after_prologue: bool = False) -> None:
         """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
         [B, H, d] the splits are merged as well (a merge launch enqueued right behind)."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
         if after_absorb and not simt:                   # the launch enqueued just before was absorb_step: stream pages early
             flags |= _lib.ATTN_EARLY_STREAM
+        if after_prologue and not simt:                 # ... was prologue_step: it also writes the newest token's rows
+            flags |= _lib.ATTN_EARLY_STREAM | _lib.ATTN_TAIL_WRITTEN
         if packed_out is not None:                      # merged (o, m, l) triple [B, H, d+2] instead of the normalised output
             out, flags = packed_out, flags | _lib.ATTN_PACKED_OUT
         qsrc = ws.qabs if simt else ws.qop

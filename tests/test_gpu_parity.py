@@ -260,6 +260,75 @@ def test_decode_time_write_path(config, n):
     assert rel(b.cpu(), a.cpu()) < 5e-3
 
 
+@pytest.mark.parametrize("config,n", [("cfg2", 16), ("cfg2", 1), ("cfg2", 37), ("cfg5", 64), ("cfg3", 5)])
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
+    """The one-launch step prologue (write of the newest tokens + absorb) leaves the bits of the two
+    separate calls: cache codes and scales, V rows, unquantised rows, absorbed queries, operand.
+    cfg3 (R = 120, not a multiple of 16) takes the entry point's two-launch route."""
+    sc = Scenario(config, seqlens=(n,), pos0=32767)
+    pk, W = sc.pk, sc.spec.cache_width
+    x = sc.x[0].cuda().to(x_dtype)
+    wpos = sc.pos[0].to(torch.int32).cuda()
+    slots = sc.slots_of(0)
+    v = sc.v[0].cuda()
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn((n, sc.spec.n_q, sc.spec.head_dim), generator=g).cuda()
+    qpos = (wpos + 1).contiguous()
+    caches, outs, wss = [], [], []
+    for fused in (False, True):
+        cache = pk.new_cache(1, n)
+        ws = pk.workspace(n, 1)
+        ws.qabs.zero_()
+        ws.qop.zero_()
+        out = torch.zeros((n, W), device="cuda")
+        if fused:
+            pk.prologue_step(cache, x, wpos, slots, q, qpos, ws, v=v, latent_out=out)
+        else:
+            pk.write_paged(cache, x, wpos, slots, v=v, latent_out=out, scratch=ws.wscratch)
+            pk.absorb_step(q, qpos, ws)
+        torch.cuda.synchronize()
+        caches.append(cache), outs.append(out), wss.append(ws)
+    assert torch.equal(outs[0], outs[1])
+    assert float(outs[1].abs().max()) > 0
+    assert torch.equal(caches[0].latent, caches[1].latent)
+    assert torch.equal(caches[0].v, caches[1].v)
+    assert torch.equal(caches[1].v[slots.long()].cpu(), sc.v[0])
+    assert torch.equal(wss[0].qabs, wss[1].qabs) and float(wss[1].qabs.abs().max()) > 0
+    assert torch.equal(wss[0].qop, wss[1].qop) and int(wss[1].qop.max()) > 0
+
+
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_attention_behind_prologue_sees_the_newest_token(n_split):
+    """Attention launched right behind the prologue streams pages early, except the page the prologue
+    is writing: replacing the newest token of every sequence (latent row and V row) and attending at
+    once gives what a fully ordered launch gives afterwards, and the oracle's result for the new rows."""
+    sc = Scenario("cfg2", seqlens=(300, 129, 128, 1), pos0=5000)
+    pk, B = sc.pk, sc.B
+    g = torch.Generator().manual_seed(77)
+    x_new = (synth.make_hidden(g, B, 4096) * 3.0).cuda()
+    v_new = (synth.make_values(g, B, sc.spec.n_kv, sc.spec.head_dim) * 4.0)
+    lens = torch.tensor(sc.seqlens, dtype=torch.int32, device="cuda")
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    slots = sc.cache.slots(seq, lens - 1)
+    wpos = (lens - 1 + 5000).contiguous()
+    ws = pk.workspace(B, n_split)
+    out_early = torch.zeros((B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
+    for _ in range(3):                                      # repeated: the launch pair must be ordered every time
+        pk.prologue_step(sc.cache, x_new, wpos, slots, sc.q.cuda(), sc.qpos.cuda(), ws, v=v_new.cuda())
+        pk.attend_step(sc.cache, ws, out=out_early, after_prologue=True)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    out_late = torch.zeros_like(out_early)
+    pk.attend_step(sc.cache, ws, out=out_late)
+    torch.cuda.synchronize()
+    assert torch.equal(out_early, out_late)
+    for b, T in enumerate(sc.seqlens):
+        sc.v[b][T - 1] = v_new[b]
+        _, _, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b))
+        assert rel(out_early[b].cpu(), O_ref) < OUT_TOL
+
+
 # ------------------------------------------------------------------------------------------------
 # tensor-core kernel (tcgen05 block-scaled NVFP4 scores, bf16 P.V): same checks, same tolerances
 # ------------------------------------------------------------------------------------------------
