@@ -413,20 +413,29 @@ def run_sharded(st, args, dist, world):
     ex = None
     if world > 1 and args.collective == "p2p":
         from phasorkv_b200.sharded import ShardExchange
-        ex = ShardExchange.from_process_group(dist.group.WORLD, B4, st.n_q, st.d, dev)
+        ex = ShardExchange.from_process_group(dist.group.WORLD, B4, st.n_q, st.d, dev, n_cta=B4 * st.n_q)
+    # the newest token (global position T-1) belongs to the last rank: only that rank writes it
+    owner = int(os.environ.get("RANK", 0)) == world - 1 and not st.simt
+    wpos = torch.full((B4,), T4 - 1, dtype=torch.int32, device=dev)
+    wslots = (pt[:, (Tl - 1) // 128] * 128 + (Tl - 1) % 128).to(torch.int32).contiguous()
 
     def step():
         for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
-            pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
+            if owner:
+                pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4])
+            else:
+                pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
+            early = dict(after_prologue=True) if owner else dict(after_absorb=True)
             if world > 1:
-                pk.attend_step(cache, ws, simt=st.simt, packed_out=ws.packed, after_absorb=True)     # local splits merged in the same launch
                 if ex is not None:
-                    ex.run(ws.packed, out)                  # peer stores + flags + merge, one kernel
+                    pk.attend_step(cache, ws, simt=st.simt, **early)
+                    ex.run_parts(ws.partials, ws.n_split, out)      # local merge + peer stores + merge, one kernel
                 else:
+                    pk.attend_step(cache, ws, simt=st.simt, packed_out=ws.packed, **early)   # local splits merged by a launch behind
                     dist.all_gather_into_tensor(gathered, ws.packed)
                     pk.merge_gathered(gathered, out)
             else:
-                pk.attend_step(cache, ws, simt=st.simt, out=out, after_absorb=True)
+                pk.attend_step(cache, ws, simt=st.simt, out=out, **early)
     for c in st.caches:
         c.page_table, c.seqlens, c.max_pages = pt, seqlens, pages
     graphed = False
@@ -458,8 +467,8 @@ def run_sharded(st, args, dist, world):
     per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
     return {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, args.layers),
             "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
-            "scaling": "strong", "cuda_graph": graphed,
-            "collective": "none" if world == 1 else ("fused exchange+merge kernel over NVLink peer memory, [B,H,d+2] fp32 per layer"
+            "scaling": "strong", "cuda_graph": graphed, "newest_token_written_by": "rank %d (fused prologue)" % (world - 1),
+            "collective": "none" if world == 1 else ("local merge + exchange + merge in one kernel over NVLink peer memory, [B,H,d+2] fp32 per layer"
                                                      if ex is not None else "NCCL all_gather of [B,H,d+2] fp32 per layer + merge"),
             "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
             "hbm_gbs_per_gpu": round(per_gpu_bytes * args.layers / (ms * 1e-3) / 1e9, 1)}

@@ -217,6 +217,13 @@ typedef struct pkv_exchange {
 } pkv_exchange_t;
 int pkv_exchange_merge(const pkv_exchange_t* x, const float* packed_dev, float* out_dev, uint32_t phases,
                        int32_t* status_dev, void* stream);
+/* pkv_merge of the local split-T partials (same parts_dev / strides / n_parts as pkv_merge, batch, n_q and
+ * head_dim <= 128 taken from x) and pkv_exchange_merge in ONE launch: the merged local triple of a row
+ * goes from registers straight to the peers. One CTA per row: x->n_cta must equal batch * n_q (and
+ * epoch_dev hold that many counters). A handle is used with either this entry point or
+ * pkv_exchange_merge, not both in turn. */
+int pkv_merge_exchange(const pkv_exchange_t* x, const float* parts_dev, int64_t stride_b, int64_t stride_p,
+                       int32_t n_parts, float* out_dev, int32_t* status_dev, void* stream);
 
 /* Decode attention and merge for callers that cannot allocate device memory (no counterpart in the
  * reference, whose callers always allocate their own scratch with torch).  It is meant for hosts that

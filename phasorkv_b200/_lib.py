@@ -66,6 +66,7 @@ SIGNATURES = {
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                           c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_exchange_merge": (c_int32, [POINTER(Exchange), c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),
+    "pkv_merge_exchange": (c_int32, [POINTER(Exchange), c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }

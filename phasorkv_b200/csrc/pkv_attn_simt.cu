@@ -3,6 +3,7 @@
 // 32-token tiles of the latent, scores all query heads against them, keeps a running base-2
 // softmax and accumulates P.V from the bf16 V pages. Also the log-sum-exp merge kernel.
 #include "pkv_common.cuh"
+#include "pkv_merge.cuh"
 
 int pkv_check_layer(const pkv_layer_t* L);
 int pkv_check_cache(const pkv_cache_t* c);
@@ -12,6 +13,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                        int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream);
 
 namespace {
+
+using pkv_merge_impl::MG;
+using pkv_merge_impl::MergeSmem;
+using pkv_merge_impl::merge_row;
 
 constexpr int NT = 256;
 constexpr int TT = 32;          // tokens per tile
@@ -174,91 +179,31 @@ __global__ void __launch_bounds__(NT) pkv_attn_simt_kernel(
     }
 }
 
-// One CTA per (sequence, head). The kernel is pure latency (a few hundred KB at most), so every load is
-// issued before anything is consumed: thread p fetches the (m, l) pair of partial p, thread (g, d)
-// fetches output dim d of the partials g, g + MG, ... into registers; only then are the maxima reduced,
-// the weights formed and the register values scaled and added (across the MG groups through smem).
-constexpr int MG = 4;                       // partial groups per CTA
-constexpr int MERGE_REG_PARTS = 16;         // partials per thread held in registers in one pass
-constexpr int MERGE_MAX_PARTS = MG * 128;   // one (m, l) pair per thread
-
+// One CTA per (sequence, head): the merge of pkv_merge.cuh, then the normalised and / or packed store.
 __global__ void __launch_bounds__(MG * 128) pkv_merge_kernel(const float* __restrict__ parts, long stride_b, long stride_p,
                                                              int n_parts, int n_q, int head_dim, int batch,
                                                              float* __restrict__ out, float* __restrict__ packed_out) {
-    __shared__ float w_s[MERGE_MAX_PARTS];
-    __shared__ float red_s[MG][256];
-    __shared__ float wred_s[MG * 4];
-    __shared__ float M_s, den_s;
+    __shared__ MergeSmem S;
     const int tid = threadIdx.x, d = tid & 127, g = tid >> 7;
     const int b = blockIdx.x / n_q, h = blockIdx.x % n_q;
     const int PW = head_dim + 2;
-    const float* base = parts + (size_t)b * stride_b + (size_t)h * PW;
     pkv_grid_launch_dependents();
     pkv_grid_wait();
-    // ---- all loads first
-    float2 ml = make_float2(-INFINITY, 0.0f);
-    if (tid < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)tid * stride_p + head_dim));
-    float o0[MERGE_REG_PARTS], o1[MERGE_REG_PARTS];
-#pragma unroll
-    for (int k = 0; k < MERGE_REG_PARTS; ++k) {
-        const int p = g + k * MG;
-        o0[k] = (p < n_parts && d < head_dim) ? __ldcg(base + (size_t)p * stride_p + d) : 0.0f;
-        o1[k] = (p < n_parts && d + 128 < head_dim) ? __ldcg(base + (size_t)p * stride_p + d + 128) : 0.0f;
-    }
-    // ---- maximum over the partials, weights, denominator
-    float M = ml.x;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if ((tid & 31) == 0) wred_s[tid >> 5] = M;
-    __syncthreads();
-    if (tid == 0) {
-        float mm = -INFINITY;
-        for (int i = 0; i < MG * 4; ++i) mm = fmaxf(mm, wred_s[i]);
-        M_s = mm;
-    }
-    __syncthreads();
-    M = M_s;
-    const float w = (tid < n_parts && M > -INFINITY) ? exp2f(ml.x - M) : 0.0f;     // a split that saw no token: m = -inf, w = 0
-    if (tid < n_parts) w_s[tid] = w;
-    float lw = w * ml.y;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, o);
-    __syncthreads();                         // everyone has read wred_s / M_s
-    if ((tid & 31) == 0) wred_s[tid >> 5] = lw;
-    __syncthreads();
-    if (tid == 0) {
-        float dd = 0.0f;
-        for (int i = 0; i < MG * 4; ++i) dd += wred_s[i];
-        den_s = dd;
-    }
-    // ---- weighted sums: registers first, further partials (more than MG * 16) straight from memory
-    float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll
-    for (int k = 0; k < MERGE_REG_PARTS; ++k) {
-        const int p = g + k * MG;
-        if (p < n_parts) { acc0 = fmaf(w_s[p], o0[k], acc0); acc1 = fmaf(w_s[p], o1[k], acc1); }
-    }
-#pragma unroll 4
-    for (int p = g + MERGE_REG_PARTS * MG; p < n_parts; p += MG) {
-        const float* pp = base + (size_t)p * stride_p;
-        if (d < head_dim) acc0 = fmaf(w_s[p], __ldcg(pp + d), acc0);
-        if (d + 128 < head_dim) acc1 = fmaf(w_s[p], __ldcg(pp + d + 128), acc1);
-    }
-    red_s[g][d] = acc0;
-    red_s[g][d + 128] = acc1;
-    __syncthreads();
+    float a0, a1, M, den;
+    merge_row(parts + (size_t)b * stride_b + (size_t)h * PW, stride_p, n_parts, head_dim, S, a0, a1, M, den);
     if (g == 0) {
-        const float den = den_s;
-        for (int dd = d; dd < head_dim; dd += 128) {
-            float a = 0.0f;
-#pragma unroll
-            for (int k = 0; k < MG; ++k) a += red_s[k][dd];
-            if (out) out[((size_t)b * n_q + h) * head_dim + dd] = den > 0.0f ? a / den : 0.0f;
-            if (packed_out) packed_out[((size_t)b * n_q + h) * PW + dd] = a;
+        const size_t row = (size_t)b * n_q + h;
+        if (d < head_dim) {
+            if (out) out[row * head_dim + d] = den > 0.0f ? a0 / den : 0.0f;
+            if (packed_out) packed_out[row * PW + d] = a0;
+        }
+        if (d + 128 < head_dim) {
+            if (out) out[row * head_dim + d + 128] = den > 0.0f ? a1 / den : 0.0f;
+            if (packed_out) packed_out[row * PW + d + 128] = a1;
         }
         if (packed_out && d == 0) {
-            packed_out[((size_t)b * n_q + h) * PW + head_dim] = M;
-            packed_out[((size_t)b * n_q + h) * PW + head_dim + 1] = den;
+            packed_out[row * PW + head_dim] = M;
+            packed_out[row * PW + head_dim + 1] = den;
         }
     }
 }
@@ -333,7 +278,7 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
 extern "C" int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
                          int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream) {
     if (!parts_dev || n_parts <= 0 || batch < 0 || n_q <= 0 || head_dim <= 0 || head_dim > 256) return PKV_ERR_INVALID;
-    if (n_parts > MERGE_MAX_PARTS) return PKV_ERR_UNSUPPORTED;
+    if (n_parts > pkv_merge_impl::MAX_PARTS) return PKV_ERR_UNSUPPORTED;
     if ((head_dim & 1) || (stride_b & 1) || (stride_p & 1) || (((uintptr_t)parts_dev) & 7u)) return PKV_ERR_INVALID;   // (m, l) is read as one 8-byte pair
     if (!out_dev && !packed_out_dev) return PKV_ERR_INVALID;
     if (batch == 0) return PKV_OK;

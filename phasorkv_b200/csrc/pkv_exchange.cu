@@ -14,6 +14,7 @@
 // CTA keeps in device memory, so the kernel can be replayed from a CUDA graph; a rank can be at most
 // one exchange ahead of any peer (it needs that peer's words to finish), which two slots cover.
 #include "pkv_common.cuh"
+#include "pkv_merge.cuh"
 
 namespace {
 
@@ -29,40 +30,17 @@ __device__ __forceinline__ uint2 ld_word(const uint2* p) {
     asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
-__global__ void __launch_bounds__(NT) pkv_exchange_merge_kernel(pkv_exchange_t X, const float* __restrict__ packed,
-                                                                float* __restrict__ out, uint32_t phases,
-                                                                int32_t* __restrict__ status) {
-    __shared__ uint32_t epoch_s;
-    __shared__ int fail_s;
-    const int tid = threadIdx.x, c = blockIdx.x;
-    const int rows = X.batch * X.n_q, PW = X.head_dim + 2;
-    const int rows_per = (rows + X.n_cta - 1) / X.n_cta;
-    const int r0 = c * rows_per, r1 = min(rows, r0 + rows_per);
-    const int nrow = max(0, r1 - r0);
-    pkv_grid_launch_dependents();
-    pkv_grid_wait();                               // the attention launch before this one has written `packed`
-    if (tid == 0) { epoch_s = X.epoch_dev[c] + 1u; fail_s = 0; }
-    __syncthreads();
-    const uint32_t epoch = epoch_s;
-    const size_t rank_words = (size_t)rows * PW;                        // one rank's triple
-    const size_t slot_off = (size_t)(epoch & 1u) * X.world * rank_words;
-
-    if (phases & PKV_EXCHANGE_PUSH) {
-        const float* src = packed + (size_t)r0 * PW;
-        const int n = nrow * PW;
-        for (int i = tid; i < n; i += NT) {
-            const float v = src[i];
-            for (int dst = 0; dst < X.world; ++dst)
-                st_word(reinterpret_cast<uint2*>(X.peer_data_dev[dst]) + slot_off + X.rank * rank_words + (size_t)r0 * PW + i, v, epoch);
-        }
-    }
-    if (!(phases & PKV_EXCHANGE_MERGE)) return;
-
-    // ---- gather: all words this CTA needs, [source][row][d+2], into shared memory. Every thread keeps a
-    // batch of independent loads in flight and re-reads only the words whose epoch is not there yet.
-    extern __shared__ float got[];                  // [world][nrow][PW]
+// Gather and merge of rows r0 .. r0 + nrow - 1: all words this CTA needs, [source][row][d+2], are polled into
+// shared memory `got`. Every thread keeps a batch of independent loads in flight and re-reads only the
+// words whose epoch is not there yet. Called by all NTH threads of the CTA.
+template <int NTH>
+__device__ __forceinline__ void gather_merge(const pkv_exchange_t& X, int c, int r0, int nrow, uint32_t epoch, size_t slot_off,
+                                             size_t rank_words, float* got, int* fail_s, float* __restrict__ out,
+                                             int32_t* __restrict__ status) {
+    const int tid = threadIdx.x, PW = X.head_dim + 2;
+    constexpr int NT = NTH;
     const uint2* mine = reinterpret_cast<const uint2*>(X.peer_data_dev[X.rank]) + slot_off;
-    volatile int* fail = &fail_s;
+    volatile int* fail = fail_s;
     const int row_words = nrow * PW, total = X.world * row_words;
     constexpr int BATCH = 8;
     for (int base = 0; base < total; base += NT * BATCH) {
@@ -98,7 +76,7 @@ __global__ void __launch_bounds__(NT) pkv_exchange_merge_kernel(pkv_exchange_t X
         if (pending) *fail = 1;
     }
     __syncthreads();
-    if (!fail_s) {
+    if (!*fail) {
         for (int e = tid; e < nrow * X.head_dim; e += NT) {
             const int rr = e / X.head_dim, d = e % X.head_dim;
             float M = -INFINITY;
@@ -114,11 +92,75 @@ __global__ void __launch_bounds__(NT) pkv_exchange_merge_kernel(pkv_exchange_t X
         }
     }
     __syncthreads();
-    if (fail_s) {                                   // epoch not advanced: the exchange did not happen
+    if (*fail) {                                   // epoch not advanced: the exchange did not happen
         if (tid == 0 && status) { atomicExch(&status[0], 3); atomicExch(&status[1], c); }
         return;
     }
     if (tid == 0) X.epoch_dev[c] = epoch;
+}
+
+__global__ void __launch_bounds__(NT) pkv_exchange_merge_kernel(pkv_exchange_t X, const float* __restrict__ packed,
+                                                                float* __restrict__ out, uint32_t phases,
+                                                                int32_t* __restrict__ status) {
+    __shared__ uint32_t epoch_s;
+    __shared__ int fail_s;
+    const int tid = threadIdx.x, c = blockIdx.x;
+    const int rows = X.batch * X.n_q, PW = X.head_dim + 2;
+    const int rows_per = (rows + X.n_cta - 1) / X.n_cta;
+    const int r0 = c * rows_per, r1 = min(rows, r0 + rows_per);
+    const int nrow = max(0, r1 - r0);
+    pkv_grid_launch_dependents();
+    pkv_grid_wait();                               // the attention launch before this one has written `packed`
+    if (tid == 0) { epoch_s = X.epoch_dev[c] + 1u; fail_s = 0; }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    const size_t rank_words = (size_t)rows * PW;                        // one rank's triple
+    const size_t slot_off = (size_t)(epoch & 1u) * X.world * rank_words;
+
+    if (phases & PKV_EXCHANGE_PUSH) {
+        const float* src = packed + (size_t)r0 * PW;
+        const int n = nrow * PW;
+        for (int i = tid; i < n; i += NT) {
+            const float v = src[i];
+            for (int dst = 0; dst < X.world; ++dst)
+                st_word(reinterpret_cast<uint2*>(X.peer_data_dev[dst]) + slot_off + X.rank * rank_words + (size_t)r0 * PW + i, v, epoch);
+        }
+    }
+    if (!(phases & PKV_EXCHANGE_MERGE)) return;
+
+    extern __shared__ float got[];                  // [world][nrow][PW]
+    gather_merge<NT>(X, c, r0, nrow, epoch, slot_off, rank_words, got, &fail_s, out, status);
+}
+
+// The merge of a row's split-T partials (pkv_merge.cuh) and its exchange in one launch: CTA = one
+// (sequence, head) row, MG * 128 threads. The row's local triple never goes through global memory: it is
+// pushed to the peers straight from the registers that hold it.
+constexpr int NTM = pkv_merge_impl::MG * 128;
+
+__global__ void __launch_bounds__(NTM) pkv_merge_exchange_kernel(pkv_exchange_t X, const float* __restrict__ parts, long stride_b,
+                                                                 long stride_p, int n_parts, float* __restrict__ out,
+                                                                 int32_t* __restrict__ status) {
+    __shared__ pkv_merge_impl::MergeSmem S;
+    __shared__ float got[MAX_WORLD * (128 + 2)];
+    __shared__ uint32_t epoch_s;
+    __shared__ int fail_s;
+    const int tid = threadIdx.x, c = blockIdx.x;     // c = row = b * n_q + h
+    const int PW = X.head_dim + 2;
+    pkv_grid_launch_dependents();
+    pkv_grid_wait();                               // the attention launch before this one has written the partials
+    if (tid == 0) { epoch_s = X.epoch_dev[c] + 1u; fail_s = 0; }
+    float a0, a1, M, den;
+    pkv_merge_impl::merge_row(parts + (size_t)(c / X.n_q) * stride_b + (size_t)(c % X.n_q) * PW, stride_p, n_parts, X.head_dim,
+                              S, a0, a1, M, den);    // has block-wide barriers: epoch_s is visible afterwards
+    const uint32_t epoch = epoch_s;
+    const size_t rank_words = (size_t)X.batch * X.n_q * PW;
+    const size_t slot_off = (size_t)(epoch & 1u) * X.world * rank_words;
+    if (tid < PW) {                                // head_dim <= 128: thread d holds dim d, threads d, d+1 beyond push m and l
+        const float v = tid < X.head_dim ? a0 : (tid == X.head_dim ? M : den);
+        for (int dst = 0; dst < X.world; ++dst)
+            st_word(reinterpret_cast<uint2*>(X.peer_data_dev[dst]) + slot_off + X.rank * rank_words + (size_t)c * PW + tid, v, epoch);
+    }
+    gather_merge<NTM>(X, c, c, 1, epoch, slot_off, rank_words, got, &fail_s, out, status);
 }
 
 }  // namespace
@@ -136,5 +178,19 @@ extern "C" int pkv_exchange_merge(const pkv_exchange_t* x, const float* packed_d
     if ((phases & PKV_EXCHANGE_MERGE) && !out_dev) return PKV_ERR_INVALID;
     PKV_CUDA_TRY(pkv_launch_chained(pkv_exchange_merge_kernel, dim3(x->n_cta), dim3(NT), smem, (cudaStream_t)stream, *x,
                                     packed_dev, out_dev, phases, status_dev));
+    return PKV_OK;
+}
+
+extern "C" int pkv_merge_exchange(const pkv_exchange_t* x, const float* parts_dev, int64_t stride_b, int64_t stride_p,
+                                  int32_t n_parts, float* out_dev, int32_t* status_dev, void* stream) {
+    if (!x || !x->peer_data_dev || !x->epoch_dev || !parts_dev || !out_dev) return PKV_ERR_INVALID;
+    if (x->world <= 0 || x->world > MAX_WORLD || x->rank < 0 || x->rank >= x->world) return PKV_ERR_INVALID;
+    if (x->batch <= 0 || x->n_q <= 0 || x->head_dim <= 0 || (x->head_dim & 1)) return PKV_ERR_INVALID;
+    if (x->head_dim > 128) return PKV_ERR_UNSUPPORTED;
+    if (x->n_cta != x->batch * x->n_q) return PKV_ERR_INVALID;             // one CTA (and one epoch counter) per row
+    if (n_parts <= 0 || (stride_b & 1) || (stride_p & 1) || (((uintptr_t)parts_dev) & 7u)) return PKV_ERR_INVALID;
+    if (n_parts > pkv_merge_impl::MAX_PARTS) return PKV_ERR_UNSUPPORTED;
+    PKV_CUDA_TRY(pkv_launch_chained(pkv_merge_exchange_kernel, dim3(x->n_cta), dim3(NTM), 0, (cudaStream_t)stream, *x, parts_dev,
+                                    (long)stride_b, (long)stride_p, n_parts, out_dev, status_dev));
     return PKV_OK;
 }

@@ -41,6 +41,14 @@ class ShardExchange:
         _lib.check(_lib.load().pkv_exchange_merge(ctypes.byref(self.x), _lib.ptr(packed), _lib.ptr(out), phases,
                                                   _lib.ptr(self.status), _lib.current_stream()), "pkv_exchange_merge")
 
+    def run_parts(self, partials: torch.Tensor, n_split: int, out: torch.Tensor) -> None:
+        """Merge of the local split-T partials [B, n_split, H, d+2] and the exchange in ONE launch
+        (`pkv_merge_exchange`); needs a handle made with ``n_cta = batch * n_q``."""
+        pw = self.x.head_dim + 2
+        _lib.check(_lib.load().pkv_merge_exchange(ctypes.byref(self.x), _lib.ptr(partials), n_split * self.x.n_q * pw,
+                                                  self.x.n_q * pw, n_split, _lib.ptr(out), _lib.ptr(self.status),
+                                                  _lib.current_stream()), "pkv_merge_exchange")
+
     # ------------------------------------------------------------------ construction
     @classmethod
     def local_group(cls, world: int, batch: int, n_q: int, head_dim: int, device="cuda", n_cta: int = 64):

@@ -51,8 +51,19 @@ def main():
     full.pk.merge_gathered(gathered, out2)
     torch.cuda.synchronize()
     errs.append(rel(out2.cpu(), out.cpu()))
+    # local merge + exchange in one launch (its own handle: one epoch counter per row)
+    ex2 = ShardExchange.from_process_group(dist.group.WORLD, full.B, full.spec.n_q, full.spec.head_dim, dev,
+                                           n_cta=full.B * full.spec.n_q)
+    out3 = torch.empty_like(out)
+    for rnd in range(3):
+        full.pk.absorb_step(full.q.cuda(), full.qpos.cuda(), ws)
+        full.pk.attend_step(cache, ws, after_absorb=True)
+        ex2.run_parts(ws.partials, ws.n_split, out3)
+        torch.cuda.synchronize()
+        errs.append(rel(out3.cpu(), out.cpu()))
+        assert int(ex2.status.abs().sum()) == 0
     print(f"rank {rank}: rel errors {errs}", flush=True)
-    assert max(errs[:3]) < 2e-3 and errs[3] < 1e-5
+    assert max(errs[:3]) < 2e-3 and errs[3] < 1e-5 and max(errs[4:]) < 1e-5
     dist.barrier()
     dist.destroy_process_group()
 

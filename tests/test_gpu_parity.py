@@ -459,6 +459,45 @@ def test_exchange_merge_emulated_ranks():
             assert int(ranks[r]._epoch[0]) == rnd + 1
 
 
+def test_merge_exchange_one_launch_emulated_ranks():
+    """Merge of the local split-T partials and the exchange in ONE launch. With the ranks' buffers on
+    one GPU the peers' triples are delivered first (push phase of the separate kernel), then rank 0 runs
+    the fused launch: it merges its own partials, pushes, finds the peers' words and must obtain the
+    merge of everything. Two rounds (both slots)."""
+    from phasorkv_b200.sharded import ShardExchange
+    from phasorkv_b200 import _lib
+    G, B, H, d, NS = 3, 2, 32, 128, 7
+    ranks = ShardExchange.local_group(G, B, H, d, n_cta=B * H)
+    pk = PhasorKey.from_spec(synth.make_layer("cfg2", 0))
+    gen = torch.Generator().manual_seed(9)
+    for rnd in range(2):
+        parts = torch.randn((B, NS, H, d + 2), generator=gen)
+        parts[..., -2] *= 10.0
+        parts[..., -1] = parts[..., -1].abs() + 0.1
+        parts[1, 3, :, :] = 0.0
+        parts[1, 3, :, -2] = float("-inf")                             # an empty split
+        parts = parts.cuda()
+        mine = torch.empty((B, H, d + 2), device="cuda")               # what rank 0 contributes
+        _lib.check(_lib.load().pkv_merge(_lib.ptr(parts), NS * H * (d + 2), H * (d + 2), NS, B, H, d, None, _lib.ptr(mine),
+                                         _lib.current_stream()), "pkv_merge")
+        peers = torch.randn((G - 1, B, H, d + 2), generator=gen)
+        peers[..., -2] *= 10.0
+        peers[..., -1] = peers[..., -1].abs() + 0.1
+        peers = peers.cuda()
+        want = torch.empty((B, H, d), device="cuda")
+        pk.merge_gathered(torch.cat([mine[None], peers]), want)
+        for r in range(1, G):
+            ranks[r].run(peers[r - 1], None, _lib.EXCHANGE_PUSH)
+        out = torch.full((B, H, d), float("nan"), device="cuda")
+        ranks[0].run_parts(parts, NS, out)
+        torch.cuda.synchronize()
+        assert int(ranks[0].status.abs().sum()) == 0
+        assert torch.allclose(out, want, rtol=1e-5, atol=1e-6), rnd
+        assert int(ranks[0]._epoch.min()) == rnd + 1
+        for r in range(1, G):                                          # the silent peers follow the epoch by hand
+            ranks[r]._epoch.fill_(rnd + 1)
+
+
 def test_exchange_gives_up_when_a_rank_never_pushes():
     """A peer that never delivers: the merge phase runs out of its bounded wait, reports it in the
     status word and leaves the output untouched; the context stays usable."""
