@@ -535,3 +535,22 @@ def test_tc_reports_page_index_outside_the_pool():
     sc.pk.attend_step(sc.cache, ws, out=ws.out)
     torch.cuda.synchronize()
     assert int(ws.status.abs().sum()) == 0 and rel(ws.out.cpu(), want.cpu()) < 1e-6
+
+
+def test_bench_decode_cli_small(tmp_path):
+    """The decode-benchmark CLI end to end on a small sweep: result file in the reference's form, and
+    an interrupted sweep resumes (keys present are not re-timed)."""
+    import json
+    from phasorkv_b200 import bench_decode as bd
+    out, shp = tmp_path / "r.json", tmp_path / "s.json"
+    argv = ["--configs", "cfg2", "--lens", "1024,4096", "--batches", "2", "--layers", "2", "--iters", "3",
+            "--out", str(out), "--shapes-out", str(shp)]
+    assert bd.main(argv) == 0
+    res = json.load(open(out))
+    keys = sorted(res)
+    assert len(keys) == 2 and keys[0].startswith("cfg2|T1024|B2|algo=tc,n_split=")
+    for v in res.values():
+        assert v["ms"] > 0 and v["gbs"] > 0 and v["tflops"] > 0
+    before = dict(res)
+    assert bd.main(argv) == 0
+    assert json.load(open(out)) == before

@@ -145,3 +145,24 @@ def test_no_cpu_path():
     pk = PhasorKey.from_spec(spec, device="cpu")
     with pytest.raises(_lib.PhasorKVError):
         pk.write(torch.zeros(2, 64), torch.ones(2, 64, dtype=torch.complex64))
+
+
+def test_bench_decode_shapes_and_result_keys(tmp_path):
+    """The decode-benchmark CLI: per-layer shapes export (no GPU) and the reference's result-key form
+    `name|T..|B..|options` (scripts/bench_decode.py:141)."""
+    import json
+    from phasorkv_b200 import bench_decode as bd
+    shapes = bd.kernel_shapes("cfg3", 2)
+    l0 = shapes["layers"]["0"]
+    assert l0["R"] == 120 and l0["R_s"] == 16 and l0["n_slow"] == 8 and l0["W"] == 256
+    assert sum(l0["ranks"]) == 120 and len(l0["ranks"]) == 64 and l0["ranks"][-8:] == [0] * 8
+    s2 = bd.kernel_shapes("cfg2", 32)
+    assert bd.bytes_per_token(s2) == 32 * (144 + 2048)                   # per token: 144 B latent + 2048 B V per layer
+    assert bd.flops_per_token(s2) == 32 * (16384 + 8192)
+    s5 = bd.kernel_shapes("cfg5", 1)
+    assert bd.bytes_per_token(s5) == 72 + 8192
+    assert bd.result_key("cfg2", 4096, 8, dict(algo="tc", n_split=18)) == "cfg2|T4096|B8|algo=tc,n_split=18"
+    out = tmp_path / "shapes.json"
+    assert bd.main(["--configs", "cfg2,cfg5", "--layers", "2", "--shapes-only", "--shapes-out", str(out)]) == 0
+    got = json.load(open(out))
+    assert set(got) == {"cfg2", "cfg5"} and got["cfg5"]["layers"]["1"]["n_kv"] == 32
