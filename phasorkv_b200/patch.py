@@ -12,20 +12,121 @@ on the attention module as ``layer.self_attn.phasor_key`` (with the layer index 
 ``phasor_layer``); ``undo`` removes both. ``prep`` is either a ready ``PhasorKey``, a
 ``synth.LayerSpec``, or a mapping with ``fac`` and ``ranks`` (the reference's ``Factorization``
 and its water-filled ranks) and optionally ``inv_freq`` / ``second``.
+
+With ``install_forward=True`` the patch also replaces the forward of a Hugging Face Llama attention
+module (``hidden_states, position_embeddings, attention_mask, past_key_values, **kwargs`` ->
+``(attn_output, None)``), the way the reference's patches wrap ``self_attn.forward``
+(phasorkv/kvmethods.py:560-611):
+
+  prefill (more than one query token)  the module's own forward computes the output with exact keys;
+                                       beside it every token's rotated latent and V row go into this
+                                       layer's paged caches (``write_paged``, chunked),
+  decode (one query token)             ``prologue_step`` (write + absorb) -> ``attend_step`` ->
+                                       ``o_proj``: keys are never rebuilt, the Hugging Face KV cache
+                                       is not touched.
+
+Positions are counted by the layer's own cache (``seqlens``), so the caller runs the model with
+``use_cache=False`` and feeds one new token per decode call. ``undo`` restores the original forward
+and drops the caches.
 """
 from __future__ import annotations
 
-from .latent import PhasorKey
+from typing import Optional
+
+import torch
+
+from .latent import PAGE_TOKENS, PhasorKey
 
 NVFP4_BITS = 4.5          # E2M1 code + one E4M3 scale per 16 codes (phasorkv/quant.py:9)
 
 
+class LayerDecodeState:
+    """Paged caches, workspace and position bookkeeping of one patched attention layer."""
+
+    def __init__(self, pk: PhasorKey, batch: int, max_tokens: int, write_chunk: int = 4096):
+        self.pk, self.batch, self.max_tokens, self.write_chunk = pk, batch, max_tokens, write_chunk
+        self.cache = pk.new_cache(batch, max_tokens)
+        self.ws = pk.workspace(batch, pk.default_splits(batch, max_tokens))
+        self.seq = torch.arange(batch, dtype=torch.int32, device=pk.device)
+        self.length = 0                                     # tokens cached per sequence (all sequences advance together)
+        self.calibrated = False
+
+    def reset(self) -> None:
+        self.length = 0
+        self.cache.seqlens.zero_()
+
+    def _need(self, n: int) -> None:
+        if self.length + n > self.max_tokens:
+            raise RuntimeError(f"latent cache holds {self.max_tokens} tokens per sequence; {self.length + n} asked")
+
+    def prefill(self, x: torch.Tensor, v: torch.Tensor) -> None:
+        """x [B, T, D] layer input, v [B, T, n_kv, d] value rows: append T tokens to every sequence."""
+        B, T = x.shape[0], x.shape[1]
+        self._need(T)
+        pk = self.pk
+        if not self.calibrated:                             # static tensor scale from the first tokens seen (phasorkv/quant.py:119-124)
+            n = min(T, 4096)
+            pos = torch.arange(self.length, self.length + n, dtype=torch.int32, device=pk.device)
+            rows = torch.empty((n, pk.cache_width), dtype=torch.float32, device=pk.device)
+            pk.write_paged(None, x[0, :n].contiguous(), pos, None, latent_out=rows)
+            pk.calibrate_second(rows)
+            self.calibrated = True
+        for b in range(B):
+            for t0 in range(0, T, self.write_chunk):
+                n = min(self.write_chunk, T - t0)
+                lp = torch.arange(self.length + t0, self.length + t0 + n, dtype=torch.int32, device=pk.device)
+                slots = self.cache.slots(torch.full((n,), b, dtype=torch.int32, device=pk.device), lp)
+                pk.write_paged(self.cache, x[b, t0:t0 + n].contiguous(), lp, slots, v=v[b, t0:t0 + n].contiguous())
+        self.length += T
+        self.cache.seqlens.fill_(self.length)
+
+    def decode(self, x: torch.Tensor, q: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """x [B, D], q [B, n_q, d] pre-RoPE, v [B, n_kv, d] of the one new token -> O [B, n_q, d] fp32."""
+        self._need(1)
+        pk = self.pk
+        pos = torch.full((self.batch,), self.length, dtype=torch.int32, device=pk.device)
+        slots = self.cache.slots(self.seq, pos)
+        self.length += 1
+        self.cache.seqlens.fill_(self.length)
+        # the newest token attends to itself too: query position = its own position
+        pk.prologue_step(self.cache, x.contiguous(), pos, slots, q.float().contiguous(), pos, self.ws, v=v)
+        pk.attend_step(self.cache, self.ws, out=self.ws.out, after_prologue=True)
+        return self.ws.out
+
+
+def _patched_forward(attn, state_of, original):
+    def forward(hidden_states, position_embeddings=None, attention_mask=None, past_key_values=None, **kwargs):
+        B, T = hidden_states.shape[0], hidden_states.shape[1]
+        st: LayerDecodeState = state_of(B)
+        d = attn.head_dim
+        v = attn.v_proj(hidden_states).view(B, T, -1, d)
+        if T > 1:
+            out = original(hidden_states, position_embeddings=position_embeddings, attention_mask=attention_mask,
+                           past_key_values=None, **kwargs)
+            st.prefill(hidden_states, v)
+            return out
+        q = attn.q_proj(hidden_states).view(B, -1, d)
+        o = st.decode(hidden_states[:, 0], q, v[:, 0])
+        o = o.to(hidden_states.dtype).reshape(B, 1, -1)
+        return attn.o_proj(o), None
+    return forward
+
+
 class PhasorKeyPatch:
-    def __init__(self, tag: str = "phasor.nvfp4", bits_v: float = 16.0):
+    def __init__(self, tag: str = "phasor.nvfp4", bits_v: float = 16.0, install_forward: bool = False,
+                 max_tokens: int = 4096):
         self.tag = tag
         self.bits_v = bits_v
+        self.install_forward = install_forward
+        self.max_tokens = ((max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS
         self.layer_stats = {}
         self.keys = {}
+        self.states = {}
+
+    def reset(self) -> None:
+        """Forget the cached tokens of every patched layer (a new prompt follows)."""
+        for st in self.states.values():
+            st.reset()
 
     @property
     def name(self) -> str:
@@ -51,8 +152,27 @@ class PhasorKeyPatch:
         self.layer_stats[i] = dict(bits_k=NVFP4_BITS * pk.cache_width, bits_v=self.bits_v * n_kv * d,
                                    width=pk.cache_width, R=pk.R, R_s=pk.R_s)
 
+        original = None
+        if self.install_forward:
+            original = attn.forward
+            own_forward = attn.__dict__.get("forward")          # an earlier instance-level override, if any
+            max_tokens = self.max_tokens
+
+            def state_of(batch, i=i, pk=pk):
+                st = self.states.get(i)
+                if st is None or st.batch != batch:
+                    st = self.states[i] = LayerDecodeState(pk, batch, max_tokens)
+                return st
+            attn.forward = _patched_forward(attn, state_of, original)
+
         def undo():
             attn.phasor_key, attn.phasor_layer = had
             if had[0] is None:
                 del attn.phasor_key, attn.phasor_layer
+            if original is not None:
+                if own_forward is not None:
+                    attn.forward = own_forward
+                else:
+                    del attn.forward                          # back to the class's forward
+                self.states.pop(i, None)
         return undo

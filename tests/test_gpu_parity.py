@@ -554,3 +554,52 @@ def test_bench_decode_cli_small(tmp_path):
     before = dict(res)
     assert bd.main(argv) == 0
     assert json.load(open(out)) == before
+
+
+def test_hf_llama_attention_patch_decodes_like_the_model():
+    """The patch object installed into the attention modules of a small random Hugging Face Llama whose
+    key projections ARE the factors' W_hat: prefill runs the model's own attention and fills the latent
+    caches, every decode step runs write + absorb + latent attention instead of rebuilding keys. The
+    logits follow the unpatched model (with its own KV cache) up to the NVFP4 error of the latent."""
+    transformers = pytest.importorskip("transformers")
+    import copy
+    from phasorkv_b200.patch import PhasorKeyPatch
+    cfg = transformers.LlamaConfig(vocab_size=256, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                                   num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                                   max_position_embeddings=4096, attn_implementation="eager")
+    torch.manual_seed(3)
+    model = transformers.LlamaForCausalLM(cfg).cuda().float().eval()
+    inv_freq = model.model.rotary_emb.inv_freq.double().cpu()
+    specs = []
+    for l, layer in enumerate(model.model.layers):
+        spec = synth.make_layer("cfg2", l, d_model=512, factor_gain=48.0)
+        spec.inv_freq = inv_freq
+        W = po.w_hat(spec.A, spec.B, spec.freq, spec.n_kv, spec.head_dim)
+        layer.self_attn.k_proj.weight.data.copy_(W.float())
+        specs.append(spec)
+    ref = copy.deepcopy(model)
+    patch = PhasorKeyPatch(install_forward=True, max_tokens=512)
+    undos = [patch.patch(l, layer, specs[l], 8, 128, 32, "cuda") for l, layer in enumerate(model.model.layers)]
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 256, (2, 200), generator=g).cuda()
+    with torch.no_grad():
+        r = ref(input_ids=ids, use_cache=True)
+        o = model(input_ids=ids, use_cache=False)
+        assert rel(o.logits, r.logits) < 1e-5                                  # prefill: the model's own attention
+        past, errs = r.past_key_values, []
+        nxt = r.logits[:, -1].argmax(-1)[:, None]
+        for step in range(4):
+            r = ref(input_ids=nxt, past_key_values=past, use_cache=True)
+            o = model(input_ids=nxt, use_cache=False)
+            errs.append(rel(o.logits, r.logits))
+            past, nxt = r.past_key_values, r.logits[:, -1].argmax(-1)[:, None]
+    torch.cuda.synchronize()
+    print("decode logits rel errors", errs)
+    assert all(int(st.ws.status.abs().sum()) == 0 for st in patch.states.values())
+    assert patch.states[0].length == 204
+    assert max(errs) < 1e-2                                                    # measured 2.4e-3
+    for u in undos:
+        u()
+    assert "forward" not in model.model.layers[0].self_attn.__dict__ and not patch.states
+    with torch.no_grad():
+        assert rel(model(input_ids=ids).logits, ref(input_ids=ids).logits) < 1e-6
