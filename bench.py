@@ -415,7 +415,8 @@ def run_sharded(st, args, dist, world):
         from phasorkv_b200.sharded import ShardExchange
         ex = ShardExchange.from_process_group(dist.group.WORLD, B4, st.n_q, st.d, dev, n_cta=B4 * st.n_q)
     # the newest token (global position T-1) belongs to the last rank: only that rank writes it
-    owner = int(os.environ.get("RANK", 0)) == world - 1 and not st.simt
+    from phasorkv_b200.sharded import owner_of
+    owner = int(os.environ.get("RANK", 0)) == owner_of(T4 - 1, world, T4) and not st.simt
     wpos = torch.full((B4,), T4 - 1, dtype=torch.int32, device=dev)
     wslots = (pt[:, (Tl - 1) // 128] * 128 + (Tl - 1) % 128).to(torch.int32).contiguous()
 

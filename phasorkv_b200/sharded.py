@@ -17,6 +17,26 @@ import torch
 from . import _lib
 
 
+def token_range(rank: int, world: int, n_tokens: int) -> tuple:
+    """Contiguous token range [lo, hi) of a sequence of `n_tokens` tokens that rank `rank` of `world`
+    holds: ranges are disjoint, cover the sequence, differ by at most one token, and keep global
+    positions (the stored phasors need no fix-up)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a group of {world}")
+    return rank * n_tokens // world, (rank + 1) * n_tokens // world
+
+
+def owner_of(position: int, world: int, n_tokens: int) -> int:
+    """Rank that holds (and therefore writes) the token at `position` of a sequence of `n_tokens`."""
+    if not 0 <= position < n_tokens:
+        raise ValueError(f"position {position} outside a sequence of {n_tokens} tokens")
+    for r in range(world):
+        lo, hi = token_range(r, world, n_tokens)
+        if lo <= position < hi:
+            return r
+    raise AssertionError("ranges cover the sequence")
+
+
 def gather_words(world: int, batch: int, n_q: int, head_dim: int) -> int:
     """8-byte words of one rank's gather buffer: [2 slots][world][B*H*(d+2)]."""
     return 2 * world * batch * n_q * (head_dim + 2)

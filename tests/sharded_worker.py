@@ -16,17 +16,17 @@ def main():
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
     from helpers import Scenario, rel
-    from phasorkv_b200.sharded import ShardExchange
+    from phasorkv_b200.sharded import ShardExchange, token_range
     T = 2048
     full = Scenario("cfg2", seqlens=(T, T // 2), gain=64.0, pos0=50000)          # same seeds on every rank
     ws_full = full.pk.workspace(full.B, 2)
     full.pk.absorb_step(full.q.cuda(), full.qpos.cuda(), ws_full)
     full.pk.attend_step(full.cache, ws_full, out=ws_full.out)
     # this rank's token range of every sequence in its own cache
-    lens = [(rank + 1) * Tb // world - rank * Tb // world for Tb in full.seqlens]
+    lens = [token_range(rank, world, Tb)[1] - token_range(rank, world, Tb)[0] for Tb in full.seqlens]
     cache = full.pk.new_cache(full.B, max(lens))
     for b, Tb in enumerate(full.seqlens):
-        lo, hi = rank * Tb // world, (rank + 1) * Tb // world
+        lo, hi = token_range(rank, world, Tb)
         n = hi - lo
         seq = torch.full((n,), b, dtype=torch.int32, device=dev)
         slots = cache.slots(seq, torch.arange(n, dtype=torch.int32, device=dev))

@@ -166,3 +166,37 @@ def test_bench_decode_shapes_and_result_keys(tmp_path):
     assert bd.main(["--configs", "cfg2,cfg5", "--layers", "2", "--shapes-only", "--shapes-out", str(out)]) == 0
     got = json.load(open(out))
     assert set(got) == {"cfg2", "cfg5"} and got["cfg5"]["layers"]["1"]["n_kv"] == 32
+
+
+def test_token_sharded_merge_two_cpu_ranks_gloo():
+    """world_size 2 over gloo on the CPU: each rank takes its token range (the package's sharding rule),
+    computes its partial triple with the oracle, all-gathers, merges: equal to the unsharded result."""
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(os.path.dirname(__file__), "gloo_worker.py")],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, out[-2000:]
+        assert f"rank {r}: tokens" in out
+
+
+def test_token_ranges():
+    from phasorkv_b200.sharded import owner_of, token_range
+    for world in (1, 2, 3, 8):
+        for T in (1, 7, 128, 131072):
+            rs = [token_range(r, world, T) for r in range(world)]
+            assert rs[0][0] == 0 and rs[-1][1] == T
+            assert all(a[1] == b[0] for a, b in zip(rs, rs[1:]))
+            assert max(hi - lo for lo, hi in rs) - min(hi - lo for lo, hi in rs) <= 1
+            assert owner_of(T - 1, world, T) == world - 1
+    with pytest.raises(ValueError):
+        token_range(2, 2, 10)
