@@ -193,6 +193,23 @@ int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const vo
 int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
               int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream);
 
+/* Exact-token side path: the tokens a serving stack keeps as rotated bf16 keys instead of latent rows
+ * (attention sinks, the recent window) take part in the same softmax
+ * (phasorkv/kernels/latent_attn.py:448-495,548-596: exact = (k, v) bf16 [B, n_kv, E, d], k after RoPE).
+ * pkv_exact_partial forms their partial triple (o unnormalised, base-2 max m, sum l) per (sequence,
+ * head) into exact_out_dev [B, n_q, head_dim+2]; pkv_merge_exact is pkv_merge with that triple as one
+ * more part (exact_dev NULL: plain pkv_merge).
+ *   q_dev [B, n_q, head_dim] fp32 pre-RoPE, rotated by the kernel to positions_dev [B] (double angle,
+ *   the layer's attn_scale; band layouts leave their slow frequencies unrotated, as the keys are);
+ *   k_exact_dev, v_exact_dev bf16 [B, n_kv, e_max, head_dim], n_exact_dev [B] valid tokens (NULL: e_max).
+ * Limits: e_max <= 512, head_dim <= 128, at most 8 query heads per kv head. */
+int pkv_exact_partial(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
+                      const void* k_exact_dev, const void* v_exact_dev, const int32_t* n_exact_dev, int32_t e_max,
+                      int32_t batch, float* exact_out_dev, void* stream);
+int pkv_merge_exact(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
+                    int32_t n_q, int32_t head_dim, const float* exact_dev, float* out_dev, float* packed_out_dev,
+                    void* stream);
+
 /* Token-sharded sequences (the token axis of every sequence split over the GPUs of one box; no
  * counterpart in the reference, which is single-GPU): exchange of the per-rank merged triples
  * [B, n_q, head_dim+2] over NVLink peer memory and their merge, in one launch per rank.

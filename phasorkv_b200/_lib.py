@@ -67,6 +67,10 @@ SIGNATURES = {
                                           c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_exchange_merge": (c_int32, [POINTER(Exchange), c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),
     "pkv_merge_exchange": (c_int32, [POINTER(Exchange), c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p]),
+    "pkv_exact_partial": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p,
+                                    c_void_p]),
+    "pkv_merge_exact": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
+                                  c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }

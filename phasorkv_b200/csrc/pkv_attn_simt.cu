@@ -182,7 +182,8 @@ __global__ void __launch_bounds__(NT) pkv_attn_simt_kernel(
 // One CTA per (sequence, head): the merge of pkv_merge.cuh, then the normalised and / or packed store.
 __global__ void __launch_bounds__(MG * 128) pkv_merge_kernel(const float* __restrict__ parts, long stride_b, long stride_p,
                                                              int n_parts, int n_q, int head_dim, int batch,
-                                                             float* __restrict__ out, float* __restrict__ packed_out) {
+                                                             const float* __restrict__ exact, float* __restrict__ out,
+                                                             float* __restrict__ packed_out) {
     __shared__ MergeSmem S;
     const int tid = threadIdx.x, d = tid & 127, g = tid >> 7;
     const int b = blockIdx.x / n_q, h = blockIdx.x % n_q;
@@ -190,7 +191,8 @@ __global__ void __launch_bounds__(MG * 128) pkv_merge_kernel(const float* __rest
     pkv_grid_launch_dependents();
     pkv_grid_wait();
     float a0, a1, M, den;
-    merge_row(parts + (size_t)b * stride_b + (size_t)h * PW, stride_p, n_parts, head_dim, S, a0, a1, M, den);
+    merge_row(parts + (size_t)b * stride_b + (size_t)h * PW, stride_p, n_parts, head_dim, S, a0, a1, M, den,
+              exact ? exact + ((size_t)b * n_q + h) * PW : nullptr);
     if (g == 0) {
         const size_t row = (size_t)b * n_q + h;
         if (d < head_dim) {
@@ -275,15 +277,22 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
     return rc;
 }
 
-extern "C" int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
-                         int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream) {
+extern "C" int pkv_merge_exact(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
+                               int32_t n_q, int32_t head_dim, const float* exact_dev, float* out_dev, float* packed_out_dev,
+                               void* stream) {
     if (!parts_dev || n_parts <= 0 || batch < 0 || n_q <= 0 || head_dim <= 0 || head_dim > 256) return PKV_ERR_INVALID;
-    if (n_parts > pkv_merge_impl::MAX_PARTS) return PKV_ERR_UNSUPPORTED;
+    if (n_parts + (exact_dev ? 1 : 0) > pkv_merge_impl::MAX_PARTS) return PKV_ERR_UNSUPPORTED;
     if ((head_dim & 1) || (stride_b & 1) || (stride_p & 1) || (((uintptr_t)parts_dev) & 7u)) return PKV_ERR_INVALID;   // (m, l) is read as one 8-byte pair
+    if (((uintptr_t)exact_dev) & 7u) return PKV_ERR_INVALID;
     if (!out_dev && !packed_out_dev) return PKV_ERR_INVALID;
     if (batch == 0) return PKV_OK;
     PKV_CUDA_TRY(pkv_launch_chained(pkv_merge_kernel, dim3(batch * n_q), dim3(MG * 128), 0, (cudaStream_t)stream,
-                                    parts_dev, (long)stride_b, (long)stride_p, n_parts, n_q, head_dim, batch, out_dev,
+                                    parts_dev, (long)stride_b, (long)stride_p, n_parts, n_q, head_dim, batch, exact_dev, out_dev,
                                     packed_out_dev));
     return PKV_OK;
+}
+
+extern "C" int pkv_merge(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,
+                         int32_t n_q, int32_t head_dim, float* out_dev, float* packed_out_dev, void* stream) {
+    return pkv_merge_exact(parts_dev, stride_b, stride_p, n_parts, batch, n_q, head_dim, nullptr, out_dev, packed_out_dev, stream);
 }

@@ -73,15 +73,6 @@ struct Extra {                       // lives at X_OFF
 
 static_assert(sizeof(Extra) <= 4096, "barriers and exchange arrays must fit behind the stages");
 
-__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
-                 "r"(r[3]) : "memory");
-}
-
 // order-preserving map float -> uint so that an integer warp reduction gives the float maximum
 __device__ __forceinline__ uint32_t f2ord(float f) { uint32_t b = __float_as_uint(f); return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u); }
 __device__ __forceinline__ float ord2f(uint32_t u) { return __uint_as_float(u ^ ((u >> 31) ? 0x80000000u : 0xFFFFFFFFu)); }
@@ -106,7 +97,15 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
     int32_t* __restrict__ status) {
     using C = Cfg<WP>;
-    constexpr int NKV = NQ / REP;                 // kv heads
+    // A CTA handles at most 8 kv heads (their O^T accumulators take 16 tensor-memory columns each). With
+    // grouped queries (REP = 4 or 8) that is the whole layer; with one query head per kv head (REP = 1, 32
+    // kv heads) blockIdx.z selects a group of 8 heads: the scores of all 32 heads are formed (the latent is
+    // 1 % of the bytes), softmax and P.V run for the group's 8.
+    constexpr int NKV = NQ / REP > 8 ? 8 : NQ / REP;      // kv heads per CTA
+    constexpr int HPC = NKV * REP;                         // query heads per CTA
+    constexpr int PGS = (HPC / 8) * 256;                   // bytes of P per 8-token group: per 8 heads [hi 128 | lo 128]
+    const int h_base = (WV ? (int)blockIdx.z : 0) * HPC, g_base = (WV ? (int)blockIdx.z : 0) * NKV;
+    static_assert(WV || HPC == NQ, "scores-only launches use a grouped-query instantiation");
     extern __shared__ __align__(1024) uint8_t smem[];
     Extra* X = reinterpret_cast<Extra*>(smem + C::X_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -229,8 +228,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                                 if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }
                                 uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
                                 mbar_arrive_expect_tx(&X->v_full[s], V_STAGE_BYTES);
-                                tma_load_2d(dst, &vmap, g * DH, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
-                                tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, g * DH + 64, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                tma_load_2d(dst, &vmap, (g_base + g) * DH, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, (g_base + g) * DH + 64, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
                                 issued = j + 1;
                             }
                         }
@@ -266,10 +265,10 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                     // B operand: 16 rows = the hi weights of the 8-head group holding this kv head's heads, then their lo parts
                     const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + ((g * REP) >> 3) * 256;
                     const uint64_t v_desc = smem_desc(va, V_STAGE_BYTES / 2, 1024, SWZ_128B);
-                    const uint64_t p_desc = smem_desc(pa, 1024, 128, SWZ_NONE);
+                    const uint64_t p_desc = smem_desc(pa, PGS, 128, SWZ_NONE);
 #pragma unroll
                     for (int k = 0; k < PKV_PAGE_TOKENS / 16; ++k)
-                        mma_bf16(tb + TM_O + 16 * g, v_desc + (uint64_t)(k * 2048 / 16), p_desc + (uint64_t)(k * 2048 / 16), idesc_o,
+                        mma_bf16(tb + TM_O + 16 * g, v_desc + (uint64_t)(k * 2048 / 16), p_desc + (uint64_t)(k * 2 * PGS / 16), idesc_o,
                                  !(i == 0 && k == 0));
                     tc_commit(&X->v_empty[s]);
                 }
@@ -321,41 +320,42 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         // Per head (all kept in registers, identical in every thread that shares statistics): the
         // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
         // this thread's share of the sum of 2^(s - m).
-        float cs[NQ], m[NQ], l[NQ];
+        float cs[HPC], m[HPC], l[HPC];
         bool ok = wait_all(&X->q_full, 0, 40);
 #pragma unroll
-        for (int h = 0; h < NQ; ++h) { cs[h] = ok ? rs[h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
+        for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
         for (int i = sg; i < P && ok; i += SG) {
             const int sb = i % NSB;                         // score buffer
             const int buf = i & 1;                          // P buffer and exchange slots
             ok = wait_all(&X->s_full[sb], (i / NSB) & 1, 41);
             if (!ok) break;
             tc_fence_after_sync();
-            float s[NQ];
+            float s[HPC];
             {
 #pragma unroll
                 for (int t = 0; t < PKV_QUERY_TERMS; ++t) {     // the terms share the head's tensor scale: plain sum
-                    uint32_t r[32];
-                    tmem_ld32(tl + TM_S + 128 * sb + 32 * t, r);
+                    uint32_t r[HPC];
+                    if constexpr (HPC == 32) tmem_ld32(tl + TM_S + 128 * sb + 32 * t, r);
+                    else tmem_ld8(tl + TM_S + 128 * sb + 32 * t + h_base, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int h = 0; h < NQ; ++h) s[h] = t == 0 ? __uint_as_float(r[h]) : s[h] + __uint_as_float(r[h]);
+                    for (int h = 0; h < HPC; ++h) s[h] = t == 0 ? __uint_as_float(r[h]) : s[h] + __uint_as_float(r[h]);
                 }
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) s[h] *= cs[h];
+                for (int h = 0; h < HPC; ++h) s[h] *= cs[h];
             }
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
             const bool valid = token < T;
             if (scores_out && valid) {
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) scores_out[((size_t)b * NQ + h) * scores_stride + token] = s[h] * inv_logit_scale;
+                for (int h = 0; h < HPC; ++h) scores_out[((size_t)b * NQ + h_base + h) * scores_stride + token] = s[h] * inv_logit_scale;
             }
             // ---- does any head of any row outgrow its reference maximum by more than the threshold?
             float exc = -INFINITY;
 #pragma unroll
-            for (int h = 0; h < NQ; ++h) {
+            for (int h = 0; h < HPC; ++h) {
                 if (!valid) s[h] = -INFINITY;
                 exc = fmaxf(exc, s[h] - m[h]);              // +inf while the head has no reference yet
             }
@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 // exact tile maximum per head: warp reduction, then (with V) across the four warps
                 float wm = -INFINITY;
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) {
+                for (int h = 0; h < HPC; ++h) {
                     const uint32_t red = __reduce_max_sync(0xffffffffu, f2ord(s[h]));
                     if (lane == h) wm = ord2f(red);
                 }
@@ -387,9 +387,9 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                         tc_fence_after_sync();
                     }
                 }
-                float corr[NQ];
+                float corr[HPC];
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) {
+                for (int h = 0; h < HPC; ++h) {
                     const float m_new = fmaxf(m[h], __shfl_sync(0xffffffffu, tm, h));
                     corr[h] = m[h] > -INFINITY ? exp2f(m[h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
                     m[h] = m_new;
@@ -398,19 +398,15 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 if (with_v && i > 0) {
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
-                        // REP query heads of kv head g: hi columns (g * REP) % 8 .. + REP - 1 of its 16, lo columns 8 further
-                        const uint32_t a = tl + TM_O + 16 * g + ((g * REP) & 7);
+                        // the 16 columns of kv head g are the hi and lo weights of the 8-head group that holds its
+                        // REP query heads (the columns of the group's other heads are never read: any factor does)
+                        uint32_t r[16];
+                        tmem_ld16(tl + TM_O + 16 * g, r);
+                        tmem_ld_wait();
 #pragma unroll
-                        for (int half = 0; half < 2; ++half)                     // hi columns, then lo columns
-#pragma unroll
-                            for (int c0 = 0; c0 < REP; c0 += 4) {
-                                uint32_t r[4];
-                                tmem_ld4(a + 8 * half + c0, r);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int c = 0; c < 4; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[g * REP + c0 + c]);
-                                tmem_st4(a + 8 * half + c0, r);
-                            }
+                        for (int c = 0; c < 16; ++c)
+                            r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[((g * REP) >> 3) * 8 + (c & 7)]);
+                        tmem_st16(tl + TM_O + 16 * g, r);
                     }
                     tmem_st_wait();
                     tc_fence_before_sync();
@@ -423,9 +419,9 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             }
             // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 8-head group
             // [hi | lo] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
-            uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * 1024 + (row & 7) * 2;
+            uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * PGS + (row & 7) * 2;
 #pragma unroll
-            for (int h = 0; h < NQ; ++h) {
+            for (int h = 0; h < HPC; ++h) {
                 float p = exp2f(s[h] - (m[h] > -INFINITY ? m[h] : 0.0f));             // exp2(-inf) = 0 for masked rows
                 if (with_v) {
                     // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
@@ -451,15 +447,13 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             if (with_v) {
 #pragma unroll
                 for (int g = 0; g < NKV; ++g) {
+                    uint32_t r[16];
+                    tmem_ld16(tl + TM_O + 16 * g, r);
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int c0 = 0; c0 < REP; c0 += 4) {
-                        uint32_t r[4], r2[4];
-                        tmem_ld4(tl + TM_O + 16 * g + ((g * REP) & 7) + c0, r);
-                        tmem_ld4(tl + TM_O + 16 * g + 8 + ((g * REP) & 7) + c0, r2);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            part[(g * REP + c0 + c) * (DH + 2) + row] = __uint_as_float(r[c]) + __uint_as_float(r2[c]);
+                    for (int c = 0; c < REP; ++c) {
+                        const int col = ((g * REP) & 7) + c;                  // hi column; its lo part 8 further
+                        part[(h_base + g * REP + c) * (DH + 2) + row] = __uint_as_float(r[col]) + __uint_as_float(r[8 + col]);
                     }
                 }
             } else {
@@ -468,7 +462,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             }
             float lw = 0.0f, mw = -INFINITY;
 #pragma unroll
-            for (int h = 0; h < NQ; ++h) {
+            for (int h = 0; h < HPC; ++h) {
                 float v = l[h];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -476,7 +470,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             }
             X->lsum[sg][quad][lane] = lw;
             X->mfin[sg][quad][lane] = mw;                   // per warp in scores-only mode, identical otherwise
-            if (softmax_sync() && quad == 0 && sg == 0) {
+            if (softmax_sync() && quad == 0 && sg == 0 && lane < HPC) {
                 float M = -INFINITY, lt = 0.0f;
 #pragma unroll
                 for (int w = 0; w < 4 * SG; ++w) M = fmaxf(M, X->mfin[w >> 2][w & 3][lane]);
@@ -485,8 +479,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                     const float mw2 = X->mfin[w >> 2][w & 3][lane];
                     if (mw2 > -INFINITY) lt = fmaf(X->lsum[w >> 2][w & 3][lane], exp2f(mw2 - M), lt);
                 }
-                part[lane * (DH + 2) + DH] = M;
-                part[lane * (DH + 2) + DH + 1] = lt;
+                part[(h_base + lane) * (DH + 2) + DH] = M;
+                part[(h_base + lane) * (DH + 2) + DH + 1] = lt;
             }
         } else {
             softmax_sync();                                 // keep the rendezvous count whole when a group gave up
@@ -556,7 +550,7 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
     if (rc) return rc;
     rc = encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
     if (rc) return rc;
-    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch), dim3(WV ? NTHREADS : NTHREADS_SCORES), smem, st, vmap, kmap, qmap,
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(WV ? NTHREADS : NTHREADS_SCORES), smem, st, vmap, kmap, qmap,
                                     pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
                                     1.0f / logit_scale, flags, partials, scores, scores_stride, status));
     return PKV_OK;
@@ -569,7 +563,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
                        int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream) {
     const int rep = layer->n_q / layer->n_kv;
-    if (rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;          // P.V on tensor cores needs >= 4 query heads per kv head
+    if (rep != 1 && rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;
     if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
     CUtensorMap vmap;
@@ -591,8 +585,13 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)       \
                 : launch_tc<WP_, R_, false>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
                                             flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)
-    if (rep == 4) { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }
-    else { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
+    if (rep == 1 && with_v) {                       // one query head per kv head: 4 CTAs of 8 heads per (sequence, split)
+        rc = wide ? launch_tc<256, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
+                                            partials_dev, scores_out_dev, scores_stride, status_dev, stream)
+                  : launch_tc<128, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
+                                            partials_dev, scores_out_dev, scores_stride, status_dev, stream);
+    } else if (rep == 8) { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
+    else { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }      // scores only never touches V: any grouping
 #undef PKV_TC_CASE
     if (rc == PKV_OK && out_dev) {                  // the merge of the splits: a second, latency-tuned launch
         const int64_t pw = DH + 2;

@@ -24,20 +24,26 @@ struct MergeSmem {
 };
 
 // Called by all MG * 128 threads. `base` = partial 0 of the row, partial p at base + p * stride_p,
-// layout [head_dim values | m | l]. On return every thread holds M and the denominator; the threads
-// with tid < 128 hold the weighted sums of dims tid (a0) and tid + 128 (a1), relative to M.
+// layout [head_dim values | m | l]; `extra`, if not null, is one more partial of the same layout (the
+// exact-token side path) merged as partial number n_parts. On return every thread holds M and the
+// denominator; the threads with tid < 128 hold the weighted sums of dims tid (a0) and tid + 128 (a1),
+// relative to M.
 __device__ __forceinline__ void merge_row(const float* __restrict__ base, long stride_p, int n_parts, int head_dim,
-                                          MergeSmem& S, float& a0, float& a1, float& M_out, float& den_out) {
+                                          MergeSmem& S, float& a0, float& a1, float& M_out, float& den_out,
+                                          const float* __restrict__ extra = nullptr) {
     const int tid = threadIdx.x, d = tid & 127, g = tid >> 7;
+    const int n_own = n_parts;
+    if (extra) ++n_parts;
+    auto part_ptr = [&](int p) -> const float* { return p < n_own ? base + (size_t)p * stride_p : extra; };
     // ---- all loads first
     float2 ml = make_float2(-INFINITY, 0.0f);
-    if (tid < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)tid * stride_p + head_dim));
+    if (tid < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(part_ptr(tid) + head_dim));
     float o0[REG_PARTS], o1[REG_PARTS];
 #pragma unroll
     for (int k = 0; k < REG_PARTS; ++k) {
         const int p = g + k * MG;
-        o0[k] = (p < n_parts && d < head_dim) ? __ldcg(base + (size_t)p * stride_p + d) : 0.0f;
-        o1[k] = (p < n_parts && d + 128 < head_dim) ? __ldcg(base + (size_t)p * stride_p + d + 128) : 0.0f;
+        o0[k] = (p < n_parts && d < head_dim) ? __ldcg(part_ptr(p) + d) : 0.0f;
+        o1[k] = (p < n_parts && d + 128 < head_dim) ? __ldcg(part_ptr(p) + d + 128) : 0.0f;
     }
     // ---- maximum over the partials, weights, denominator
     float M = ml.x;
@@ -74,7 +80,7 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ base, long s
     }
 #pragma unroll 4
     for (int p = g + REG_PARTS * MG; p < n_parts; p += MG) {
-        const float* pp = base + (size_t)p * stride_p;
+        const float* pp = part_ptr(p);
         if (d < head_dim) acc0 = fmaf(S.w[p], __ldcg(pp + d), acc0);
         if (d + 128 < head_dim) acc1 = fmaf(S.w[p], __ldcg(pp + d + 128), acc1);
     }

@@ -104,6 +104,7 @@ class DecodeWorkspace:
         self.out = torch.empty((batch, n_q, head_dim), dtype=torch.float32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.wscratch = None                                                  # decode-time write, see write_scratch()
+        self.exact = None                                                     # exact-token partial, see exact_step()
 
 
 class PhasorKey:
@@ -272,7 +273,9 @@ class PhasorKey:
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         pages = max(1, (max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS)
         per_sm = 3 if simt else 1
-        return max(1, min(pages, (sms * per_sm) // max(1, batch)))
+        # one query head per kv head: the tensor-core kernel runs 4 CTAs (8 heads each) per (sequence, split)
+        groups = 4 if (not simt and self.n_kv == self.n_q) else 1
+        return max(1, min(pages, (sms * per_sm) // max(1, batch * groups)))
 
     def absorb_step(self, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace, operand: bool = True) -> None:
         """q [B, H, d] fp32 at `positions` [B] -> ws.qabs (fp32) and, if asked, ws.qop (operand form)."""
@@ -320,14 +323,30 @@ class PhasorKey:
                                                stride, _lib.ptr(ws.status), _lib.ptr(out),
                                                _lib.current_stream()), "pkv_decode_attn")
 
+    def exact_step(self, q: torch.Tensor, positions: torch.Tensor, k_exact: torch.Tensor, v_exact: torch.Tensor,
+                   ws: DecodeWorkspace, n_exact: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Partial triple of the exact (bf16, rotated keys) tokens: k_exact, v_exact [B, n_kv, E, d] bf16,
+        optional valid counts n_exact [B] -> ws.exact [B, H, d+2]; merged by ``merge_step(exact=True)``."""
+        L = self._layer()
+        B, E = q.shape[0], k_exact.shape[2]
+        if getattr(ws, "exact", None) is None:
+            ws.exact = torch.empty((B, self.n_q, self.head_dim + 2), dtype=torch.float32, device=self.device)
+        k_exact, v_exact = k_exact.to(torch.bfloat16).contiguous(), v_exact.to(torch.bfloat16).contiguous()
+        _lib.check(_lib.load().pkv_exact_partial(ctypes.byref(L), _lib.ptr(q), _lib.ptr(positions), _lib.ptr(k_exact),
+                                                 _lib.ptr(v_exact), _lib.ptr(n_exact), E, B, _lib.ptr(ws.exact),
+                                                 _lib.current_stream()), "pkv_exact_partial")
+        return ws.exact
+
     def merge_step(self, ws: DecodeWorkspace, normalise: bool = True, packed: bool = False,
-                   out: Optional[torch.Tensor] = None) -> None:
-        """Log-sum-exp merge of ws.partials -> `out` or ws.out (normalised) and / or ws.packed (o, m, l)."""
+                   out: Optional[torch.Tensor] = None, exact: bool = False) -> None:
+        """Log-sum-exp merge of ws.partials (and, with `exact`, of ws.exact) -> `out` or ws.out (normalised)
+        and / or ws.packed (o, m, l)."""
         pw = self.head_dim + 2
         out = ws.out if out is None else out
-        _lib.check(_lib.load().pkv_merge(_lib.ptr(ws.partials), ws.n_split * self.n_q * pw, self.n_q * pw, ws.n_split,
-                                         ws.batch, self.n_q, self.head_dim, _lib.ptr(out) if normalise else None,
-                                         _lib.ptr(ws.packed) if packed else None, _lib.current_stream()), "pkv_merge")
+        _lib.check(_lib.load().pkv_merge_exact(_lib.ptr(ws.partials), ws.n_split * self.n_q * pw, self.n_q * pw, ws.n_split,
+                                               ws.batch, self.n_q, self.head_dim, _lib.ptr(ws.exact) if exact else None,
+                                               _lib.ptr(out) if normalise else None,
+                                               _lib.ptr(ws.packed) if packed else None, _lib.current_stream()), "pkv_merge_exact")
 
     def merge_gathered(self, gathered: torch.Tensor, out: torch.Tensor) -> None:
         """gathered [G, B, H, d+2] packed triples of G token shards -> out [B, H, d]."""

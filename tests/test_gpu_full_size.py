@@ -13,8 +13,8 @@ from helpers import rel
 
 pytestmark = pytest.mark.gpu
 
-#            config  batch  context  query heads per kv head allows the tensor-core kernel
-CASES = [("cfg2", 16, 32768, True), ("cfg3", 32, 16384, True), ("cfg4", 4, 131072, True), ("cfg5", 8, 32768, False)]
+#            config  batch  context  tensor-core kernel (cfg5: one query head per kv head, 4 head-group CTAs)
+CASES = [("cfg2", 16, 32768, True), ("cfg3", 32, 16384, True), ("cfg4", 4, 131072, True), ("cfg5", 8, 32768, True)]
 
 
 def _fill(pk, cache, B, T, gen):

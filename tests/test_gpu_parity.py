@@ -338,7 +338,8 @@ def test_tc_decode_lengths(T):
     _check_decode(Scenario("cfg2", seqlens=(T,), pos0=4000), n_split=3, simt=False)
 
 
-@pytest.mark.parametrize("config,gain", [("cfg2", 1.0), ("cfg2", 256.0), ("cfg3", 1.0), ("cfg3", 256.0)])
+@pytest.mark.parametrize("config,gain", [("cfg2", 1.0), ("cfg2", 256.0), ("cfg3", 1.0), ("cfg3", 256.0), ("cfg5", 1.0),
+                                         ("cfg5", 256.0)])
 def test_tc_decode_ragged_batch(config, gain):
     _check_decode(Scenario(config, seqlens=(513, 0, 77, 300), gain=gain, pos0=100000), n_split=4, simt=False)
 
@@ -603,3 +604,56 @@ def test_hf_llama_attention_patch_decodes_like_the_model():
     assert "forward" not in model.model.layers[0].self_attn.__dict__ and not patch.states
     with torch.no_grad():
         assert rel(model(input_ids=ids).logits, ref(input_ids=ids).logits) < 1e-6
+
+
+@pytest.mark.parametrize("config,n_sink,n_recent", [("cfg2", 4, 128), ("cfg3", 4, 128), ("cfg5", 2, 37), ("cfg2", 0, 0)])
+def test_exact_token_side_path(config, n_sink, n_recent):
+    """Attention sinks and a recent window kept as rotated bf16 keys join the softmax of the latent
+    tokens: the extra partial triple, merged with the splits, reproduces softmax over the concatenation
+    [exact tokens | latent tokens] (the reference's latent_decode with `exact`)."""
+    pos0 = 1000
+    sc = Scenario(config, seqlens=(300, 129), gain=48.0, pos0=pos0)
+    spec, B, E = sc.spec, sc.B, n_sink + n_recent
+    g = torch.Generator().manual_seed(31)
+    W = po.w_hat(spec.A, spec.B, spec.freq, spec.n_kv, spec.head_dim, spec.A_s, spec.B_s, spec.slow)
+    slow = spec.slow if spec.slow is not None else torch.zeros(0, dtype=torch.long)
+    k_e = torch.zeros((B, spec.n_kv, max(E, 1), spec.head_dim), dtype=torch.bfloat16)
+    v_e = torch.zeros_like(k_e)
+    for b, T in enumerate(sc.seqlens):
+        # sinks at positions 0.., the recent window right behind the latent tokens; the query follows it
+        pos_e = torch.cat([torch.arange(n_sink), pos0 + T + torch.arange(n_recent)])
+        sc.qpos[b] = pos0 + T + n_recent
+        if E == 0:
+            continue
+        x_e = synth.make_hidden(g, E)
+        ph = po.rope_phasors(spec.inv_freq, pos_e, spec.attn_scale).clone()
+        if slow.numel():
+            ph[:, slow] = ph[0, 0].abs().to(ph.dtype)
+        k = (x_e.double() @ W.T).reshape(E, spec.n_kv, spec.head_dim).transpose(0, 1)
+        cos, sin = torch.cat([ph.real, ph.real], -1), torch.cat([ph.imag, ph.imag], -1)
+        k_e[b, :, :E] = po.hf_rotate(k, cos[None], sin[None]).to(torch.bfloat16)
+        v_e[b, :, :E] = synth.make_values(g, E, spec.n_kv, spec.head_dim).transpose(0, 1)
+    ws = sc.pk.workspace(B, 3)
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    sc.pk.absorb_step(q, qpos, ws)
+    sc.pk.attend_step(sc.cache, ws, after_absorb=True)
+    n_e = torch.full((B,), E, dtype=torch.int32, device="cuda")
+    sc.pk.exact_step(q, qpos, k_e.cuda(), v_e.cuda(), ws, n_exact=n_e)
+    sc.pk.merge_step(ws, exact=True)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    for b, T in enumerate(sc.seqlens):
+        _, S_lat, _ = sc.oracle_scores_and_output(b, sc.dequantised(b))
+        ph_q = po.rope_phasors(spec.inv_freq, sc.qpos[b:b + 1], spec.attn_scale).clone()
+        if slow.numel():
+            ph_q[:, slow] = ph_q[0, 0].abs().to(ph_q.dtype)
+        cq, sq = torch.cat([ph_q.real, ph_q.real], -1), torch.cat([ph_q.imag, ph_q.imag], -1)
+        qr = po.hf_rotate(sc.q[b].double(), cq, sq)                                       # [H, d]
+        ke = k_e[b, :, :E].double().repeat_interleave(spec.n_q // spec.n_kv, dim=0)      # [H, E, d]
+        S_ex = torch.einsum("hd,hed->he", qr, ke).float()
+        S = torch.cat([S_ex, S_lat], dim=1)
+        V = torch.cat([v_e[b, :, :E].transpose(0, 1), sc.v[b]], dim=0)
+        O_ref = po.attend(S, V, spec.n_kv, spec.head_dim)
+        assert rel(ws.out[b].cpu(), O_ref) < OUT_TOL, (b, T)
+        if E:                                                                            # the side path matters in this test
+            assert rel(po.attend(S_lat, sc.v[b], spec.n_kv, spec.head_dim), O_ref) > 5 * OUT_TOL
