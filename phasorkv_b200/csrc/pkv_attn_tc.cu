@@ -35,11 +35,14 @@ constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logi
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // tensor memory columns
-constexpr int NSB_V = 2, NSB_S = 3;   // score buffers (pages in flight between MMA and softmax): with V / scores only
-constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residual terms x 32 heads); 384 columns reserved
+// Score buffers (pages in flight between MMA and softmax): two. In scores-only mode buffer = page parity, so
+// each MMA issuer shares its buffer and barriers with exactly one softmax group (a barrier whose phases are
+// waited for by two threads in turn could be seen a whole phase early by the one that runs ahead).
+constexpr int NSB_V = 2, NSB_S = 2;
+constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residual terms x 32 heads)
 constexpr uint32_t TM_O = 256;        // with V only (then NSB = 2): n_kv x 16 O^T accumulators, 8 hi + 8 lo weight columns
 constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set per score buffer
-constexpr uint32_t TM_SFB = 432;      // 16 : query scale factors, a 4-column group per K step
+constexpr uint32_t TM_SFB = 432;      // 16 per MMA issuer (two in scores-only mode): query scale factors, a 4-column group per K step
 constexpr uint32_t TM_COLS = 512;
 
 template <int WP>
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     constexpr bool with_v = WV;                      // scores-only launches are a separate instantiation
     constexpr int SG = WV ? 1 : 2;                   // softmax groups
     constexpr int NSB = WV ? NSB_V : NSB_S;
-    const int nks = with_v ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
+    constexpr int nks = WV ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
 
     if (P <= 0) {                                  // this split has no token: the neutral partial
@@ -207,9 +210,9 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             if (q_sent) mbar_wait(&X->q_full, 0, 1u << 16);
             for (int i = max(0, issued - nks); i < issued; ++i) mbar_wait(&X->k_full[i % nks], (i / nks) & 1, 1u << 16);
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 && WV) {
         // ================================================================== V producer
-        if (with_v) {
+        {
             if (lane == 0) tma_prefetch_desc(&vmap);
             int issued = 0;
             bool stop = false, waited = !(early && tail_written);
@@ -241,16 +244,24 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
                     mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
         }
-    } else if (warp == 2) {
+    } else if (warp == 2 || warp == 1) {
         // ================================================================== MMA issuer
+        // One thread issues every tcgen05 instruction of its pages; what bounds it is the latency of its own
+        // instruction chain (two satisfied barrier waits, 4 + 4 tcgen05 issues of ~75 cycles, two commits:
+        // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V it is the longest
+        // link, so the warp the V stream leaves idle becomes a second issuer: warp 2 takes the even pages,
+        // warp 1 the odd ones (each feeds the softmax group of its parity).
         if (lane == 0) {
+            const int first = (!WV && warp == 1) ? 1 : 0;
+            constexpr int STEP = WV ? 1 : 2;
+            const uint32_t sfb_tm = tb + TM_SFB + (first ? 16u : 0u);
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
             constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
             bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
             if (ok) {
                 tc_fence_after_sync();
                 for (int k = 0; k < C::KB; ++k)
-                    tmem_cp_32x128b_warpx4(tb + TM_SFB + 4 * k, smem_desc(sbase + C::Q_OFF + C::CODES + k * 512, 0, 128, SWZ_NONE));
+                    tmem_cp_32x128b_warpx4(sfb_tm + 4 * k, smem_desc(sbase + C::Q_OFF + C::CODES + k * 512, 0, 128, SWZ_NONE));
             }
             const uint64_t q_desc = smem_desc(sbase + C::Q_OFF, 0, C::SBO, C::SWZ);
             auto do_pv = [&](int i) -> bool {
@@ -275,10 +286,13 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 tc_commit(&X->pv_done[pb]);
                 return true;
             };
-            for (int i = 0; i < P && ok; ++i) {
-                const int s = i % nks, buf = i % NSB;
-                ok = wait_or_abort(&X->k_full[s], (i / nks) & 1, X, status, 33);
-                if (ok && i >= NSB) ok = wait_or_abort(&X->s_empty[buf], ((i / NSB) - 1) & 1, X, status, 34);
+            // stage, buffer and their barrier phases advance by counters (this thread's instruction chain is the
+            // critical path: no divisions by run-time values in it)
+            int s = first % nks, buf = first % NSB;
+            uint32_t k_phase = 0, s_round = 0;               // s_round = i / NSB
+            for (int i = first; i < P && ok; i += STEP) {
+                ok = wait_or_abort(&X->k_full[s], k_phase, X, status, 33);
+                if (ok && s_round > 0) ok = wait_or_abort(&X->s_empty[buf], (s_round - 1) & 1, X, status, 34);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t ka = sbase + C::K_OFF + s * C::PAGE;
@@ -294,10 +308,14 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
 #pragma unroll
                 for (int k = 0; k < C::KB; ++k)
                     mma_nvfp4(s_tm, a_desc + (uint64_t)(k * 32 / 16), q_desc + (uint64_t)(k * 32 / 16), idesc_s, sfa_tm + 4 * k,
-                              tb + TM_SFB + 4 * k, k != 0);
+                              sfb_tm + 4 * k, k != 0);
                 tc_commit(&X->k_empty[s]);
                 tc_commit(&X->s_full[buf]);
                 if (with_v && i >= 1) ok = do_pv(i - 1);
+                s += STEP;
+                if (s >= nks) { s -= nks; k_phase ^= 1u; }
+                buf += STEP;
+                if (buf >= NSB) { buf -= NSB; ++s_round; }
             }
             if (ok && with_v) do_pv(P - 1);
         }
