@@ -117,7 +117,15 @@ class Stack:
         from phasorkv_b200.latent import PhasorKey
         c = synth.CONFIGS[config]
         self.config, self.algo = config, algo
-        self.B = batch or c["batch"]
+        # cfg5 is quoted on 8 GPUs (64 sequences, 8 per GPU: 69 GB of cache per GPU); the others fit one GPU whole
+        self.B = batch or (c["batch"] // 8 if config == "cfg5" else c["batch"])
+        need = self.B * (context or c["context"]) * n_layers * 2 * 1.02
+        spec0 = synth.make_layer(config, 0)
+        need *= (spec0.cache_width * 9 // 16 + spec0.n_kv * spec0.head_dim * 2) / 2
+        free = torch.cuda.mem_get_info(device)[0]
+        if need > 0.9 * free:
+            raise SystemExit("workload %s needs %.0f GB of cache on this GPU, %.0f GB are free: lower --batch / --context / --layers"
+                             % (config, need / 1e9, free / 1e9))
         self.T = context or c["context"]
         self.device = device
         self.simt = algo == "simt"

@@ -1,10 +1,10 @@
 """Generate the golden vectors under tests/golden/ by running the UNMODIFIED reference.
 
-Run once in a container that has the reference checked out (path in $PHASORKV_REFERENCE, default
-/root/reference); the produced .npz files are committed, this script is not needed to run the
-tests. Everything is seeded; sizes are small so the fixtures stay a few hundred KB.
+Run once on a machine that has the reference checked out, with its path in $PHASORKV_REFERENCE; the
+produced .npz files are committed, this script is not needed to run the tests. Everything is seeded;
+sizes are small so the fixtures stay a few hundred KB.
 
-  python tests/golden/make_golden.py
+  PHASORKV_REFERENCE=<checkout of PhasorKV> python tests/golden/make_golden.py
 """
 import os
 import sys
@@ -12,7 +12,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("PHASORKV_REFERENCE", "/root/reference")
+REF = os.environ.get("PHASORKV_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "phasorkv")):
+    raise SystemExit("set PHASORKV_REFERENCE to a checkout of the reference (the directory that holds phasorkv/)")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
