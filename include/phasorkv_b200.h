@@ -98,6 +98,28 @@ int pkv_device_check(void);
 int64_t pkv_latent_page_bytes(int32_t W);
 int64_t pkv_v_page_bytes(int32_t n_kv, int32_t head_dim);
 
+/* Host-side description of a layer for pkv_layer_create: the arrays of phasorkv.latent.PhasorKey
+ * (phasorkv/latent.py:47-54) in HOST memory, complex arrays as separate real and imaginary parts. */
+typedef struct pkv_layer_host {
+    int32_t d_model, n_q, n_kv, head_dim, R, R_s, n_slow;
+    float   attn_scale, second;
+    const float*   B_re;             /* [R, D] */
+    const float*   B_im;             /* [R, D] */
+    const float*   B_s;              /* [R_s, D] or NULL */
+    const float*   A_re;             /* [n_kv, R] */
+    const float*   A_im;             /* [n_kv, R] */
+    const float*   A_s;              /* [n_kv, 2*n_slow, R_s] or NULL */
+    const int32_t* freq;             /* [R] */
+    const int32_t* slow;             /* [n_slow] or NULL */
+    const double*  inv_freq;         /* [head_dim/2] */
+} pkv_layer_host_t;
+/* Layer handle for hosts without a tensor library: uploads the factors (and builds the three bf16
+ * terms of the tensor-core cache write) into device memory owned by the handle.  These two calls are
+ * the only ones that allocate, free or synchronise; `second` may be changed in the returned struct at
+ * any time (it is read at every call).  Python callers fill pkv_layer_t from torch tensors instead. */
+int pkv_layer_create(const pkv_layer_host_t* host, pkv_layer_t** out);
+int pkv_layer_destroy(pkv_layer_t* layer);
+
 /* NVFP4 quantise-and-pack of given fp32 latent rows into the paged cache: the bit-exact
  * counterpart of quantize_nv_block + pack_nibbles (phasorkv/kernels/nvfp4.py:34-55;
  * rounding rules of phasorkv/quant.py:70-89).  rows_dev [n, W]; slots_dev [n]. */
@@ -136,6 +158,17 @@ int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slot
  * codes_out [n, W/2] packed nibbles; scales_out [n, W/16] E4M3 bytes. */
 int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, float second,
                    float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream);
+
+/* The same entry points under the names of the reference's vocabulary: pkv_quantize_nvfp4 is
+ * pkv_quantize_rows (quantize_nv_block, phasorkv/kernels/nvfp4.py:43-55); pkv_dequant is pkv_cache_read
+ * with the fp32 rows only (nvfp4.py:55).  pkv_status_read copies the 4 status words a kernel may have
+ * written (0 = fine; 1 = a pipeline wait gave up, 2 = page index outside the pool, 3 = a peer never
+ * delivered; word 1 says where) to host memory and waits for the stream: the one call that synchronises. */
+int pkv_quantize_nvfp4(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev, int32_t n_tokens,
+                       float second, void* stream);
+int pkv_dequant(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, float second,
+                float* rows_out_dev, void* stream);
+int pkv_status_read(const int32_t* status_dev, int32_t* status_host, void* stream);
 
 /* Query absorption, PhasorKey.absorb for one query position per sequence
  * (phasorkv/latent.py:72-83).  q_dev [B, n_q, head_dim] fp32 pre-RoPE; positions_dev [B] or, as for

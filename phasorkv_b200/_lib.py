@@ -37,6 +37,14 @@ class Exchange(ctypes.Structure):
                 ("n_cta", c_int32), ("peer_data_dev", c_void_p), ("epoch_dev", c_void_p)]
 
 
+class LayerHost(ctypes.Structure):
+    """struct pkv_layer_host: host arrays for pkv_layer_create."""
+    _fields_ = [("d_model", c_int32), ("n_q", c_int32), ("n_kv", c_int32), ("head_dim", c_int32), ("R", c_int32),
+                ("R_s", c_int32), ("n_slow", c_int32), ("attn_scale", c_float), ("second", c_float),
+                ("B_re", c_void_p), ("B_im", c_void_p), ("B_s", c_void_p), ("A_re", c_void_p), ("A_im", c_void_p),
+                ("A_s", c_void_p), ("freq", c_void_p), ("slow", c_void_p), ("inv_freq", c_void_p)]
+
+
 class Cache(ctypes.Structure):
     _fields_ = [("latent_dev", c_void_p), ("v_dev", c_void_p), ("n_pages", c_int32), ("W", c_int32),
                 ("n_kv", c_int32), ("head_dim", c_int32)]
@@ -57,6 +65,11 @@ SIGNATURES = {
     "pkv_write_scratch_floats": (c_int64, [c_int32, c_int32]),
     "pkv_v_write": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p]),
     "pkv_cache_read": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "pkv_layer_create": (c_int32, [POINTER(LayerHost), POINTER(POINTER(Layer))]),
+    "pkv_layer_destroy": (c_int32, [POINTER(Layer)]),
+    "pkv_quantize_nvfp4": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_float, c_void_p]),
+    "pkv_dequant": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p]),
+    "pkv_status_read": (c_int32, [c_void_p, c_void_p, c_void_p]),
     "pkv_absorb": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_prologue": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -657,3 +657,59 @@ def test_exact_token_side_path(config, n_sink, n_recent):
         assert rel(ws.out[b].cpu(), O_ref) < OUT_TOL, (b, T)
         if E:                                                                            # the side path matters in this test
             assert rel(po.attend(S_lat, sc.v[b], spec.n_kv, spec.head_dim), O_ref) > 5 * OUT_TOL
+
+
+@pytest.mark.parametrize("config", ["cfg2", "cfg3"])
+def test_layer_handle_from_host_arrays(config):
+    """pkv_layer_create (a host without a tensor library uploads PhasorKey's arrays once) gives a layer
+    that writes, quantises and reads back exactly what the torch-owned layer does; the entry points
+    under the reference's names (quantize_nvfp4, dequant, status_read) answer like their originals."""
+    import ctypes
+    from phasorkv_b200 import _lib
+    lib = _lib.load()
+    sc = Scenario(config, seqlens=(200,), pos0=777)
+    spec, pk = sc.spec, sc.pk
+    f32 = lambda t: np.ascontiguousarray(t.numpy().astype(np.float32))
+    keep = dict(B_re=f32(spec.B.real), B_im=f32(spec.B.imag), A_re=f32(spec.A.real), A_im=f32(spec.A.imag),
+                freq=np.ascontiguousarray(spec.freq.numpy().astype(np.int32)),
+                inv_freq=np.ascontiguousarray(spec.inv_freq.numpy().astype(np.float64)))
+    if spec.R_s:
+        keep.update(B_s=f32(spec.B_s), A_s=f32(spec.A_s), slow=np.ascontiguousarray(spec.slow.numpy().astype(np.int32)))
+    p = lambda k: keep[k].ctypes.data if k in keep else None
+    host = _lib.LayerHost(spec.d_model, spec.n_q, spec.n_kv, spec.head_dim, spec.R, spec.R_s,
+                          0 if spec.slow is None else int(spec.slow.numel()), spec.attn_scale, sc.second,
+                          p("B_re"), p("B_im"), p("B_s"), p("A_re"), p("A_im"), p("A_s"), p("freq"), p("slow"), p("inv_freq"))
+    handle = ctypes.POINTER(_lib.Layer)()
+    _lib.check(lib.pkv_layer_create(ctypes.byref(host), ctypes.byref(handle)), "pkv_layer_create")
+    try:
+        n, W = 200, spec.cache_width
+        slots = sc.slots_of(0)
+        for dt in (torch.float32, torch.bfloat16):                   # CUDA-core and tensor-core write kernels
+            x = sc.x[0].cuda().to(dt)
+            cache2 = pk.new_cache(1, n)
+            out = torch.zeros((n, W), device="cuda")
+            pos = sc.pos[0].to(torch.int32).cuda()
+            _lib.check(lib.pkv_cache_write(handle, ctypes.byref(cache2.c), _lib.ptr(x), pk._xdt(x), _lib.ptr(pos), None,
+                                           _lib.ptr(slots), n, _lib.ptr(out), None, None, _lib.ptr(pk._dev["status"]),
+                                           _lib.current_stream()), "pkv_cache_write")
+            cache3 = pk.new_cache(1, n)
+            out3 = torch.zeros_like(out)
+            pk.write_paged(cache3, x, pos, slots, latent_out=out3)
+            torch.cuda.synchronize()
+            assert torch.equal(out, out3) and torch.equal(cache2.latent, cache3.latent)
+        # the aliases
+        rows = torch.empty((n, W), device="cuda")
+        _lib.check(lib.pkv_dequant(ctypes.byref(cache3.c), _lib.ptr(slots), n, sc.second, _lib.ptr(rows), _lib.current_stream()),
+                   "pkv_dequant")
+        want, _, _ = cache3.read(slots, sc.second, codes=False)
+        cache4 = pk.new_cache(1, n)
+        _lib.check(lib.pkv_quantize_nvfp4(ctypes.byref(cache4.c), _lib.ptr(out3), _lib.ptr(slots), n, sc.second,
+                                          _lib.current_stream()), "pkv_quantize_nvfp4")
+        host_status = (ctypes.c_int32 * 4)(9, 9, 9, 9)
+        _lib.check(lib.pkv_status_read(_lib.ptr(pk._dev["status"]), host_status, _lib.current_stream()), "pkv_status_read")
+        assert torch.equal(rows, want)
+        assert torch.equal(cache4.latent, cache3.latent)              # quantising the dumped rows again: same codes
+        assert list(host_status) == [0, 0, 0, 0]
+    finally:
+        _lib.check(lib.pkv_layer_destroy(handle), "pkv_layer_destroy")
+    assert lib.pkv_layer_create(None, ctypes.byref(handle)) != 0
