@@ -130,6 +130,9 @@ class Stack:
         self.device = device
         self.simt = algo == "simt"
         self.fused_prologue = os.environ.get("PKV_BENCH_SEPARATE_PROLOGUE", "0") != "1"
+        # PKV_BENCH_INLINE_ABSORB=1: the write alone as prologue and pkv_decode_attn_q (absorption inside the attention
+        # kernel). Measured slower at present (251 against 196 us per layer): the default keeps the fused prologue.
+        self.inline_absorb = os.environ.get("PKV_BENCH_INLINE_ABSORB", "0") == "1"
         self.layers, self.caches = [], []
         g = torch.Generator(device=device).manual_seed(seed)
         for l in range(n_layers):
@@ -195,7 +198,11 @@ class Stack:
             if pre is not None:
                 pre(l)
             fused = write and not self.simt and self.fused_prologue
-            if fused:                                                 # newest token's write + absorb: one launch
+            inline = fused and self.inline_absorb and not scores_only
+            if inline:                                                # the write alone; attention absorbs the raw queries
+                pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], None, None, ws, v=self.v_new[l])
+                n += 1
+            elif fused:                                               # newest token's write + absorb: one launch
                 pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l])
                 n += 1
             else:
@@ -208,8 +215,13 @@ class Stack:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=events is None and not fused,
-                           after_prologue=events is None and fused)
+            if inline:
+                # the queries of the step exist before the layer's first launch: attention starts with the write,
+                # streams pages and absorbs at once, and waits for the write only before the page being written
+                pk.attend_q_step(cache, self.q[l], self.qpos, ws, early=events is None, tail_written=True, query_ready=True)
+            else:
+                pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=events is None and not fused,
+                               after_prologue=events is None and fused)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
@@ -428,23 +440,34 @@ def run_sharded(st, args, dist, world):
     wpos = torch.full((B4,), T4 - 1, dtype=torch.int32, device=dev)
     wslots = (pt[:, (Tl - 1) // 128] * 128 + (Tl - 1) % 128).to(torch.int32).contiguous()
 
-    def step():
-        for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
+    inline = st.inline_absorb and not st.simt
+
+    def attend(pk, cache, l, **out_kw):
+        """attention of layer l on this rank's shard: raw queries absorbed in the kernel, or absorb launch + operand"""
+        if inline:
+            if owner:                                       # the write alone; attention waits for it before the last page only
+                pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, None, None, ws, v=st.v_new[l, :B4])
+            pk.attend_q_step(cache, st.q[l, :B4], qpos, ws, early=True, tail_written=owner, query_ready=True, **out_kw)
+        else:
             if owner:
                 pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4])
             else:
                 pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
             early = dict(after_prologue=True) if owner else dict(after_absorb=True)
+            pk.attend_step(cache, ws, simt=st.simt, **early, **out_kw)
+
+    def step():
+        for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
             if world > 1:
                 if ex is not None:
-                    pk.attend_step(cache, ws, simt=st.simt, **early)
+                    attend(pk, cache, l)
                     ex.run_parts(ws.partials, ws.n_split, out)      # local merge + peer stores + merge, one kernel
                 else:
-                    pk.attend_step(cache, ws, simt=st.simt, packed_out=ws.packed, **early)   # local splits merged by a launch behind
+                    attend(pk, cache, l, packed_out=ws.packed)      # local splits merged by a launch behind
                     dist.all_gather_into_tensor(gathered, ws.packed)
                     pk.merge_gathered(gathered, out)
             else:
-                pk.attend_step(cache, ws, simt=st.simt, out=out, **early)
+                attend(pk, cache, l, out=out)
     for c in st.caches:
         c.page_table, c.seqlens, c.max_pages = pt, seqlens, pages
     graphed = False

@@ -48,6 +48,9 @@ enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
 #define PKV_ATTN_TAIL_WRITTEN 16u    /* with PKV_ATTN_EARLY_STREAM: the launch before is pkv_decode_prologue, which also
                                         writes the newest token (position seqlen-1) of each sequence: the last page
                                         of a sequence is fetched only after that launch has completed */
+#define PKV_ATTN_QUERY_READY 32u     /* pkv_decode_attn_q with PKV_ATTN_EARLY_STREAM: the queries and their positions were
+                                        complete before the launch directly before this one was enqueued (they do
+                                        not come from it): the kernel absorbs them without waiting for that launch */
 #define PKV_ATTN_PACKED_OUT  4u      /* out_dev receives the merged triple [B, n_q, head_dim+2] (o, m, l), not normalised */
 
 /* One layer's factors, in the attribute convention of phasorkv.latent.PhasorKey
@@ -190,7 +193,8 @@ int64_t pkv_query_operand_bytes(int32_t W);
  * those of the two separate calls. The single launch needs batch <= PKV_SMALL_WRITE_TOKENS, R a
  * multiple of 16 and d_model a multiple of 32 and at most 16384; otherwise the two separate launches
  * are made (scratch_dev, optional, is only used then). latent_out_dev, qabs_out_dev, qop_out_dev,
- * v_rows_dev are optional as in the separate calls. */
+ * v_rows_dev are optional as in the separate calls. q_dev NULL: the write alone (the queries are then
+ * absorbed by pkv_decode_attn_q). */
 int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                         const int32_t* write_positions_dev, const int32_t* slots_dev, const void* v_rows_dev,
                         const float* q_dev, const int32_t* query_positions_dev, int32_t batch,
@@ -217,6 +221,18 @@ int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const vo
                     int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
                     float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
                     void* stream);
+
+/* pkv_decode_attn on RAW queries: q_dev [B, n_q, head_dim] fp32 pre-RoPE at query_positions_dev [B].
+ * The tensor-core kernel absorbs them itself (every CTA forms the NVFP4 operand of its sequence in
+ * shared memory with the arithmetic of pkv_absorb: same bits, same results) - no pkv_absorb launch, no
+ * operand in global memory.  Flags as for pkv_decode_attn except PKV_ATTN_SIMT (unsupported);
+ * PKV_ATTN_EARLY_STREAM here means that the launch directly before writes neither page table nor
+ * lengths nor cache rows (except, with PKV_ATTN_TAIL_WRITTEN, rows of each sequence's last page), and
+ * the queries are waited for unless PKV_ATTN_QUERY_READY is given as well. */
+int pkv_decode_attn_q(const pkv_layer_t* layer, const pkv_cache_t* cache, const float* q_dev,
+                      const int32_t* query_positions_dev, const int32_t* page_table_dev, int32_t max_pages,
+                      const int32_t* seqlens_dev, int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
+                      float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev, void* stream);
 
 /* Log-sum-exp merge of n_parts partial triples per (sequence, head): M = max m, w = 2^(m - M),
  * O = sum w o / sum w l (phasorkv/kernels/dense_attn.py:72-74).  parts_dev is addressed as

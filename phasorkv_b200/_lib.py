@@ -16,7 +16,7 @@ MAX_WIDTH = 256
 QUERY_TERMS = 4
 NOALLOC_MAX_PARTS = 320
 F32, BF16 = 0, 1
-ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT, ATTN_EARLY_STREAM, ATTN_TAIL_WRITTEN = 1, 2, 4, 8, 16
+ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT, ATTN_EARLY_STREAM, ATTN_TAIL_WRITTEN, ATTN_QUERY_READY = 1, 2, 4, 8, 16, 32
 EXCHANGE_PUSH, EXCHANGE_MERGE = 1, 2
 
 
@@ -76,6 +76,8 @@ SIGNATURES = {
                                       c_void_p]),
     "pkv_decode_attn": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                   c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "pkv_decode_attn_q": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int32,
+                                    c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                           c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_exchange_merge": (c_int32, [POINTER(Exchange), c_void_p, c_void_p, c_uint32, c_void_p, c_void_p]),

@@ -212,4 +212,108 @@ __device__ __forceinline__ void body(const Args& P, int b, int hg, float* sm) {
 }
 
 
+// The same arithmetic for ALL 32 query heads of one sequence by a group of 128 threads, the operand tile
+// written to SHARED memory: the attention kernel absorbs its own query instead of reading the blob a
+// separate launch left in global memory. Thread (h = tid / 4, quarter = tid % 4) owns a quarter of head
+// h's row in registers. `blob` = the kernel's query-operand region, `scratch` = TILE_SCRATCH_FLOATS floats
+// of shared memory free until the call returns. The 128 threads meet on named barrier 1. Every operation
+// is the one `body` makes, in the same order per value: the operand bytes are identical.
+constexpr int TILE_THREADS = 128;
+constexpr int TILE_QP = 132;                                   // pitch of a query row in shared memory (bank spread)
+constexpr int TILE_SCRATCH_FLOATS = 2 * MAX_H + 32 * TILE_QP;
+
+__device__ __forceinline__ void tile_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int WP>
+__device__ __forceinline__ void body_tile(const Args& P, int b, uint8_t* blob, float* scratch, int tid) {
+    constexpr int NBT = WP / 64;                               // 16-column blocks per thread
+    const int head_dim = P.head_dim, h2 = head_dim / 2, R = P.R, R_s = P.R_s, n_slow = P.n_slow;
+    const int W = 2 * R + R_s, n_q = P.n_q;
+    float2* ph = reinterpret_cast<float2*>(scratch);           // [h2]
+    float* qs = scratch + 2 * MAX_H;                           // [n_q][TILE_QP] raw (pre-RoPE) query
+    const float* qb = P.q + (size_t)b * n_q * head_dim;
+    // query rows first (the loads fly while the phasors are formed)
+    const int n4 = n_q * head_dim / 4;
+    constexpr int QV = 8;                                      // 16-byte loads per thread: 32 heads x 128 dims
+    float4 qv[QV];
+#pragma unroll
+    for (int n = 0; n < QV; ++n) {
+        const int i = tid + n * TILE_THREADS;
+        qv[n] = i < n4 ? *reinterpret_cast<const float4*>(qb + (size_t)i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int j = tid; j < h2; j += TILE_THREADS) {
+        double sn, cs;
+        sincos((double)P.positions[b] * P.inv_freq[j], &sn, &cs);
+        ph[j] = make_float2((float)((double)P.attn_scale * cs), (float)((double)P.attn_scale * sn));
+    }
+#pragma unroll
+    for (int n = 0; n < QV; ++n) {
+        const int i = tid + n * TILE_THREADS;
+        if (i < n4) {
+            const int e = i * 4, hh = e / head_dim, col = e % head_dim;
+            float* dst = qs + hh * TILE_QP + col;
+            dst[0] = qv[n].x; dst[1] = qv[n].y; dst[2] = qv[n].z; dst[3] = qv[n].w;
+        }
+    }
+    tile_barrier();
+    const int h = tid >> 2, quarter = tid & 3, g = h / (n_q / P.n_kv);
+    const float* qh = qs + h * TILE_QP;
+    float res[NBT][16];
+    float am = 0.0f;
+#pragma unroll
+    for (int blk = 0; blk < NBT; ++blk) {
+        // all global loads of the block first (frequency index and factor of each column are independent
+        // loads: one memory latency per block, not one per column), then the arithmetic
+        int fk[16];
+        float ar[16], ai[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {                       // unconditional (index clamped): straight-line code, loads in flight together
+            const int c = (quarter * NBT + blk) * 16 + i;
+            const int k = min(c < R ? c : c - R, R - 1);
+            fk[i] = P.freq[k];
+            ar[i] = P.A_re[g * R + k];
+            ai[i] = P.A_im[g * R + k];
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = (quarter * NBT + blk) * 16 + i;
+            float v = 0.0f;
+            if (c < 2 * R) {
+                const int f = fk[i];
+                const float a = qh[f], cc = qh[f + h2];
+                const float2 p = ph[f];
+                const float zx = __fsub_rn(__fmul_rn(a, p.x), __fmul_rn(cc, p.y));
+                const float zy = __fadd_rn(__fmul_rn(a, p.y), __fmul_rn(cc, p.x));
+                // conj(A) * z = (ar*zr + ai*zi) + i (ar*zi - ai*zr)
+                v = c < R ? __fadd_rn(__fmul_rn(ar[i], zx), __fmul_rn(ai[i], zy)) : __fsub_rn(__fmul_rn(ar[i], zy), __fmul_rn(ai[i], zx));
+            } else if (c < W) {
+                const int r = c - 2 * R;
+                for (int s = 0; s < 2 * n_slow; ++s) {
+                    const int col = s < n_slow ? P.slow[s] : P.slow[s - n_slow] + h2;
+                    v = fmaf(qh[col], P.A_s[((size_t)g * 2 * n_slow + s) * R_s + r], v);
+                }
+            }
+            res[blk][i] = v;
+            am = fmaxf(am, fabsf(v));
+        }
+    }
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));        // the four threads of a head are neighbours in a warp
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    const float second = fmaxf(am, 1e-30f) * (1.0f / (448.0f * 6.0f));
+    const float inv_second = __frcp_rn(second);
+    constexpr int RB = WP / 2, CODES = PKV_PAGE_TOKENS * RB, PAGE = CODES + (WP / 64) * 512;
+    for (int term = 0; term < PKV_QUERY_TERMS; ++term) {
+        const uint32_t n = term * n_q + h;
+#pragma unroll
+        for (int blk = 0; blk < NBT; ++blk) {
+            const int j = quarter * NBT + blk;
+            uint8_t sb;
+            const uint2 packed = quantize_query_block16(res[blk], second, inv_second, sb);
+            *reinterpret_cast<uint2*>(blob + pkv_code_offset(n, j * 8, RB)) = packed;
+            blob[CODES + pkv_scale_offset(n, j)] = sb;
+        }
+    }
+    if (quarter == 0) reinterpret_cast<float*>(blob + PAGE)[h] = second;
+}
+
 }  // namespace pkv_absorb_impl

@@ -10,7 +10,8 @@ int pkv_check_cache(const pkv_cache_t* c);
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream);
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream,
+                       const float* q_raw_dev = nullptr, const int32_t* q_positions_dev = nullptr);
 
 namespace {
 
@@ -275,6 +276,28 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
                        packed ? out_dev : nullptr, stream);
     }
     return rc;
+}
+
+extern "C" int pkv_decode_attn_q(const pkv_layer_t* layer, const pkv_cache_t* cache, const float* q_dev,
+                                 const int32_t* query_positions_dev, const int32_t* page_table_dev, int32_t max_pages,
+                                 const int32_t* seqlens_dev, int32_t batch, int32_t n_split, uint32_t flags,
+                                 float* partials_dev, float* scores_out_dev, int64_t scores_stride, int32_t* status_dev,
+                                 float* out_dev, void* stream) {
+    int st = pkv_check_layer(layer);
+    if (st) return st;
+    st = pkv_check_cache(cache);
+    if (st) return st;
+    if (batch == 0) return PKV_OK;
+    if (!q_dev || !query_positions_dev || !page_table_dev || !seqlens_dev || !partials_dev) return PKV_ERR_INVALID;
+    if (batch < 0 || n_split <= 0 || max_pages <= 0 || n_split > 65535 || batch > 65535) return PKV_ERR_INVALID;
+    if (cache->W != 2 * layer->R + layer->R_s || cache->n_kv != layer->n_kv || cache->head_dim != layer->head_dim)
+        return PKV_ERR_INVALID;
+    if (layer->n_q != NQ || layer->head_dim != DH) return PKV_ERR_UNSUPPORTED;
+    if (flags & PKV_ATTN_SIMT) return PKV_ERR_UNSUPPORTED;             // the CUDA-core kernel takes the fp32 absorbed query
+    if (!(flags & PKV_ATTN_SCORES_ONLY) && !cache->v_dev) return PKV_ERR_INVALID;
+    return pkv_attn_tc_launch(layer, cache, nullptr, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, partials_dev,
+                              scores_out_dev, scores_stride, status_dev, out_dev, (cudaStream_t)stream, q_dev,
+                              query_positions_dev);
 }
 
 extern "C" int pkv_merge_exact(const float* parts_dev, int64_t stride_b, int64_t stride_p, int32_t n_parts, int32_t batch,

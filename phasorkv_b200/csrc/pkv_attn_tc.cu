@@ -12,6 +12,7 @@
 //                           rare rescale of the O accumulators in TMEM
 // Stages are handed over through mbarriers; every wait is bounded and a give-up is recorded in
 // `status` while all roles unwind, free TMEM and return.
+#include "pkv_absorb.cuh"
 #include "pkv_common.cuh"
 #include "pkv_tcgen05.cuh"
 
@@ -92,14 +93,17 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
 }
 
 
-template <int WP, int REP, bool WV>
+template <int WP, int REP, bool WV, bool INLQ>
 __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_tc_kernel(
     const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap kmap,
     const __grid_constant__ CUtensorMap qmap, const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
-    int32_t* __restrict__ status) {
+    int32_t* __restrict__ status, const pkv_absorb_impl::Args qa) {
     using C = Cfg<WP>;
+    // qa.q set: the kernel absorbs the raw queries itself (softmax group 0, pkv_absorb_impl::body_tile) instead
+    // of loading the operand a pkv_absorb launch left in global memory
+    constexpr bool inline_q = INLQ;                  // a separate instantiation: the plain kernels do not carry this code
     // A CTA handles at most 8 kv heads (their O^T accumulators take 16 tensor-memory columns each). With
     // grouped queries (REP = 4 or 8) that is the whole layer; with one query head per kv head (REP = 1, 32
     // kv heads) blockIdx.z selects a group of 8 heads: the scores of all 32 heads are formed (the latent is
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
 
     // ---- prologue that touches no global memory: barriers, tensor memory
     if (tid == 0) {
-        mbar_init(&X->q_full, 1);
+        mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
         for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
 
     if (P <= 0) {                                  // this split has no token: the neutral partial
+        if (early) pkv_grid_wait();                // the partials may still be read by the launches before (see the epilogue)
         for (int i = tid; i < NQ * (DH + 2); i += blockDim.x) {
             int c = i % (DH + 2);
             part[i] = c == DH ? -INFINITY : 0.0f;
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         // at one page per memory latency.
         if (lane == 0) { tma_prefetch_desc(&kmap); tma_prefetch_desc(&qmap); }
         int issued = 0;
-        bool q_sent = false, stop = false;
+        bool q_sent = inline_q, stop = false, waited = !early;
         for (int base = 0; base <= P && !stop; base += 32) {
             const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
             for (int jj = 0; jj < 32 && base + jj <= P && !stop; ++jj) {
@@ -181,11 +186,12 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 if (lane == 0) {
                     // early mode: first fill the latent stages (but never with a page that is still being written)
                     if (!q_sent && (!early || i == min(P, nks) || (tail_written && p_lo + i == npages - 1))) {
-                        if (early) pkv_grid_wait();
+                        if (!waited) { pkv_grid_wait(); waited = true; }
                         mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
                         tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
                         q_sent = true;
                     }
+                    if (!waited && tail_written && i < P && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                     if (i < P) {
                         const int s = i % nks;
                         if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) {
@@ -339,6 +345,13 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
         // this thread's share of the sum of 2^(s - m).
         float cs[HPC], m[HPC], l[HPC];
+        if constexpr (INLQ) if (sg == 0) {
+            // the query may come from the launch before this one unless the caller says it was ready earlier
+            if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
+            pkv_absorb_impl::body_tile<WP>(qa, b, smem + C::Q_OFF, reinterpret_cast<float*>(smem + C::P_OFF), tid - 3 * 32);
+            fence_proxy_async_smem();                       // generic-proxy writes -> visible to tcgen05.mma / tcgen05.cp
+            mbar_arrive(&X->q_full);
+        }
         bool ok = wait_all(&X->q_full, 0, 40);
 #pragma unroll
         for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
@@ -460,6 +473,10 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         }
         // ---- epilogue: O^T back from TMEM, row sums reduced over the 128 token rows
         if (ok && with_v) ok = wait_all(&X->pv_done[(P - 1) & 1], ((P - 1) >> 1) & 1, 44);
+        // A CTA that streamed early may never have waited for the launch before this one. It does so now, at no
+        // cost: every launch of the chain then completes only after its predecessor, so a launch further
+        // back that still reads these partials (the merge of the step before) is known to have finished.
+        if (early) pkv_grid_wait();
         if (ok) {
             tc_fence_after_sync();
             if (with_v) {
@@ -551,11 +568,11 @@ int encode_rows128_map(CUtensorMap* map, const void* base, uint64_t rows, uint32
     return PKV_OK;
 }
 
-template <int WP, int REP, bool WV>
-int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
+template <int WP, int REP, bool WV, bool INLQ>
+int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
-              long scores_stride, int32_t* status, cudaStream_t st) {
-    auto kern = pkv_attn_tc_kernel<WP, REP, WV>;
+              long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
+    auto kern = pkv_attn_tc_kernel<WP, REP, WV, INLQ>;
     constexpr int smem = Cfg<WP>::SMEM;
     static bool attr_done = false;                                  // once per instantiation
     if (!attr_done) {
@@ -566,12 +583,24 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
     CUtensorMap kmap, qmap;
     int rc = encode_rows128_map(&kmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::PAGE / 128);
     if (rc) return rc;
-    rc = encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
+    // with in-kernel absorption the operand map is never used: it is encoded over the latent pool to stay well formed
+    rc = qa.q ? encode_rows128_map(&qmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::QBLOB / 128)
+              : encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
     if (rc) return rc;
     PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(WV ? NTHREADS : NTHREADS_SCORES), smem, st, vmap, kmap, qmap,
                                     pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
-                                    1.0f / logit_scale, flags, partials, scores, scores_stride, status));
+                                    1.0f / logit_scale, flags, partials, scores, scores_stride, status, qa));
     return PKV_OK;
+}
+
+template <int WP, int REP, bool WV>
+int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
+              int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
+              long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
+    return qa.q ? launch_tc_impl<WP, REP, WV, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials, scores,
+                                                    scores_stride, status, qa, st)
+                : launch_tc_impl<WP, REP, WV, false>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
+                                                     scores, scores_stride, status, qa, st);
 }
 
 }  // namespace
@@ -579,10 +608,20 @@ int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* 
 int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev,
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
-                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream) {
+                       int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream,
+                       const float* q_raw_dev, const int32_t* q_positions_dev) {
     const int rep = layer->n_q / layer->n_kv;
+    pkv_absorb_impl::Args qa;
+    memset(&qa, 0, sizeof(qa));
+    if (q_raw_dev) {                                // raw queries: absorbed inside the kernel
+        if (!q_positions_dev || (((uintptr_t)q_raw_dev) & 15u)) return PKV_ERR_INVALID;
+        if (layer->head_dim / 2 > pkv_absorb_impl::MAX_H) return PKV_ERR_UNSUPPORTED;
+        qa = pkv_absorb_impl::make_args(layer, q_raw_dev, q_positions_dev, nullptr, nullptr, nullptr);
+    } else if (!q_dev) {
+        return PKV_ERR_INVALID;
+    }
     if (rep != 1 && rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;
-    if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
+    if (q_dev && (((uintptr_t)q_dev) & 15u)) return PKV_ERR_INVALID;
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
     CUtensorMap vmap;
     memset(&vmap, 0, sizeof(vmap));
@@ -600,14 +639,14 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     int rc;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
     rc = with_v ? launch_tc<WP_, R_, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
-                                           flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)       \
+                                           flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)       \
                 : launch_tc<WP_, R_, false>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
-                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, stream)
+                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
     if (rep == 1 && with_v) {                       // one query head per kv head: 4 CTAs of 8 heads per (sequence, split)
         rc = wide ? launch_tc<256, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
-                                            partials_dev, scores_out_dev, scores_stride, status_dev, stream)
+                                            partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
                   : launch_tc<128, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
-                                            partials_dev, scores_out_dev, scores_stride, status_dev, stream);
+                                            partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream);
     } else if (rep == 8) { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
     else { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }      // scores only never touches V: any grouping
 #undef PKV_TC_CASE

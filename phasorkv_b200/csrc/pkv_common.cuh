@@ -89,10 +89,12 @@ __device__ __forceinline__ uint8_t pkv_float_to_e4m3(float x) {
 }
 
 __device__ __forceinline__ float pkv_e2m1_value(uint32_t code) {
-    // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 : code bits 0-2, sign bit 3
-    uint32_t m = code & 7u;
-    float v = (m < 2u) ? 0.5f * (float)m : (float)(2u + (m & 1u)) * (float)(1u << (m >> 1)) * 0.25f;
-    return (code & 8u) ? -v : v;
+    // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 : code bits 0-2 (2 exponent bits, bias 1, and 1 mantissa bit), sign bit 3.
+    // The float is assembled from its fields (integer ALU only: int -> float conversions share a slow pipe):
+    // exponent field e >= 1 -> 2^(e-1) * (1 + mant/2); e == 0 -> mant * 0.5
+    const uint32_t e = (code >> 1) & 3u, mant = code & 1u;
+    const uint32_t bits = e ? (((126u + e) << 23) | (mant << 22)) : (mant ? 0x3F000000u : 0u);
+    return __uint_as_float(bits | ((code & 8u) << 28));
 }
 
 // E4M3 scale byte of a block with the given max magnitude

@@ -273,7 +273,7 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     if (st) return st;
     if (batch < 0) return PKV_ERR_INVALID;
     if (batch == 0) return PKV_OK;
-    if (!cache || !x_dev || !write_positions_dev || !slots_dev || !q_dev || !query_positions_dev) return PKV_ERR_INVALID;
+    if (!cache || !x_dev || !write_positions_dev || !slots_dev || (q_dev && !query_positions_dev)) return PKV_ERR_INVALID;
     st = pkv_check_cache(cache);
     if (st) return st;
     const int W = 2 * layer->R + layer->R_s, WP = pkv_padded_width(W), D = layer->d_model;
@@ -286,7 +286,7 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     if (!fused) {                                        // same results from the separate launches
         st = pkv_cache_write(layer, cache, x_dev, x_dtype, write_positions_dev, nullptr, slots_dev, batch, latent_out_dev,
                              scratch_dev, v_rows_dev, status_dev, stream);
-        if (st) return st;
+        if (st || !q_dev) return st;
         return pkv_absorb(layer, q_dev, query_positions_dev, nullptr, batch, qabs_out_dev, qop_out_dev, stream);
     }
     WriteArgs Wa;
@@ -303,7 +303,8 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     size_t smem = WRITE_SMEM;
     const size_t absorb_smem = pkv_absorb_impl::smem_bytes(layer->head_dim, WP);
     if (absorb_smem > smem) smem = absorb_smem;
-    PKV_CUDA_TRY(x_dtype == PKV_F32 ? launch_prologue<float>(Wa, Aa, batch, smem, (cudaStream_t)stream)
-                                    : launch_prologue<uint16_t>(Wa, Aa, batch, smem, (cudaStream_t)stream));
+    const int absorb_batch = q_dev ? batch : 0;                      // no queries: the write role alone
+    PKV_CUDA_TRY(x_dtype == PKV_F32 ? launch_prologue<float>(Wa, Aa, absorb_batch, smem, (cudaStream_t)stream)
+                                    : launch_prologue<uint16_t>(Wa, Aa, absorb_batch, smem, (cudaStream_t)stream));
     return PKV_OK;
 }

@@ -285,11 +285,12 @@ class PhasorKey:
                                           _lib.current_stream()), "pkv_absorb")
 
     def prologue_step(self, cache: PagedLatentCache, x: torch.Tensor, write_positions: torch.Tensor, slots: torch.Tensor,
-                      q: torch.Tensor, query_positions: torch.Tensor, ws: DecodeWorkspace,
+                      q: Optional[torch.Tensor], query_positions: Optional[torch.Tensor], ws: DecodeWorkspace,
                       v: Optional[torch.Tensor] = None, latent_out: Optional[torch.Tensor] = None,
                       operand: bool = True) -> None:
         """`write_paged` of the newest token of every sequence and `absorb_step` of the step's queries
-        as one launch (same bits as the two calls)."""
+        as one launch (same bits as the two calls). `q=None`: the write alone (the queries then go to
+        `attend_q_step`)."""
         L = self._layer()
         x = self._x(x)
         if v is not None:
@@ -300,6 +301,28 @@ class PhasorKey:
                                                    _lib.ptr(getattr(ws, "wscratch", None)), _lib.ptr(ws.qabs),
                                                    _lib.ptr(ws.qop) if operand else None, _lib.ptr(self._dev["status"]),
                                                    _lib.current_stream()), "pkv_decode_prologue")
+
+    def attend_q_step(self, cache: PagedLatentCache, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace,
+                      scores_only: bool = False, scores_out: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None, packed_out: Optional[torch.Tensor] = None,
+                      early: bool = False, tail_written: bool = False, query_ready: bool = False) -> None:
+        """`attend_step` on RAW queries q [B, H, d] fp32 at `positions` [B]: the attention kernel absorbs them
+        itself (no `absorb_step`, same bits). `early`: the launch enqueued just before writes nothing this
+        kernel reads except, with `tail_written`, rows of each sequence's last page (a write of the newest
+        token) and, unless `query_ready`, the queries."""
+        L = self._layer()
+        flags = _lib.ATTN_SCORES_ONLY if scores_only else 0
+        if early:
+            flags |= _lib.ATTN_EARLY_STREAM | (_lib.ATTN_TAIL_WRITTEN if tail_written else 0) | \
+                (_lib.ATTN_QUERY_READY if query_ready else 0)
+        if packed_out is not None:
+            out, flags = packed_out, flags | _lib.ATTN_PACKED_OUT
+        stride = 0 if scores_out is None else scores_out.shape[-1]
+        _lib.check(_lib.load().pkv_decode_attn_q(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(q), _lib.ptr(positions),
+                                                 _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
+                                                 ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
+                                                 stride, _lib.ptr(ws.status), _lib.ptr(out), _lib.current_stream()),
+                   "pkv_decode_attn_q")
 
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
                     scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,

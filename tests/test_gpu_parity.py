@@ -713,3 +713,64 @@ def test_layer_handle_from_host_arrays(config):
     finally:
         _lib.check(lib.pkv_layer_destroy(handle), "pkv_layer_destroy")
     assert lib.pkv_layer_create(None, ctypes.byref(handle)) != 0
+
+
+@pytest.mark.parametrize("config,gain", [("cfg2", 1.0), ("cfg2", 128.0), ("cfg3", 64.0), ("cfg5", 64.0)])
+def test_attention_absorbs_raw_queries_itself(config, gain):
+    """pkv_decode_attn_q (the attention kernel forms the NVFP4 query operand in shared memory) gives the
+    bits of pkv_absorb followed by pkv_decode_attn, in both kernel modes, and the oracle's result."""
+    sc = Scenario(config, seqlens=(700, 0, 129, 300), gain=gain, pos0=90000)
+    pk, B = sc.pk, sc.B
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    Tmax = max(sc.seqlens)
+    for n_split in (1, 3):
+        ws_a, ws_b = pk.workspace(B, n_split), pk.workspace(B, n_split)
+        Sa = torch.zeros((B, sc.spec.n_q, Tmax), device="cuda")
+        Sb = torch.zeros_like(Sa)
+        pk.absorb_step(q, qpos, ws_a)
+        pk.attend_step(sc.cache, ws_a, scores_out=Sa, out=ws_a.out)
+        pk.attend_q_step(sc.cache, q, qpos, ws_b, scores_out=Sb, out=ws_b.out)
+        torch.cuda.synchronize()
+        assert int(ws_b.status.abs().sum()) == 0
+        assert torch.equal(Sa, Sb) and torch.equal(ws_a.out, ws_b.out) and float(ws_b.out.abs().max()) > 0
+        # scores-only mode: log-sum-exp partials
+        pk.attend_step(sc.cache, ws_a, scores_only=True)
+        pk.attend_q_step(sc.cache, q, qpos, ws_b, scores_only=True)
+        torch.cuda.synchronize()
+        assert torch.equal(ws_a.partials[..., -2:], ws_b.partials[..., -2:])
+    for b, T in enumerate(sc.seqlens):
+        if T:
+            _, S_ref, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b))
+            assert rel(Sb[b, :, :T].cpu(), S_ref) < LOGIT_TOL and rel(ws_b.out[b].cpu(), O_ref) < OUT_TOL
+
+
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_raw_query_attention_behind_a_write_only_prologue(n_split):
+    """The decode step as the bench chains it: the newest token's write alone, then attention on raw queries
+    that starts at once (pages stream early, the query is declared ready) and waits for the write only
+    before it fetches the page being written."""
+    sc = Scenario("cfg2", seqlens=(300, 129, 128, 1), pos0=5000)
+    pk, B = sc.pk, sc.B
+    g = torch.Generator().manual_seed(78)
+    x_new = (synth.make_hidden(g, B, 4096) * 3.0).cuda()
+    v_new = (synth.make_values(g, B, sc.spec.n_kv, sc.spec.head_dim) * 4.0)
+    lens = torch.tensor(sc.seqlens, dtype=torch.int32, device="cuda")
+    slots = sc.cache.slots(torch.arange(B, dtype=torch.int32, device="cuda"), lens - 1)
+    wpos = (lens - 1 + 5000).contiguous()
+    ws = pk.workspace(B, n_split)
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    out_early = torch.zeros((B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
+    for _ in range(3):
+        pk.prologue_step(sc.cache, x_new, wpos, slots, None, None, ws, v=v_new.cuda())
+        pk.attend_q_step(sc.cache, q, qpos, ws, out=out_early, early=True, tail_written=True, query_ready=True)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    out_late = torch.zeros_like(out_early)
+    pk.absorb_step(q, qpos, ws)
+    pk.attend_step(sc.cache, ws, out=out_late)
+    torch.cuda.synchronize()
+    assert torch.equal(out_early, out_late)
+    for b, T in enumerate(sc.seqlens):
+        sc.v[b][T - 1] = v_new[b]
+        _, _, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b))
+        assert rel(out_early[b].cpu(), O_ref) < OUT_TOL
