@@ -5,6 +5,9 @@
  *   - enqueues work on the CUDA stream it is given and returns without synchronising,
  *   - allocates nothing: inputs, outputs and scratch are all owned by the caller,
  *   - returns 0 on success or a negative pkv_status code (never throws, never exits).
+ * (Three calls say otherwise in their own comments: pkv_layer_create / pkv_layer_destroy allocate and free
+ * the device copy of a layer for hosts without a tensor library, pkv_status_read waits for the stream.)
+ * The library keeps per-process state only for kernel attributes it has set: use one device per process.
  * This is the convention of the reference's own FFI, which launches extern "C" kernels on torch's
  * current stream with caller-owned buffers (phasorkv/kernels/cubin.py:34-55,
  * phasorkv/kernels/latent_attn.py:610-629).  "file:line" citations below are paths inside the
