@@ -388,8 +388,9 @@ def run_b200(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V",
         "data": "synthetic",
-        "config": {"workload": "%s: Llama-3.1-8B layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers"
-                   % (args.workload, st.B, st.T, st.W, st.n_kv, st.d, L),
+        "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers"
+                   % (args.workload, "7B multi-head-attention" if st.n_kv == st.n_q else "Llama-3.1-8B", st.B, st.T, st.W,
+                      st.n_kv, st.d, L),
                    "algo": args.algo, "n_split": st.n_split, "parallelism": "batch-parallel x%d" % world,
                    "l2": "inputs larger than L2 (%.2f GB streamed per layer, %.1f GB per step)"
                          % (st.bytes_full() / 1e9, L * st.bytes_full() / 1e9)},
