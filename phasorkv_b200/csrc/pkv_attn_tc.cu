@@ -1,15 +1,21 @@
 // Decode attention on the NVFP4 latent cache with 5th-generation tensor cores.
 //
-// One CTA = one (sequence, token split). Seven warps, each with one job:
-//   warp 0     K producer : bulk-copies latent pages (codes + scales, already in operand layout) to smem
+// One CTA = one (sequence, token split) -- and, with one query head per kv head, one group of 8 heads.
+// Seven warps, each with one job:
+//   warp 0     K producer : TMA tiles of whole latent pages (codes + scales, already in operand layout);
+//                           the page table is fetched 32 entries at a time by the warp
 //   warp 1     V producer : TMA tensor loads of the bf16 V page, one kv head (128 tokens x 128 dims) per stage
-//   warp 2     MMA issuer : S = C . Q'^T as block-scaled NVFP4 tcgen05.mma (tokens on M = 128, the 32 query
-//                           heads on N; the four NVFP4 residual terms of the query are four passes over
-//                           the same cache tile that accumulate in TMEM), scale factors copied
-//                           smem -> TMEM with tcgen05.cp; O^T += V^T . P^T as bf16 tcgen05.mma per kv head
-//   warps 3-6  softmax    : one token row (TMEM lane) per thread; online base-2 softmax whose reference
-//                           maximum only moves when a tile exceeds it by 2^8, P to smem as bf16, and the
-//                           rare rescale of the O accumulators in TMEM
+//   warp 2     MMA issuer : S = C . Q'^T as block-scaled NVFP4 tcgen05.mma, tokens on M = 128 and on N = 128
+//                           the 32 query heads x the four NVFP4 residual terms of the query (one operand
+//                           tile, one pass per K step of 64), scale factors copied smem -> TMEM with
+//                           tcgen05.cp; O^T += V^T . P^T as bf16 tcgen05.mma per kv head (N = 16: hi and lo
+//                           halves of the weights of 8 heads)
+//   warps 3-6  softmax    : one token row (TMEM lane) per thread; adds the four term columns of a head; online
+//                           base-2 softmax whose reference maximum only moves when a tile exceeds it by 2^8,
+//                           P to smem as hi + lo bf16, and the rare rescale of the O accumulators in TMEM
+// Scores-only launches (no V) are a separate instantiation with eleven warps: warp 1 becomes a second MMA
+// issuer and warps 7-10 a second softmax group (even / odd pages). A further instantiation absorbs raw
+// queries itself (pkv_absorb_impl::body_tile) instead of loading the operand.
 // Stages are handed over through mbarriers; every wait is bounded and a give-up is recorded in
 // `status` while all roles unwind, free TMEM and return.
 #include "pkv_absorb.cuh"
