@@ -69,6 +69,30 @@ def test_quantiser_bit_exact_on_oracle_latent(config, T):
     assert np.array_equal(c_codes, ref_codes.numpy()) and np.array_equal(c_scales, ref_scales.numpy())
 
 
+@pytest.mark.parametrize("second", [1e-3, 1.0, 37.5])
+def test_quantiser_bit_exact_over_wide_magnitudes(second):
+    """Blocks whose magnitudes span 2^-24 .. 2^14 around the tensor scale (scale saturation at 448,
+    subnormal and zero block scales), blocks of exact zeros, and values that sit exactly on the E2M1
+    rounding boundaries of their block: codes, scales and dequantised values equal the oracle's bits."""
+    g = torch.Generator().manual_seed(int(second * 1000) + 3)
+    n, W = 768, 256
+    mag = torch.exp2(torch.rand((n, W // 16, 1), generator=g) * 38.0 - 24.0) * second
+    x = (torch.randn((n, W // 16, 16), generator=g) * mag).reshape(n, W)
+    x[::7, 32:48] = 0.0                                                   # zero blocks
+    # boundary rows: block maximum 6 * s with s a power of two, the other entries on the midpoints .25 .75 1.25 ... 5
+    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    for r in range(0, 64):
+        s_blk = second * 2.0 ** (r % 12 - 6)
+        x[r, 64:80] = mids * s_blk
+    ref_codes, ref_scales, ref_hat = po.nvfp4_quantize(x, torch.tensor([second]))
+    xhat, codes, scales = _quantise_and_read(x, float(second))
+    assert torch.equal(codes, po.pack_nibbles(ref_codes))
+    assert torch.equal(scales, ref_scales)
+    assert torch.equal(xhat, ref_hat)
+    c_codes, c_scales, _ = c_oracle.nvfp4_quantize(x.numpy(), float(second))
+    assert np.array_equal(c_codes, ref_codes.numpy()) and np.array_equal(c_scales, ref_scales.numpy())
+
+
 def test_quantiser_empty_and_bad_slots():
     cache = PagedLatentCache(256, 8, 128, 1, 128, "cuda", with_v=False)
     cache.quantize_rows(torch.zeros(0, 256), torch.zeros(0, dtype=torch.int32, device="cuda"), 1.0)
