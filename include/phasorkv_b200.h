@@ -126,6 +126,13 @@ typedef struct pkv_layer_host {
 int pkv_layer_create(const pkv_layer_host_t* host, pkv_layer_t** out);
 int pkv_layer_destroy(pkv_layer_t* layer);
 
+/* Rounding of the E4M3 block scales in every quantising entry point.  0 (default): round to nearest,
+ * the reference's default.  1: round up, so that a block's largest element is never clipped by a scale
+ * that was rounded down -- the reference's PHASORKV_SCALE_UP=1 (phasorkv/quant.py:57,85-88).  Like
+ * there the switch is process-wide; it is taken from the same environment variable at first use unless
+ * this call has set it. */
+int pkv_set_scale_round_up(int32_t on);
+
 /* NVFP4 quantise-and-pack of given fp32 latent rows into the paged cache: the bit-exact
  * counterpart of quantize_nv_block + pack_nibbles (phasorkv/kernels/nvfp4.py:34-55;
  * rounding rules of phasorkv/quant.py:70-89).  rows_dev [n, W]; slots_dev [n]. */

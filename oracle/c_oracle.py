@@ -30,14 +30,14 @@ def _p(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
 
-def nvfp4_quantize(x: np.ndarray, second: float):
+def nvfp4_quantize(x: np.ndarray, second: float, scale_up: bool = False):
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, width = x.shape
     codes = np.empty((rows, width), np.uint8)
     scales = np.empty((rows, width // 16), np.uint8)
     xhat = np.empty((rows, width), np.float32)
-    lib().pkv_ref_nvfp4_quantize(_p(x), ctypes.c_long(rows), ctypes.c_long(width), ctypes.c_float(second),
-                                 _p(codes), _p(scales), _p(xhat))
+    fn = lib().pkv_ref_nvfp4_quantize_scale_up if scale_up else lib().pkv_ref_nvfp4_quantize
+    fn(_p(x), ctypes.c_long(rows), ctypes.c_long(width), ctypes.c_float(second), _p(codes), _p(scales), _p(xhat))
     return codes, scales, xhat
 
 

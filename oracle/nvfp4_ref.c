@@ -43,8 +43,8 @@ static const float LEVEL[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
 
 /* x [rows, width] fp32 (width % 16 == 0) -> codes [rows, width] (one code per byte),
  * scales [rows, width/16] E4M3 bytes, xhat [rows, width] (may be NULL). */
-void pkv_ref_nvfp4_quantize(const float* x, long rows, long width, float second,
-                            uint8_t* codes, uint8_t* scales, float* xhat) {
+static void quantize_impl(const float* x, long rows, long width, float second, int scale_up,
+                          uint8_t* codes, uint8_t* scales, float* xhat) {
     long nb = width / 16;
     for (long r = 0; r < rows; ++r)
         for (long b = 0; b < nb; ++b) {
@@ -57,6 +57,9 @@ void pkv_ref_nvfp4_quantize(const float* x, long rows, long width, float second,
             if (t < 0.0f) t = 0.0f;
             if (t > 448.0f) t = 448.0f;
             uint8_t sb = float_to_e4m3_rne(t);
+            /* quant.py:85-88 (PHASORKV_SCALE_UP=1): a scale rounded below the unclamped ratio moves one E4M3
+             * step up; consecutive non-negative E4M3 values are consecutive bytes, 0x7e = 448 is the largest */
+            if (scale_up && e4m3_to_float(sb) < t1 && sb < 0x7e) sb++;
             volatile float scale = e4m3_to_float(sb) * second;
             scales[r * nb + b] = sb;
             float div = scale < 1e-30f ? 1e-30f : scale;
@@ -75,6 +78,16 @@ void pkv_ref_nvfp4_quantize(const float* x, long rows, long width, float second,
                 if (xhat) { volatile float p = v * scale; xhat[r * width + b * 16 + i] = p; }
             }
         }
+}
+
+void pkv_ref_nvfp4_quantize(const float* x, long rows, long width, float second,
+                            uint8_t* codes, uint8_t* scales, float* xhat) {
+    quantize_impl(x, rows, width, second, 0, codes, scales, xhat);
+}
+
+void pkv_ref_nvfp4_quantize_scale_up(const float* x, long rows, long width, float second,
+                                     uint8_t* codes, uint8_t* scales, float* xhat) {
+    quantize_impl(x, rows, width, second, 1, codes, scales, xhat);
 }
 
 /* inverse: value(code) * (scale * second) */

@@ -70,6 +70,7 @@ SIGNATURES = {
     "pkv_quantize_nvfp4": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_float, c_void_p]),
     "pkv_dequant": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_float, c_void_p, c_void_p]),
     "pkv_status_read": (c_int32, [c_void_p, c_void_p, c_void_p]),
+    "pkv_set_scale_round_up": (c_int32, [c_int32]),
     "pkv_absorb": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_prologue": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

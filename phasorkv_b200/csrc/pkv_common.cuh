@@ -11,6 +11,7 @@
 #define PKV_LOG2E 1.4426950408889634f
 
 extern thread_local int g_pkv_last_cuda_error;
+int pkv_scale_round_up_mode();     // 1: block scales are rounded up (pkv_set_scale_round_up / PHASORKV_SCALE_UP=1)
 
 #define PKV_CUDA_TRY(expr)                                   \
     do {                                                     \
@@ -98,10 +99,14 @@ __device__ __forceinline__ float pkv_e2m1_value(uint32_t code) {
 }
 
 // E4M3 scale byte of a block with the given max magnitude
-__device__ __forceinline__ uint8_t pkv_block_scale_byte(float amax, float second) {
-    float t = __fdiv_rn(__fdiv_rn(amax, 6.0f), second);
-    t = fminf(fmaxf(t, 0.0f), 448.0f);
-    return pkv_float_to_e4m3(t);
+// round_up (PHASORKV_SCALE_UP=1 of the reference, phasorkv/quant.py:57,85-88): a scale that round-to-nearest put
+// below the unclamped ratio moves one E4M3 step up, so the block maximum is never clipped. Consecutive
+// non-negative E4M3 values are consecutive bytes; 0x7e (448) is the largest.
+__device__ __forceinline__ uint8_t pkv_block_scale_byte(float amax, float second, bool round_up = false) {
+    const float ratio = __fdiv_rn(__fdiv_rn(amax, 6.0f), second);
+    uint8_t b = pkv_float_to_e4m3(fminf(fmaxf(ratio, 0.0f), 448.0f));
+    if (round_up && pkv_e4m3_to_float(b) < ratio && b < 0x7e) ++b;
+    return b;
 }
 
 // E2M1 code of x under `scale` (= e4m3 * second): midpoints are compared with ">" so that an
@@ -115,11 +120,12 @@ __device__ __forceinline__ uint32_t pkv_e2m1_code(float x, float scale) {
 }
 
 // quantise 16 consecutive values; returns the 8 packed code bytes (low nibble = even column)
-__device__ __forceinline__ uint2 pkv_quantize_block16(const float (&v)[16], float second, uint8_t& scale_byte) {
+__device__ __forceinline__ uint2 pkv_quantize_block16(const float (&v)[16], float second, uint8_t& scale_byte,
+                                                      bool round_up = false) {
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    scale_byte = pkv_block_scale_byte(amax, second);
+    scale_byte = pkv_block_scale_byte(amax, second, round_up);
     float scale = __fmul_rn(pkv_e4m3_to_float(scale_byte), second);
     uint32_t lo = 0u, hi = 0u;
 #pragma unroll

@@ -1,6 +1,8 @@
 // NVFP4 quantise-and-pack of fp32 latent rows into cache pages, V row store, and read-back.
 #include "pkv_common.cuh"
 
+#include <cstdlib>
+
 thread_local int g_pkv_last_cuda_error = 0;
 
 extern "C" int pkv_abi_version(void) { return 1; }
@@ -35,6 +37,23 @@ extern "C" int64_t pkv_v_page_bytes(int32_t n_kv, int32_t head_dim) {
     return (int64_t)PKV_PAGE_TOKENS * n_kv * head_dim * 2;
 }
 
+// Rounding of the E4M3 block scales: process-wide like the reference's switch, which is read once from the
+// environment when phasorkv.quant is imported (phasorkv/quant.py:57). -1 = not decided yet.
+static int g_scale_round_up = -1;
+
+int pkv_scale_round_up_mode() {
+    if (g_scale_round_up < 0) {
+        const char* e = getenv("PHASORKV_SCALE_UP");
+        g_scale_round_up = (e && e[0] == '1' && e[1] == 0) ? 1 : 0;
+    }
+    return g_scale_round_up;
+}
+
+extern "C" int pkv_set_scale_round_up(int32_t on) {
+    g_scale_round_up = on ? 1 : 0;
+    return PKV_OK;
+}
+
 int pkv_check_cache(const pkv_cache_t* c) {
     if (!c || !c->latent_dev || c->n_pages <= 0) return PKV_ERR_INVALID;
     if (c->W <= 0 || c->W > PKV_MAX_WIDTH || (c->W % 16)) return PKV_ERR_UNSUPPORTED;
@@ -46,7 +65,7 @@ int pkv_check_cache(const pkv_cache_t* c) {
 // are written as zero codes with a zero scale
 __global__ void pkv_quantize_rows_kernel(uint8_t* __restrict__ latent, const float* __restrict__ rows,
                                          const int32_t* __restrict__ slots, int n_tokens, int W, int n_pages,
-                                         float second) {
+                                         float second, int scale_up) {
     const int Wp = pkv_padded_width(W), RB = Wp / 2, nb = Wp / 16;
     const int page_bytes = pkv_page_bytes(W), codes_bytes = pkv_codes_bytes(W);
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -66,7 +85,7 @@ __global__ void pkv_quantize_rows_kernel(uint8_t* __restrict__ latent, const flo
             float4 f = src[i];
             v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
         }
-        packed = pkv_quantize_block16(v, second, sb);
+        packed = pkv_quantize_block16(v, second, sb, scale_up != 0);
     }
     *reinterpret_cast<uint2*>(page + pkv_code_offset(row, j * 8, RB)) = packed;
     page[codes_bytes + pkv_scale_offset(row, j)] = sb;
@@ -81,7 +100,7 @@ extern "C" int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev
     if (!rows_dev || !slots_dev || (((uintptr_t)rows_dev) & 15u)) return PKV_ERR_INVALID;
     long n = (long)n_tokens * (pkv_padded_width(cache->W) / 16);
     pkv_quantize_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        cache->latent_dev, rows_dev, slots_dev, n_tokens, cache->W, cache->n_pages, second);
+        cache->latent_dev, rows_dev, slots_dev, n_tokens, cache->W, cache->n_pages, second, pkv_scale_round_up_mode());
     PKV_LAUNCH_CHECK();
     return PKV_OK;
 }

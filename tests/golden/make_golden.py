@@ -5,6 +5,7 @@ produced .npz files are committed, this script is not needed to run the tests. E
 sizes are small so the fixtures stay a few hundred KB.
 
   PHASORKV_REFERENCE=<checkout of PhasorKV> python tests/golden/make_golden.py
+  PHASORKV_SCALE_UP=1 PHASORKV_REFERENCE=<checkout> python tests/golden/make_golden.py   # nvfp4_cases_scale_up.npz
 """
 import os
 import sys
@@ -80,6 +81,11 @@ def nvfp4_cases():
     var = torch.rand(64, generator=g) * 3.0
     out["static_var"] = var.numpy()
     out["static_second"] = quant.nv_static_second(var, "nvfp4").numpy()
+    if quant.SCALE_UP:                                        # the reference reads PHASORKV_SCALE_UP once, at import
+        keep = ("x", "second", "codes", "scales", "xhat", "packed")
+        np.savez_compressed(os.path.join(HERE, "nvfp4_cases_scale_up.npz"), **{k: out[k] for k in keep})
+        print("nvfp4_cases_scale_up", x.shape)
+        return
     np.savez_compressed(os.path.join(HERE, "nvfp4_cases.npz"), **out)
     print("nvfp4_cases", x.shape)
 
@@ -206,5 +212,6 @@ def phasorkey_factorized():
 if __name__ == "__main__":
     torch.set_num_threads(4)
     nvfp4_cases()
-    phasorkey_injected()
-    phasorkey_factorized()
+    if not quant.SCALE_UP:                                    # PHASORKV_SCALE_UP=1: only the quantiser vectors differ
+        phasorkey_injected()
+        phasorkey_factorized()

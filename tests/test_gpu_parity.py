@@ -69,6 +69,44 @@ def test_quantiser_bit_exact_on_oracle_latent(config, T):
     assert np.array_equal(c_codes, ref_codes.numpy()) and np.array_equal(c_scales, ref_scales.numpy())
 
 
+def test_quantiser_scale_round_up_matches_reference_golden_vectors():
+    """The reference's PHASORKV_SCALE_UP=1 mode (block scales rounded up): bit-exact against vectors it
+    produced with that switch, through the quantiser entry point and through the fused write kernels."""
+    from phasorkv_b200 import _lib
+    g = _golden("nvfp4_cases_scale_up.npz")
+    x = torch.from_numpy(g["x"])
+    lib = _lib.load()
+    try:
+        _lib.check(lib.pkv_set_scale_round_up(1), "pkv_set_scale_round_up")
+        xhat, codes, scales = _quantise_and_read(x, float(g["second"][0]))
+        assert np.array_equal(codes.numpy(), g["packed"])
+        assert np.array_equal(scales.numpy(), g["scales"])
+        assert np.array_equal(xhat.numpy(), g["xhat"])
+        # the write kernels (CUDA-core, tensor-core, decode-time, one-launch prologue) round their scales the same way:
+        # each stores what the quantiser entry point stores for the rows the kernel itself reports
+        sc = Scenario("cfg2", seqlens=(200,), pos0=100)
+        for dt, n in ((torch.float32, 200), (torch.bfloat16, 200), (torch.bfloat16, 16)):
+            xs = sc.x[0][:n].cuda().to(dt)
+            pos = sc.pos[0][:n].to(torch.int32).cuda()
+            slots = sc.slots_of(0)[:n]
+            rows = torch.empty((n, sc.spec.cache_width), device="cuda")
+            c1, c2 = sc.pk.new_cache(1, 200), sc.pk.new_cache(1, 200)
+            sc.pk.write_paged(c1, xs, pos, slots, latent_out=rows, scratch=sc.pk.write_scratch(n) if n <= 64 else None)
+            c2.quantize_rows(rows, slots, sc.second)
+            assert torch.equal(c1.latent, c2.latent), (dt, n)
+        ws = sc.pk.workspace(16, 1)
+        c1, c2 = sc.pk.new_cache(1, 200), sc.pk.new_cache(1, 200)
+        sc.pk.prologue_step(c1, xs, pos, slots, None, None, ws, latent_out=rows)
+        c2.quantize_rows(rows, slots, sc.second)
+        assert torch.equal(c1.latent, c2.latent)
+        up = c2.latent.clone()
+    finally:
+        _lib.check(lib.pkv_set_scale_round_up(0), "pkv_set_scale_round_up")
+    c3 = sc.pk.new_cache(1, 200)
+    c3.quantize_rows(rows, slots, sc.second)
+    assert not torch.equal(c3.latent, up)                      # the default (round to nearest) stores other scales
+
+
 @pytest.mark.parametrize("second", [1e-3, 1.0, 37.5])
 def test_quantiser_bit_exact_over_wide_magnitudes(second):
     """Blocks whose magnitudes span 2^-24 .. 2^14 around the tensor scale (scale saturation at 448,

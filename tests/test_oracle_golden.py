@@ -35,6 +35,25 @@ def test_nvfp4_c_oracle_bit_exact():
     assert np.array_equal(c_oracle.nvfp4_dequantize(codes, scales, float(g["second"][0])), g["xhat"])
 
 
+def test_nvfp4_scale_round_up_oracles_bit_exact():
+    """PHASORKV_SCALE_UP=1 of the reference (quant.py:57,85-88): block scales rounded up. Both oracles
+    against vectors the reference produced with that switch, and the two modes do differ."""
+    g, g0 = _load("nvfp4_cases_scale_up.npz"), _load("nvfp4_cases.npz")
+    assert np.array_equal(g["x"], g0["x"]) and not np.array_equal(g["scales"], g0["scales"])
+    x, second = torch.from_numpy(g["x"]), torch.from_numpy(g["second"])
+    codes, scales, xhat = po.nvfp4_quantize(x, second, scale_up=True)
+    assert np.array_equal(codes.numpy(), g["codes"])
+    assert np.array_equal(scales.numpy(), g["scales"])
+    assert np.array_equal(xhat.numpy(), g["xhat"])
+    c_codes, c_scales, c_xhat = c_oracle.nvfp4_quantize(g["x"], float(g["second"][0]), scale_up=True)
+    assert np.array_equal(c_codes, g["codes"]) and np.array_equal(c_scales, g["scales"]) and np.array_equal(c_xhat, g["xhat"])
+    # rounded-up scales never clip the block maximum: |x| <= 6 * scale wherever the scale is not saturated
+    sc = torch.from_numpy(g["scales"]).view(torch.float8_e4m3fn).float() * second
+    amax = x.reshape(x.shape[0], -1, 16).abs().amax(-1)
+    free = torch.from_numpy(g["scales"]) != 0x7E
+    assert bool((amax[free] <= 6.0 * sc[free] * (1 + 1e-6)).all())
+
+
 def test_nvfp4_known_behaviours():
     """Ties go to the lower magnitude, no signed zero, zero block -> scale byte 0, saturation."""
     g = _load("nvfp4_cases.npz")
