@@ -163,8 +163,8 @@ class Stack:
                 for pk, cache in zip(self.layers, self.caches):
                     slots = cache.slots(seq, lp)
                     pk.write_paged(cache, x, lp, slots)
-                    cache.v.view(-1, self.n_kv * self.d)[slots.long()] = torch.randn(
-                        (n, self.n_kv * self.d), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+                    cache.set_v_rows(slots, torch.randn((n, self.n_kv * self.d), generator=g, device=device,
+                                                        dtype=torch.float32))
         for cache in self.caches:
             cache.seqlens.fill_(self.T)
         self.n_split = n_split or pk0.default_splits(self.B, self.T, self.simt)

@@ -84,7 +84,9 @@ typedef struct pkv_layer {
  *             of a K-major tcgen05 operand, so a page is copied to shared memory verbatim.
  *     scales: after the codes, one 512-byte block per 64 columns; the E4M3 scale of row r,
  *             16-column block j sits at `(j/4)*512 + (r%32)*16 + (r/32)*4 + j%4`.
- *   V page: [128][n_kv][head_dim] bf16, row-major.
+ *   V page: [n_kv][128][head_dim] bf16 (head-major: the 128 x head_dim tile of one kv head is one
+ *           contiguous block); the value of (slot, kv head g, dim) sits at element
+ *           ((page * n_kv + g) * 128 + row) * head_dim + dim.  pkv_v_write / pkv_cache_write place rows there.
  * A token's place is its *slot*: page_index * 128 + row. */
 typedef struct pkv_cache {
     uint8_t* latent_dev;

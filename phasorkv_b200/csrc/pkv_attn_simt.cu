@@ -140,18 +140,18 @@ __global__ void __launch_bounds__(NT) pkv_attn_simt_kernel(
 #pragma unroll
                     for (int e = 0; e < EPT; ++e) acc[r][e] *= c;
                 }
-                const uint16_t* vrow = vpool + ((size_t)pidx * PKV_PAGE_TOKENS + sub * TT) * (n_kv * DH) + elem0;
+                const uint16_t* vrow = vpool + (((size_t)pidx * n_kv + g) * PKV_PAGE_TOKENS + sub * TT) * DH + elem0 % DH;
                 const int nt = min(TT, T - t0);
 #pragma unroll 4
                 for (int t = 0; t < nt; ++t) {
                     float v[EPT];
                     if constexpr (EPT == 2) {
-                        uint32_t u = *reinterpret_cast<const uint32_t*>(vrow + (size_t)t * n_kv * DH);
+                        uint32_t u = *reinterpret_cast<const uint32_t*>(vrow + (size_t)t * DH);
                         v[0] = pkv_bf16_bits_to_float(u & 0xffffu); v[1] = pkv_bf16_bits_to_float(u >> 16);
                     } else {
 #pragma unroll
                         for (int e4 = 0; e4 < EPT / 4; ++e4) {
-                            uint2 u = *reinterpret_cast<const uint2*>(vrow + (size_t)t * n_kv * DH + e4 * 4);
+                            uint2 u = *reinterpret_cast<const uint2*>(vrow + (size_t)t * DH + e4 * 4);
                             v[e4 * 4 + 0] = pkv_bf16_bits_to_float(u.x & 0xffffu); v[e4 * 4 + 1] = pkv_bf16_bits_to_float(u.x >> 16);
                             v[e4 * 4 + 2] = pkv_bf16_bits_to_float(u.y & 0xffffu); v[e4 * 4 + 3] = pkv_bf16_bits_to_float(u.y >> 16);
                         }

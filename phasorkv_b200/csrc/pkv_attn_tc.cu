@@ -243,8 +243,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                                 if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }
                                 uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
                                 mbar_arrive_expect_tx(&X->v_full[s], V_STAGE_BYTES);
-                                tma_load_2d(dst, &vmap, (g_base + g) * DH, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
-                                tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, (g_base + g) * DH + 64, pidx * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                tma_load_2d(dst, &vmap, 0, (pidx * (NQ / REP) + g_base + g) * PKV_PAGE_TOKENS, &X->v_full[s]);
+                                tma_load_2d(dst + V_STAGE_BYTES / 2, &vmap, 64, (pidx * (NQ / REP) + g_base + g) * PKV_PAGE_TOKENS, &X->v_full[s]);
                                 issued = j + 1;
                             }
                         }
@@ -548,9 +548,10 @@ int init_encoder() {
 }
 
 int encode_v_map(CUtensorMap* map, const pkv_cache_t* C) {
-    // V pool as a 2-D bf16 tensor [n_pages * 128 tokens, n_kv * head_dim]; box = 64 dims x 128 tokens, 128-byte swizzle
-    cuuint64_t dims[2] = {(cuuint64_t)C->n_kv * C->head_dim, (cuuint64_t)C->n_pages * PKV_PAGE_TOKENS};
-    cuuint64_t strides[1] = {(cuuint64_t)C->n_kv * C->head_dim * 2};
+    // V pool as a 2-D bf16 tensor [n_pages * n_kv * 128 tokens, head_dim] (pages are head-major: the tile of one kv head
+    // is one contiguous block); box = 64 dims x 128 tokens, 128-byte swizzle
+    cuuint64_t dims[2] = {(cuuint64_t)C->head_dim, (cuuint64_t)C->n_pages * C->n_kv * PKV_PAGE_TOKENS};
+    cuuint64_t strides[1] = {(cuuint64_t)C->head_dim * 2};
     cuuint32_t box[2] = {64, PKV_PAGE_TOKENS};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C->v_dev, dims, strides, box, estr,

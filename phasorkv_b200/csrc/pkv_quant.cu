@@ -107,13 +107,13 @@ extern "C" int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev
 
 // V rows: 16-byte vectors, one thread each
 __global__ void pkv_v_write_kernel(uint4* __restrict__ vpool, const uint4* __restrict__ v,
-                                   const int32_t* __restrict__ slots, int n_tokens, int vec_per_row, int n_pages) {
+                                   const int32_t* __restrict__ slots, int n_tokens, int vec_per_row, int n_kv, int n_pages) {
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)n_tokens * vec_per_row) return;
     int tok = (int)(idx / vec_per_row), c = (int)(idx % vec_per_row);
     int slot = slots[tok];
     if (slot < 0 || slot >= n_pages * PKV_PAGE_TOKENS) return;
-    vpool[(size_t)slot * vec_per_row + c] = v[(size_t)tok * vec_per_row + c];
+    vpool[pkv_v_vec_index(slot, c, n_kv, vec_per_row / n_kv)] = v[(size_t)tok * vec_per_row + c];
 }
 
 extern "C" int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slots_dev,
@@ -122,12 +122,12 @@ extern "C" int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const in
     if (n_tokens == 0) return PKV_OK;
     if (!v_dev || !slots_dev) return PKV_ERR_INVALID;
     int row_bytes = cache->n_kv * cache->head_dim * 2;
-    if (row_bytes <= 0 || (row_bytes % 16) || (((uintptr_t)v_dev | (uintptr_t)cache->v_dev) & 15u))
+    if (row_bytes <= 0 || (cache->head_dim % 8) || (((uintptr_t)v_dev | (uintptr_t)cache->v_dev) & 15u))
         return PKV_ERR_INVALID;
     if (n_tokens == 0) return PKV_OK;
     long n = (long)n_tokens * (row_bytes / 16);
     pkv_v_write_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (uint4*)cache->v_dev, (const uint4*)v_dev, slots_dev, n_tokens, row_bytes / 16, cache->n_pages);
+        (uint4*)cache->v_dev, (const uint4*)v_dev, slots_dev, n_tokens, row_bytes / 16, cache->n_kv, cache->n_pages);
     PKV_LAUNCH_CHECK();
     return PKV_OK;
 }

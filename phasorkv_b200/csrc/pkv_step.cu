@@ -51,7 +51,7 @@ struct WriteArgs {
     float* latent_out;            // [n_tokens][W] or null
     const uint4* v_rows;          // [n_tokens][v_vecs] or null
     uint4* v_pool;
-    int v_vecs;
+    int v_vecs, n_kv;
     int n_tiles;                  // grid rows of the write role: R / 16 pair tiles, then (WP - 2R) / 16 plain tiles
 };
 
@@ -117,7 +117,7 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                         if (tok >= n_tokens) break;
                         const int slot = A.slots[tok];
                         if (slot < 0 || slot >= A.n_pages * PKV_PAGE_TOKENS) continue;
-                        A.v_pool[(size_t)slot * A.v_vecs + i % A.v_vecs] = A.v_rows[(size_t)tok * A.v_vecs + i % A.v_vecs];
+                        A.v_pool[pkv_v_vec_index(slot, i % A.v_vecs, A.n_kv, A.v_vecs / A.n_kv)] = A.v_rows[(size_t)tok * A.v_vecs + i % A.v_vecs];
                     }
                 }
                 if (pair && tid < TPR * PC && my_tok < n_tokens) {
@@ -299,6 +299,7 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     Wa.v_rows = with_v ? reinterpret_cast<const uint4*>(v_rows_dev) : nullptr;
     Wa.v_pool = with_v ? reinterpret_cast<uint4*>(cache->v_dev) : nullptr;
     Wa.v_vecs = with_v ? cache->n_kv * cache->head_dim * 2 / 16 : 0;
+    Wa.n_kv = cache->n_kv;
     Wa.n_tiles = layer->R / PC + (WP - 2 * layer->R) / PC;
     const pkv_absorb_impl::Args Aa = pkv_absorb_impl::make_args(layer, q_dev, query_positions_dev, nullptr, qabs_out_dev, qop_out_dev);
     size_t smem = WRITE_SMEM;

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
     const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots, int W, int WP, int R,
     const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, float second, int scale_up,
     uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, const uint4* __restrict__ v_rows,
-    uint4* __restrict__ v_pool, int v_vecs) {
+    uint4* __restrict__ v_pool, int v_vecs, int n_kv) {
     __shared__ float row[PKV_MAX_WIDTH];
     const int tok = blockIdx.x, tid = threadIdx.x;
     pkv_grid_launch_dependents();
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
     const int slot = slots[tok];
     if (slot < 0 || slot >= n_pages * PKV_PAGE_TOKENS) return;
     if (v_rows)
-        for (int i = tid; i < v_vecs; i += 256) v_pool[(size_t)slot * v_vecs + i] = v_rows[(size_t)tok * v_vecs + i];
+        for (int i = tid; i < v_vecs; i += 256) v_pool[pkv_v_vec_index(slot, i, n_kv, v_vecs / n_kv)] = v_rows[(size_t)tok * v_vecs + i];
     const int NB = WP / 16, RB = WP / 2;
     if (tid < NB) {
         float v[16];
@@ -338,7 +338,7 @@ int launch_write_small(const pkv_layer_t* L, const pkv_cache_t* C, const void* x
                                     (const float2*)ph, L->head_dim / 2, slots, W, WP, L->R, L->freq_dev, L->inv_freq_dev,
                                     L->attn_scale, L->second, pkv_scale_round_up_mode(), C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out,
                                     with_v ? (const uint4*)v_rows : nullptr, with_v ? (uint4*)C->v_dev : nullptr,
-                                    with_v ? C->n_kv * C->head_dim * 2 / 16 : 0));
+                                    with_v ? C->n_kv * C->head_dim * 2 / 16 : 0, with_v ? C->n_kv : 1));
     return PKV_OK;
 }
 

@@ -51,7 +51,8 @@ class PagedLatentCache:
             raise _lib.PhasorKVError(f"latent width {W} is not supported (multiple of 16, <= {_lib.MAX_WIDTH})")
         self.device = torch.device(device)
         self.latent = _aligned_bytes(self.n_pages * self.page_bytes, self.device)
-        self.v = (torch.zeros((self.n_pages * PAGE_TOKENS, n_kv, head_dim), dtype=torch.bfloat16, device=self.device)
+        # V pages are head-major: the tile of one (page, kv head) is one contiguous block of 128 x head_dim values
+        self.v = (torch.zeros((self.n_pages, n_kv, PAGE_TOKENS, head_dim), dtype=torch.bfloat16, device=self.device)
                   if with_v else None)
         # contiguous default mapping: sequence b owns pages [b*max_pages, (b+1)*max_pages)
         pt = torch.arange(batch * self.max_pages, dtype=torch.int32).reshape(batch, self.max_pages)
@@ -64,6 +65,16 @@ class PagedLatentCache:
         """Slot (page * 128 + row) of token `local_pos` of sequence `seq`; int32 tensors on the device."""
         page = self.page_table[seq.long(), (local_pos // PAGE_TOKENS).long()]
         return (page * PAGE_TOKENS + (local_pos % PAGE_TOKENS).to(torch.int32)).to(torch.int32)
+
+    def v_rows(self, slots: torch.Tensor) -> torch.Tensor:
+        """Value rows [n, n_kv, head_dim] stored at `slots` (page * 128 + row)."""
+        s = slots.long()
+        return self.v[s // PAGE_TOKENS, :, s % PAGE_TOKENS, :]
+
+    def set_v_rows(self, slots: torch.Tensor, rows: torch.Tensor) -> None:
+        """Store value rows [n, n_kv, head_dim] (or [n, n_kv * head_dim]) at `slots` with torch indexing."""
+        s = slots.long()
+        self.v[s // PAGE_TOKENS, :, s % PAGE_TOKENS, :] = rows.reshape(-1, self.v.shape[1], self.v.shape[3]).to(self.v.dtype)
 
     def write_v(self, v: torch.Tensor, slots: torch.Tensor) -> None:
         """bf16 value rows [n, n_kv, head_dim] into the V pages."""

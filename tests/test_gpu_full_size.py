@@ -102,7 +102,7 @@ def test_full_size_properties(config, B, T, tc):
     ph = po.rope_phasors(spec.inv_freq, qpos[b:b + 1].cpu(), spec.attn_scale)
     qa = opk.absorb(q[b].cpu()[:, None, :], ph)[:, 0]
     S_ref = opk.scores(qa, deq.cpu())
-    O_ref = po.attend(S_ref, cache.v[slots.long()].cpu(), spec.n_kv, spec.head_dim)
+    O_ref = po.attend(S_ref, cache.v_rows(slots).cpu(), spec.n_kv, spec.head_dim)
     ws = pk.workspace(B, 9)
     S = torch.zeros((B, pk.n_q, T), device="cuda")
     pk.absorb_step(q, qpos, ws, operand=not simt_only)

@@ -314,7 +314,7 @@ def test_decode_time_write_path(config, n):
     slots = sc.slots_of(0)
     sc.pk.write_paged(cache2, sc.x[0].cuda(), sc.pos[0].to(torch.int32).cuda(), slots, v=sc.v[0].cuda(), latent_out=out,
                       scratch=scratch)
-    assert torch.equal(cache2.v[slots.long()].cpu(), sc.v[0])
+    assert torch.equal(cache2.v_rows(slots).cpu(), sc.v[0])
     assert rel(out.cpu(), sc.rows_ref[0]) < 5e-6
     a, ca, sa = sc.cache.read(slots, sc.second)
     b, cb, sb = cache2.read(slots, sc.second)
@@ -355,7 +355,7 @@ def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
     assert float(outs[1].abs().max()) > 0
     assert torch.equal(caches[0].latent, caches[1].latent)
     assert torch.equal(caches[0].v, caches[1].v)
-    assert torch.equal(caches[1].v[slots.long()].cpu(), sc.v[0])
+    assert torch.equal(caches[1].v_rows(slots).cpu(), sc.v[0])
     assert torch.equal(wss[0].qabs, wss[1].qabs) and float(wss[1].qabs.abs().max()) > 0
     assert torch.equal(wss[0].qop, wss[1].qop) and int(wss[1].qop.max()) > 0
 
