@@ -7,7 +7,11 @@
  *   - returns 0 on success or a negative pkv_status code (never throws, never exits).
  * (Three calls say otherwise in their own comments: pkv_layer_create / pkv_layer_destroy allocate and free
  * the device copy of a layer for hosts without a tensor library, pkv_status_read waits for the stream.)
- * The library keeps per-process state only for kernel attributes it has set: use one device per process.
+ * Process-wide state, all of it stated here: (1) the shared-memory opt-in of each kernel is remembered per
+ * device, so one process may drive several GPUs (make the device current before the call, as for any
+ * CUDA stream); (2) the rounding mode of pkv_set_scale_round_up is one switch for the whole process;
+ * (3) pkv_decode_attn_noalloc keeps the address of its built-in scratch per device.  None of it is
+ * guarded by a lock: two host threads that race on (1) or (3) store the same value.
  * This is the convention of the reference's own FFI, which launches extern "C" kernels on torch's
  * current stream with caller-owned buffers (phasorkv/kernels/cubin.py:34-55,
  * phasorkv/kernels/latent_attn.py:610-629).  "file:line" citations below are paths inside the
@@ -40,7 +44,7 @@ enum pkv_status {
     PKV_ERR_ARCH = -4                /* the current device is not sm_100 */
 };
 
-enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1 };
+enum pkv_dtype { PKV_F32 = 0, PKV_BF16 = 1, PKV_F64 = 2 };    /* PKV_F64: pkv_scores_exact only */
 
 /* flags of pkv_decode_attn */
 #define PKV_ATTN_SCORES_ONLY 1u      /* K path only: logits and log-sum-exp, V is not read */
@@ -197,6 +201,27 @@ int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* posi
                const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, void* stream);
 int64_t pkv_query_operand_bytes(int32_t W);
 
+/* The reference's calls in the precision of their arguments, without quantisation -- what host code written
+ * against phasorkv.latent.PhasorKey and its exactness statement (README.md:75-77) expect.  Plain CUDA-core
+ * kernels, not the decode path.
+ *   pkv_scores_exact    PhasorKey.scores (phasorkv/latent.py:85-88): out [n_query_rows, n_tokens] =
+ *                       q_abs [n_query_rows, W] . rows [n_tokens, W]^T, all of `dtype` PKV_F32 or PKV_F64.
+ *   pkv_write_rows_f64  PhasorKey.write for fp64 x (phasorkv/latent.py:63-64 keeps fp64): Bw_dev [2R+R_s, D]
+ *                       (rows Re B | Im B | B_s), x_dev [n, D], phasors_dev [n, half_dim] complex128
+ *                       (re, im interleaved) -> rows_out_dev [n, 2R+R_s].  fp32 / bf16 x go to pkv_cache_write.
+ *   pkv_absorb_rows_f64 PhasorKey.absorb for fp64 q (phasorkv/latent.py:72-83): q_dev [n_positions, n_q,
+ *                       head_dim], phasors_dev [n_positions, head_dim/2] complex128 -> out_dev
+ *                       [n_positions, n_q, 2R+R_s]; A_re/A_im [n_kv, R], A_s [n_kv, 2*n_slow, R_s]. */
+int pkv_scores_exact(const void* q_abs_dev, const void* rows_dev, int32_t n_query_rows, int32_t n_tokens, int32_t W,
+                     int32_t dtype, void* out_dev, void* stream);
+int pkv_write_rows_f64(const double* Bw_dev, const int32_t* freq_dev, int32_t d_model, int32_t R, int32_t R_s,
+                       int32_t half_dim, const double* x_dev, const double* phasors_dev, int32_t n_tokens,
+                       double* rows_out_dev, void* stream);
+int pkv_absorb_rows_f64(const double* A_re_dev, const double* A_im_dev, const double* A_s_dev, const int32_t* freq_dev,
+                        const int32_t* slow_dev, int32_t n_q, int32_t n_kv, int32_t head_dim, int32_t R, int32_t R_s,
+                        int32_t n_slow, const double* q_dev, const double* phasors_dev, int32_t n_positions,
+                        double* out_dev, void* stream);
+
 /* The two calls a decode step makes before it attends -- pkv_cache_write of the newest token of each
  * of the `batch` sequences (x_dev [batch, d_model], write_positions_dev / slots_dev / v_rows_dev
  * [batch]) and pkv_absorb of the step's queries (q_dev at query_positions_dev [batch]) -- as ONE
@@ -311,7 +336,7 @@ int pkv_merge_exchange(const pkv_exchange_t* x, const float* parts_dev, int64_t 
  * of PKV_NOALLOC_MAX_PARTS * 32 * 130 floats (about 5.3 MB) in the device memory of every GPU that
  * loads the library, held until the process exits.
  *   - same inputs as pkv_decode_attn with the tensor-core kernel (qop_dev is the operand blob of
- *     pkv_absorb; 32 query heads, head_dim 128, 4 or 8 query heads per kv head) and the V cache
+ *     pkv_absorb; 32 query heads, head_dim 128, 1, 4 or 8 query heads per kv head) and the V cache
  *     present; the result is the normalised output out_dev [B, n_q, head_dim], as pkv_merge gives
  *   - batch * n_split must not exceed PKV_NOALLOC_MAX_PARTS; larger requests return
  *     PKV_ERR_UNSUPPORTED and do nothing
@@ -320,7 +345,10 @@ int pkv_merge_exchange(const pkv_exchange_t* x, const float* parts_dev, int64_t 
  *   - all calls on one GPU share the one array: two calls whose kernels may overlap on the GPU
  *     (different streams, different threads) race on it.  Issue them on one stream or serialise
  *     them.  Nothing in the array needs clearing between calls: each call overwrites every slot it
- *     later reads. */
+ *     later reads -- also when a CTA of the attention launch gives up (bad page index, a bounded wait
+ *     that ran out): it then stores the neutral triple (o = 0, m = -inf, l = 0) in its slot, status_dev
+ *     says what happened, and out_dev is then NOT the attention output (rows whose splits all gave up
+ *     are zero).  Pass status_dev and check it when the inputs are not trusted. */
 int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* qop_dev,
                             const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
                             int32_t batch, int32_t n_split, float* out_dev, int32_t* status_dev, void* stream);

@@ -15,7 +15,7 @@ PAGE_TOKENS = 128
 MAX_WIDTH = 256
 QUERY_TERMS = 4
 NOALLOC_MAX_PARTS = 320
-F32, BF16 = 0, 1
+F32, BF16, F64 = 0, 1, 2
 ATTN_SCORES_ONLY, ATTN_SIMT, ATTN_PACKED_OUT, ATTN_EARLY_STREAM, ATTN_TAIL_WRITTEN, ATTN_QUERY_READY = 1, 2, 4, 8, 16, 32
 EXCHANGE_PUSH, EXCHANGE_MERGE = 1, 2
 
@@ -87,6 +87,11 @@ SIGNATURES = {
                                     c_void_p]),
     "pkv_merge_exact": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
                                   c_void_p]),
+    "pkv_scores_exact": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
+    "pkv_write_rows_f64": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_int32,
+                                     c_void_p, c_void_p]),
+    "pkv_absorb_rows_f64": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                      c_int32, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }

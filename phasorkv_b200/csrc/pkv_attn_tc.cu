@@ -530,6 +530,12 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     // ---- teardown: everyone meets, tensor memory goes back
     tc_fence_before_sync();
     __syncthreads();
+    if (X->abort_flag) {
+        // A role gave up (status says why). The slot of this CTA gets the neutral triple, so that a merge
+        // enqueued behind this launch never folds in what an earlier call left in the partials.
+        for (int i = tid; i < HPC * (DH + 2); i += blockDim.x)
+            part[h_base * (DH + 2) + i] = (i % (DH + 2)) == DH ? -INFINITY : 0.0f;
+    }
     if (warp == 2) tmem_dealloc(tb, TM_COLS);
 }
 
@@ -581,11 +587,8 @@ int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cach
               long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
     auto kern = pkv_attn_tc_kernel<WP, REP, WV, INLQ>;
     constexpr int smem = Cfg<WP>::SMEM;
-    static bool attr_done = false;                                  // once per instantiation
-    if (!attr_done) {
-        PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
-    }
+    static pkv_attr_flags attr;                                     // per instantiation and device
+    PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
     const float logit_scale = PKV_LOG2E / sqrtf((float)L->head_dim);
     CUtensorMap kmap, qmap;
     int rc = encode_rows128_map(&kmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::PAGE / 128);

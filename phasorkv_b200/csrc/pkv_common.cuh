@@ -24,6 +24,23 @@ int pkv_scale_round_up_mode();     // 1: block scales are rounded up (pkv_set_sc
 
 #define PKV_LAUNCH_CHECK() PKV_CUDA_TRY(cudaGetLastError())
 
+// Opt-in to more than 48 KB of dynamic shared memory. The attribute belongs to a (kernel, device) pair, so
+// it is set once per kernel on every device this process launches on (a process may drive several GPUs);
+// `done` is the kernel's own flag table. The race of two host threads on a flag is benign: both set the
+// same attribute value.
+constexpr int PKV_MAX_DEVICES = 64;
+struct pkv_attr_flags { bool done[PKV_MAX_DEVICES]; };
+template <typename K>
+inline cudaError_t pkv_set_max_smem(K kern, int bytes, pkv_attr_flags& f) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < PKV_MAX_DEVICES && f.done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < PKV_MAX_DEVICES) f.done[dev] = true;
+    return e;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Programmatic dependent launch. The kernels of a decode step form a chain on one stream; each is
 // launched with the "programmatic stream serialization" attribute, lets its successor come onto the

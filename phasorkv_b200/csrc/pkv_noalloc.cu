@@ -29,7 +29,8 @@ static __device__ __align__(256) float g_noalloc_partials[SCRATCH_FLOATS];
 constexpr int MAX_DEVICES = 64;
 float* g_scratch_ptr[MAX_DEVICES] = {nullptr};
 
-// Device address of the scratch array on the current device; looked up once per device.
+// Device address of the scratch array on the current device; looked up once per device. The table is
+// filled without a lock: two host threads that race here look up and store the same address.
 int scratch_for_current_device(float** out) {
     int dev = -1;
     PKV_CUDA_TRY(cudaGetDevice(&dev));
@@ -65,7 +66,8 @@ extern "C" int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache
     st = scratch_for_current_device(&scratch);
     if (st) return st;
     // every (sequence, split) slot of the scratch is written in full by the attention kernel before
-    // the merge reads it, so nothing left over from an earlier call can leak into this one
+    // the merge reads it -- with its partial result, or with the neutral triple when the CTA gave up
+    // (status_dev then says so) -- so nothing left over from an earlier call can leak into this one
     st = pkv_attn_tc_launch(layer, cache, qop_dev, page_table_dev, max_pages, seqlens_dev, batch, n_split, 0u, scratch,
                             nullptr, 0, status_dev, nullptr, (cudaStream_t)stream);
     if (st) return st;

@@ -225,8 +225,11 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
 template <typename XT>
 __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs Wa, const pkv_absorb_impl::Args Aa, int batch) {
     extern __shared__ __align__(16) float sm[];
-    pkv_grid_launch_dependents();
+    // Wait first, trigger second (as pkv_absorb does): the attention kernel behind this one streams cache
+    // pages before its own wait, which is only safe if every launch up to this kernel's predecessor -- a
+    // chunk write of the same cache, for instance -- has completed by the time it starts.
     pkv_grid_wait();                                     // x and q may be the output of the kernel before
+    pkv_grid_launch_dependents();
     if ((int)blockIdx.y >= Wa.n_tiles) {
         const int n_hg = (Aa.n_q + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
         const int a = ((int)blockIdx.y - Wa.n_tiles) * CL + (int)blockIdx.x;
@@ -239,11 +242,10 @@ __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs W
 template <typename XT>
 cudaError_t launch_prologue(const WriteArgs& Wa, const pkv_absorb_impl::Args& Aa, int batch, size_t smem, cudaStream_t st) {
     auto kern = pkv_step_prologue_kernel<XT>;
-    static bool attr_done = false;                       // per instantiation
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static pkv_attr_flags smem_set;                      // per instantiation and device
+    {
+        cudaError_t e = pkv_set_max_smem(kern, (int)smem, smem_set);
         if (e != cudaSuccess) return e;
-        attr_done = true;
     }
     const int n_hg = (Aa.n_q + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
     cudaLaunchConfig_t cfg = {};

@@ -325,12 +325,8 @@ int launch_write_small(const pkv_layer_t* L, const pkv_cache_t* C, const void* x
     const int n_slices = (L->d_model + SM_KC - 1) / SM_KC;
     auto kern = pkv_project_small_kernel<XT>;
     constexpr int smem = (SM_TOK * SM_KC + SM_COL * SM_BP) * 4;
-    static bool attr_done = false;
-    if (!attr_done) {
-        PKV_CUDA_TRY(cudaFuncSetAttribute(pkv_project_small_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        PKV_CUDA_TRY(cudaFuncSetAttribute(pkv_project_small_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
-    }
+    static pkv_attr_flags attr;                          // per instantiation and device
+    PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
     PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(WP / SM_COL, n_slices), dim3(256), smem, st, L->Bw_dev, (const XT*)x, n,
                                     L->d_model, W, WP, scratch));
     const bool with_v = C && C->v_dev && v_rows;

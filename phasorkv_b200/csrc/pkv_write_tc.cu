@@ -210,11 +210,8 @@ int launch_write_tc(const CUtensorMap& xmap, const CUtensorMap& bmap, const pkv_
                     cudaStream_t st) {
     auto kern = pkv_cache_write_tc_kernel<WP>;
     constexpr int smem = WCfg<WP>::SMEM;
-    static bool attr_done = false;
-    if (!attr_done) {
-        PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_done = true;
-    }
+    static pkv_attr_flags attr;                          // per instantiation and device
+    PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
     PKV_CUDA_TRY(pkv_launch_chained(kern, dim3((n + TM_TOK - 1) / TM_TOK), dim3(NTHREADS), smem, st, xmap, bmap, n, L->d_model,
                                     2 * L->R + L->R_s, L->R, pos, (const float2*)ph, L->head_dim / 2, slots, L->freq_dev,
                                     L->inv_freq_dev, L->attn_scale, L->second, pkv_scale_round_up_mode(),

@@ -187,7 +187,17 @@ class PhasorKey:
         return 2 * self.R + self.R_s
 
     def write(self, x: torch.Tensor, ph: torch.Tensor) -> torch.Tensor:
-        """Tokens x [T, D] at phasors ph [T, d/2] -> fp32 cache rows [T, 2R + R_s] (unquantised)."""
+        """Tokens x [T, D] at phasors ph [T, d/2] -> cache rows [T, 2R + R_s] (unquantised): fp64 rows for
+        fp64 x, fp32 rows otherwise, as the reference (phasorkv/latent.py:63-64)."""
+        if x.dtype == torch.float64:
+            t = self._f64()
+            xd = x.to(self.device).contiguous()
+            phd = torch.view_as_real(ph.to(torch.complex128)).to(self.device).contiguous()
+            out = torch.empty((xd.shape[0], self.cache_width), dtype=torch.float64, device=self.device)
+            _lib.check(_lib.load().pkv_write_rows_f64(_lib.ptr(t["Bw"]), _lib.ptr(t["freq"]), self.d_model, self.R, self.R_s,
+                                                      self.h, _lib.ptr(xd), _lib.ptr(phd), xd.shape[0], _lib.ptr(out),
+                                                      _lib.current_stream()), "pkv_write_rows_f64")
+            return out
         L = self._layer()
         x = self._x(x)
         phd = self._ph(ph)
@@ -198,7 +208,18 @@ class PhasorKey:
         return out
 
     def absorb(self, q: torch.Tensor, ph: torch.Tensor) -> torch.Tensor:
-        """Pre-RoPE queries q [H, Tq, d] at phasors ph [Tq, d/2] -> [H, Tq, 2R + R_s]."""
+        """Pre-RoPE queries q [H, Tq, d] at phasors ph [Tq, d/2] -> [H, Tq, 2R + R_s] (fp64 for fp64 q)."""
+        if q.dtype == torch.float64:
+            t = self._f64()
+            qd = q.to(self.device).transpose(0, 1).contiguous()
+            phd = torch.view_as_real(ph.to(torch.complex128)).to(self.device).contiguous()
+            out = torch.empty((qd.shape[0], self.n_q, self.cache_width), dtype=torch.float64, device=self.device)
+            _lib.check(_lib.load().pkv_absorb_rows_f64(_lib.ptr(t["A_re"]), _lib.ptr(t["A_im"]), _lib.ptr(t["A_s"]),
+                                                       _lib.ptr(t["freq"]), _lib.ptr(t["slow"]), self.n_q, self.n_kv,
+                                                       self.head_dim, self.R, self.R_s, int(self.slow.numel()) if self.R_s else 0,
+                                                       _lib.ptr(qd), _lib.ptr(phd), qd.shape[0], _lib.ptr(out),
+                                                       _lib.current_stream()), "pkv_absorb_rows_f64")
+            return out.transpose(0, 1)
         L = self._layer()
         qd = q.to(device=self.device, dtype=torch.float32).transpose(0, 1).contiguous()     # [Tq, H, d]
         phd = self._ph(ph)
@@ -207,12 +228,32 @@ class PhasorKey:
                                           _lib.ptr(out), None, _lib.current_stream()), "pkv_absorb")
         return out.transpose(0, 1)
 
-    def scores(self, q_abs: torch.Tensor, cache) -> torch.Tensor:
-        """Unscaled logits [H, Tq, Tk] of absorbed queries against cache rows.
+    @staticmethod
+    def scores(q_abs: torch.Tensor, cache: torch.Tensor) -> torch.Tensor:
+        """Unscaled logits [H, Tq, Tk] = q_abs @ cache^T of the rows given, in q_abs's precision (fp32 or
+        fp64), with no quantisation: the reference's static method (phasorkv/latent.py:85-88). The result
+        lives on the GPU. `scores_nvfp4` is the score on the quantised cache."""
+        if not torch.cuda.is_available():
+            raise _lib.PhasorKVError("phasorkv_b200 needs a CUDA device; there is no CPU path")
+        dt = torch.float64 if q_abs.dtype == torch.float64 else torch.float32
+        dev = q_abs.device if q_abs.is_cuda else torch.device("cuda", torch.cuda.current_device())
+        H, Tq, W = q_abs.shape
+        qa = q_abs.to(device=dev, dtype=dt).reshape(H * Tq, W).contiguous()
+        rows = cache.to(device=dev, dtype=dt).contiguous()
+        if rows.shape[1] != W:
+            raise ValueError(f"cache rows have width {rows.shape[1]}, the absorbed query {W}")
+        out = torch.empty((H * Tq, rows.shape[0]), dtype=dt, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().pkv_scores_exact(_lib.ptr(qa), _lib.ptr(rows), H * Tq, rows.shape[0], W,
+                                                    _lib.F64 if dt == torch.float64 else _lib.F32, _lib.ptr(out),
+                                                    _lib.current_stream()), "pkv_scores_exact")
+        return out.view(H, Tq, rows.shape[0])
+
+    def scores_nvfp4(self, q_abs: torch.Tensor, cache) -> torch.Tensor:
+        """Unscaled logits [H, Tq, Tk] of absorbed queries against the NVFP4 cache.
 
         `cache` is either fp32 rows [Tk, W] (they are quantised with this layer's tensor scale into a
-        scratch paged cache first, so the result is the score on the NVFP4 cache) or a tuple
-        ``(PagedLatentCache, sequence index)``."""
+        scratch paged cache first) or a tuple ``(PagedLatentCache, sequence index)``."""
         if isinstance(cache, tuple):
             pc, b = cache
         else:
@@ -259,6 +300,7 @@ class PhasorKey:
                     scratch: Optional[torch.Tensor] = None) -> None:
         """Fused write of tokens x [n, D] (fp32 or bf16) at global `positions` into `slots`; V rows too.
         With ``cache=None`` only the unquantised rows are produced (into `latent_out`)."""
+        self._need_inv_freq("write_paged")
         L = self._layer()
         x = self._x(x)
         if v is not None:
@@ -290,6 +332,7 @@ class PhasorKey:
 
     def absorb_step(self, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace, operand: bool = True) -> None:
         """q [B, H, d] fp32 at `positions` [B] -> ws.qabs (fp32) and, if asked, ws.qop (operand form)."""
+        self._need_inv_freq("absorb_step")
         L = self._layer()
         _lib.check(_lib.load().pkv_absorb(ctypes.byref(L), _lib.ptr(q), _lib.ptr(positions), None, q.shape[0],
                                           _lib.ptr(ws.qabs), _lib.ptr(ws.qop) if operand else None,
@@ -302,6 +345,7 @@ class PhasorKey:
         """`write_paged` of the newest token of every sequence and `absorb_step` of the step's queries
         as one launch (same bits as the two calls). `q=None`: the write alone (the queries then go to
         `attend_q_step`)."""
+        self._need_inv_freq("prologue_step")
         L = self._layer()
         x = self._x(x)
         if v is not None:
@@ -321,6 +365,7 @@ class PhasorKey:
         itself (no `absorb_step`, same bits). `early`: the launch enqueued just before writes nothing this
         kernel reads except, with `tail_written`, rows of each sequence's last page (a write of the newest
         token) and, unless `query_ready`, the queries."""
+        self._need_inv_freq("attend_q_step")
         L = self._layer()
         flags = _lib.ATTN_SCORES_ONLY if scores_only else 0
         if early:
@@ -361,6 +406,7 @@ class PhasorKey:
                    ws: DecodeWorkspace, n_exact: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Partial triple of the exact (bf16, rotated keys) tokens: k_exact, v_exact [B, n_kv, E, d] bf16,
         optional valid counts n_exact [B] -> ws.exact [B, H, d+2]; merged by ``merge_step(exact=True)``."""
+        self._need_inv_freq("exact_step")
         L = self._layer()
         B, E = q.shape[0], k_exact.shape[2]
         if getattr(ws, "exact", None) is None:
@@ -405,8 +451,6 @@ class PhasorKey:
             if not torch.cuda.is_available():
                 raise _lib.PhasorKVError("phasorkv_b200 needs a CUDA device; there is no CPU path")
             _lib.check(_lib.load().pkv_device_check(), "pkv_device_check")
-            if self.inv_freq is None:
-                raise _lib.PhasorKVError("inv_freq was not given")
             dev = self.device
             B = self.B.to(torch.complex64)
             rows = [B.real, B.imag] + ([self.B_s.to(torch.float32)] if self.R_s else [])
@@ -425,7 +469,10 @@ class PhasorKey:
                 A_s=None if not self.R_s else self.A_s.to(device=dev, dtype=torch.float32).contiguous(),
                 freq=self.freq.to(device=dev, dtype=torch.int32).contiguous(),
                 slow=None if not self.R_s else self.slow.to(device=dev, dtype=torch.int32).contiguous(),
-                inv_freq=self.inv_freq.to(device=dev, dtype=torch.float64).contiguous(),
+                # without inv_freq (the reference's three-argument constructor) the calls that take ready
+                # phasors still work; the calls that take positions refuse (_need_inv_freq)
+                inv_freq=(torch.zeros(self.h, dtype=torch.float64) if self.inv_freq is None else self.inv_freq
+                          ).to(device=dev, dtype=torch.float64).contiguous(),
             )
             L = _lib.Layer(self.d_model, self.n_q, self.n_kv, self.head_dim, self.R, self.R_s,
                            int(self.slow.numel()) if self.R_s else 0, self.attn_scale, self.second,
@@ -436,6 +483,39 @@ class PhasorKey:
             t["layer"] = L
             self._dev = t
         return self._dev["layer"]
+
+    def _need_inv_freq(self, what: str) -> None:
+        if self.inv_freq is None:
+            raise _lib.PhasorKVError(f"{what} forms phasors from positions and needs inv_freq: pass it to the constructor "
+                                     "(PhasorKey(fac, ranks, n_q, inv_freq=rotary.inv_freq)) or use set_inv_freq")
+
+    def set_inv_freq(self, inv_freq: torch.Tensor, attn_scale: Optional[float] = None) -> None:
+        """Rotary inverse frequencies [d/2] (and attention scaling) for the calls that take positions."""
+        self.inv_freq = inv_freq.to(torch.float64).cpu()
+        if attn_scale is not None:
+            self.attn_scale = float(attn_scale)
+        if self._dev is not None:
+            self._dev["inv_freq"].copy_(self.inv_freq)
+            self._dev["layer"].attn_scale = self.attn_scale
+
+    def _f64(self) -> dict:
+        """fp64 device copies of the factors for the fp64 forms of write / absorb (made on first use)."""
+        if getattr(self, "_dev64", None) is None:
+            if not torch.cuda.is_available():
+                raise _lib.PhasorKVError("phasorkv_b200 needs a CUDA device; there is no CPU path")
+            _lib.check(_lib.load().pkv_device_check(), "pkv_device_check")
+            dev = self.device
+            B = self.B.to(torch.complex128)
+            rows = [B.real, B.imag] + ([self.B_s.to(torch.float64)] if self.R_s else [])
+            A = self.A.to(torch.complex128)
+            self._dev64 = dict(
+                Bw=torch.cat(rows, dim=0).to(device=dev, dtype=torch.float64).contiguous(),
+                A_re=A.real.to(device=dev, dtype=torch.float64).contiguous(),
+                A_im=A.imag.to(device=dev, dtype=torch.float64).contiguous(),
+                A_s=None if not self.R_s else self.A_s.to(device=dev, dtype=torch.float64).contiguous(),
+                freq=self.freq.to(device=dev, dtype=torch.int32).contiguous(),
+                slow=None if not self.R_s else self.slow.to(device=dev, dtype=torch.int32).contiguous())
+        return self._dev64
 
     def _x(self, x: torch.Tensor) -> torch.Tensor:
         if x.dtype not in (torch.float32, torch.bfloat16):

@@ -2,6 +2,8 @@
 through the CUDA path, and the oracle's view of the same data."""
 from __future__ import annotations
 
+import types
+
 import torch
 
 from oracle import phasor_oracle as po
@@ -70,3 +72,19 @@ class Scenario:
 def rel(a: torch.Tensor, b: torch.Tensor) -> float:
     """Frobenius-norm relative error of a against b."""
     return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-300))
+
+
+class Blk(types.SimpleNamespace):
+    """One block of a reference Factorization (phasorkv/factorize.py:56-63): U, s2, sq, Mw, where, cost."""
+
+
+def fac_from_golden(g, tag):
+    """A Factorization-like object rebuilt from the block data that tests/golden/make_golden.py stored from a
+    reference `Factorization`; returns (fac, n_q)."""
+    blocks = []
+    for bi in range(int(g[f"{tag}_nblocks"])):
+        t = lambda k: torch.from_numpy(g[f"{tag}_blk{bi}_{k}"])
+        blocks.append(Blk(U=t("U"), s2=t("s2"), sq=t("sq"), Mw=t("Mw"), cost=int(g[f"{tag}_blk{bi}_cost"]),
+                          where=int(g[f"{tag}_blk{bi}_where"])))
+    D, n_q, n_kv, d = (int(v) for v in g["dims"])
+    return types.SimpleNamespace(blocks=blocks, n_kv=n_kv, d=d, absorbed=True, nope=torch.from_numpy(g[f"{tag}_nope"])), n_q

@@ -16,7 +16,7 @@ from phasorkv_b200 import synth
 from phasorkv_b200.latent import PagedLatentCache, PhasorKey
 
 from conftest import GOLDEN
-from helpers import Scenario, rel
+from helpers import Scenario, fac_from_golden, rel
 
 pytestmark = pytest.mark.gpu
 
@@ -174,11 +174,43 @@ def test_rebuilt_keys_identity(tag):
     t = lambda k: torch.from_numpy(g[f"{tag}_{k}"]) if f"{tag}_{k}" in g else None
     pk = PhasorKey.from_factors(t("A"), t("B"), t("freq"), n_q, n_kv, d, torch.from_numpy(g["inv_freq"]),
                                 t("A_s"), t("B_s"), t("slow") if f"{tag}_A_s" in g else None)
-    rows = pk.write(torch.from_numpy(g["x"]), torch.from_numpy(g["ph_k"]))
-    qabs = pk.absorb(torch.from_numpy(g["q"]), torch.from_numpy(g["ph_q"]))
-    S = (qabs.double() @ rows.double().T).cpu()
+    rows = pk.write(torch.from_numpy(g["x"]).float(), torch.from_numpy(g["ph_k"]))
+    qabs = pk.absorb(torch.from_numpy(g["q"]).float(), torch.from_numpy(g["ph_q"]))
+    S = PhasorKey.scores(qabs, rows).cpu()                          # the reference's static call, exact fp32 product
+    assert S.dtype == torch.float32
     assert rel(S, t("scores_hf")) < LOGIT_TOL
     assert rel(S, t("scores")) < 1e-5
+
+
+@pytest.mark.parametrize("tag", ["freq", "band"])
+def test_reference_call_sequence_on_a_factorization(tag):
+    """The reference's own sequence, unchanged: ``pk = PhasorKey(fac, ranks, n_q)`` (no inv_freq), then
+    ``PhasorKey.scores(pk.absorb(q, ph), pk.write(x, ph))`` -- in fp64, which the reference keeps
+    (phasorkv/latent.py:63-64), it meets the reference's scores and the rebuilt-keys identity of its
+    README.md:75-77 to 1e-13; in fp32 to 1e-5."""
+    from phasorkv_b200._lib import PhasorKVError
+    g = _golden("phasorkey_factorized.npz")
+    fac, n_q = fac_from_golden(g, tag)
+    pk = PhasorKey(fac, g[f"{tag}_ranks"].tolist(), n_q)
+    t = lambda k: torch.from_numpy(g[k])
+    x, q, ph_k, ph_q = t("x"), t("q"), t("ph_k"), t("ph_q")
+    rows, qabs = pk.write(x, ph_k), pk.absorb(q, ph_q)
+    assert rows.dtype == torch.float64 and qabs.dtype == torch.float64
+    assert rel(rows.cpu(), t(f"{tag}_rows")) < 1e-13 and rel(qabs.cpu(), t(f"{tag}_qabs")) < 1e-13
+    S = PhasorKey.scores(qabs, rows)
+    assert S.dtype == torch.float64
+    assert rel(S.cpu(), t(f"{tag}_scores")) < 1e-13
+    assert rel(S.cpu(), t(f"{tag}_scores_hf")) < 1e-13
+    S32 = PhasorKey.scores(pk.absorb(q.float(), ph_q), pk.write(x.float(), ph_k))
+    assert S32.dtype == torch.float32 and rel(S32.cpu(), t(f"{tag}_scores")) < 1e-5
+    # the calls that form phasors from positions say what they miss instead of rotating by zero
+    with pytest.raises(PhasorKVError, match="inv_freq"):
+        pk.write_paged(None, x.float().cuda(), t("pos_k").to(torch.int32).cuda(), None,
+                       latent_out=torch.empty((x.shape[0], pk.cache_width), device="cuda"))
+    pk.set_inv_freq(t("inv_freq"))
+    out = torch.empty((x.shape[0], pk.cache_width), device="cuda")
+    pk.write_paged(None, x.float().cuda(), t("pos_k").to(torch.int32).cuda(), None, latent_out=out)
+    assert rel(out.cpu(), t(f"{tag}_rows")) < 2e-6
 
 
 @pytest.mark.parametrize("config", ["cfg2", "cfg3", "cfg5"])
@@ -262,10 +294,10 @@ def test_scores_only_mode_gives_log_sum_exp():
         assert torch.allclose(got, lse, atol=2e-3)
 
 
-def test_compat_scores_method():
+def test_scores_on_the_quantised_rows():
     sc = Scenario("cfg2", seqlens=(200,))
     qa, _, _ = sc.oracle_scores_and_output(0, sc.rows_ref[0])
-    S = sc.pk.scores(qa[:, None, :], sc.rows_ref[0]).cpu()           # [H, 1, Tk], on the NVFP4 of the given rows
+    S = sc.pk.scores_nvfp4(qa[:, None, :], sc.rows_ref[0]).cpu()     # [H, 1, Tk], on the NVFP4 of the given rows
     _, _, hat = po.nvfp4_quantize(sc.rows_ref[0], torch.tensor([sc.second]))
     assert rel(S[:, 0], sc.opk.scores(qa, hat)) < LOGIT_TOL
 
@@ -389,6 +421,43 @@ def test_attention_behind_prologue_sees_the_newest_token(n_split):
         sc.v[b][T - 1] = v_new[b]
         _, _, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b))
         assert rel(out_early[b].cpu(), O_ref) < OUT_TOL
+
+
+def test_attention_behind_chunk_write_and_prologue():
+    """The first decode step after a prefill, all on one stream with nothing in between: a chunk write
+    of the cache (tensor-core kernel), the prologue of the newest token, the attention that streams pages
+    early. The attention must see the chunk's rows: the prologue lets it start only after its own wait,
+    i.e. after the chunk write has completed. Each round rewrites the chunk with other data and compares
+    with a launch that waits for everything."""
+    T, n = 1500, 1024
+    sc = Scenario("cfg2", seqlens=(T, T), pos0=0, x_dtype=torch.bfloat16)
+    pk, B = sc.pk, sc.B
+    g = torch.Generator().manual_seed(5)
+    chunks = [(synth.make_hidden(g, n, 4096) * (k + 2.0)).to(torch.bfloat16).cuda() for k in range(3)]
+    vchunks = [(synth.make_values(g, n, sc.spec.n_kv, sc.spec.head_dim) * (k + 2.0)).cuda() for k in range(3)]
+    lp = torch.arange(n, dtype=torch.int32, device="cuda")
+    cslots = sc.cache.slots(torch.zeros_like(lp), lp)                   # rows 0 .. n-1 of sequence 0
+    x_new = (synth.make_hidden(g, B, 4096) * 3.0).cuda()
+    v_new = (synth.make_values(g, B, sc.spec.n_kv, sc.spec.head_dim) * 4.0).cuda()
+    lens = torch.tensor(sc.seqlens, dtype=torch.int32, device="cuda")
+    slots = sc.cache.slots(torch.arange(B, dtype=torch.int32, device="cuda"), lens - 1)
+    wpos = (lens - 1).contiguous()
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    ws, ws2 = pk.workspace(B, 3), pk.workspace(B, 3)
+    early = torch.zeros((3, B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
+    late = torch.zeros_like(early)
+    torch.cuda.synchronize()
+    for k in range(3):
+        pk.write_paged(sc.cache, chunks[k], lp, cslots, v=vchunks[k])
+        pk.prologue_step(sc.cache, x_new, wpos, slots, q, qpos, ws, v=v_new)
+        pk.attend_step(sc.cache, ws, out=early[k], after_prologue=True)
+        pk.absorb_step(q, qpos, ws2)
+        pk.attend_step(sc.cache, ws2, out=late[k])                     # waits for every launch before it
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0 and int(ws2.status.abs().sum()) == 0
+    for k in range(3):
+        assert torch.equal(early[k], late[k]), k
+    assert not torch.equal(early[0, 0], early[1, 0])                    # the rounds really differ (sequence 0 holds the chunk)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -15,6 +15,7 @@ from phasorkv_b200.latent import PhasorKey
 from phasorkv_b200.patch import PhasorKeyPatch
 
 from conftest import GOLDEN, ROOT
+from helpers import Blk as _Blk, fac_from_golden as _fac_from_golden
 
 
 @pytest.fixture(scope="module")
@@ -68,20 +69,6 @@ def test_synth_layers_have_benchmark_shapes():
     again = synth.make_layer("cfg3", 0)
     assert torch.equal(again.A, s3.A) and torch.equal(again.B_s, s3.B_s)
     assert not torch.equal(synth.make_layer("cfg2", 1).B, s2.B)
-
-
-class _Blk(types.SimpleNamespace):
-    pass
-
-
-def _fac_from_golden(g, tag):
-    blocks = []
-    for bi in range(int(g[f"{tag}_nblocks"])):
-        t = lambda k: torch.from_numpy(g[f"{tag}_blk{bi}_{k}"])
-        blocks.append(_Blk(U=t("U"), s2=t("s2"), sq=t("sq"), Mw=t("Mw"), cost=int(g[f"{tag}_blk{bi}_cost"]),
-                           where=int(g[f"{tag}_blk{bi}_where"])))
-    D, n_q, n_kv, d = (int(v) for v in g["dims"])
-    return types.SimpleNamespace(blocks=blocks, n_kv=n_kv, d=d, absorbed=True, nope=torch.from_numpy(g[f"{tag}_nope"])), n_q
 
 
 @pytest.mark.parametrize("tag", ["freq", "band"])
