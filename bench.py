@@ -12,8 +12,14 @@ scripts/bench_decode.py:4-8); cache contents are real writes of seeded hidden st
 
 N > 1 (launched by torch.distributed.run, one rank per GPU): every rank runs its own batch (batch
 parallel, no communication, weak scaling); in addition the token-sharded 128k configuration is
-timed (`seq_sharded`), where each rank attends over its slice of the tokens and the partial
-(o, m, l) triples are exchanged by one NCCL all-gather per layer.
+timed (`seq_sharded`; `--workload cfg4` makes it the headline line), where each rank attends over its
+slice of the tokens and the partial (o, m, l) triples are exchanged by the library's own peer-memory
+kernel over NVLink (`--collective nccl`: one NCCL all-gather per layer + merge). After the timed
+replays the sharded run checks itself: status words, the two exchange routes against each other and
+the tensor-core result against the CUDA-core kernel (`seq_sharded.check`).
+
+`--workload cfg5` is the 7B multi-head shape with, per step and layer, a 2048-token chunk write for
+each of the GPU's 8 sequences (tensor-core cache write) plus the decode step.
 
 Prints one JSON line on rank 0.
 """
@@ -43,7 +49,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--no-chunk-write", action="store_true", help="cfg5 without its 2048-token chunk write per step")
     ap.add_argument("--algo", default=os.environ.get("PKV_BENCH_ALGO", "tc"), choices=["tc", "simt"])
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--batch", type=int, default=0, help="override the configuration's batch (profiling)")
@@ -112,7 +119,7 @@ class Stack:
     """32 layers of one configuration with their caches filled by real writes of seeded hidden states."""
 
     def __init__(self, config: str, n_layers: int, device, algo: str, seed: int, batch: int = 0, context: int = 0,
-                 n_split: int = 0):
+                 n_split: int = 0, chunk_write: bool = True):
         from phasorkv_b200 import synth
         from phasorkv_b200.latent import PhasorKey
         c = synth.CONFIGS[config]
@@ -183,20 +190,43 @@ class Stack:
         seq = torch.arange(self.B, dtype=torch.int32, device=device)
         self.wslots = [c.slots(seq, self.wpos) for c in self.caches]
         self.launches_per_layer = 0
+        # cfg5: per step and layer a chunk of `chunk` tokens is written for every sequence (a chunked prefill
+        # riding along with the decode step): the tokens just before the newest one, the same seeded hidden
+        # states for all layers (134 MB of bf16 x at 8 x 2048 tokens: larger than L2)
+        self.chunk = int(c.get("chunk", 0)) if chunk_write else 0
+        if self.chunk:
+            n = self.B * self.chunk
+            self.x_chunk = self._hidden(g, n).to(torch.bfloat16)
+            seqs = torch.arange(self.B, dtype=torch.int32, device=device).repeat_interleave(self.chunk)
+            lp = (self.T - 1 - self.chunk + torch.arange(self.chunk, dtype=torch.int32, device=device)).repeat(self.B)
+            self.chunk_pos = lp.contiguous()
+            self.chunk_slots = self.caches[0].slots(seqs, lp)            # every layer's cache has the same page table
 
     def _hidden(self, g, n):
         x = torch.randn((n, D_MODEL), generator=g, device=self.device, dtype=torch.float32)
         x[:, self.outliers] *= 20.0
         return x
 
-    def step(self, events=None, scores_only=False, write=True, pre=None, post=None):
+    def step(self, events=None, scores_only=False, write=True, pre=None, post=None, chunk_events=None, chain=None):
         """One decode step over all layers. `events`: list receiving (start, end) CUDA events around
-        each attention launch. `pre(l)` / `post(l)` run on the host before / after layer l is enqueued."""
+        each attention launch (`chunk_events`: around each chunk write). `pre(l)` / `post(l)` run on the
+        host before / after layer l is enqueued. `chain`: launch the attention as part of the dependent-launch
+        chain (default: whenever no events sit between the kernels)."""
         n = 0
+        chained = (events is None) if chain is None else chain
         for l, (pk, cache) in enumerate(zip(self.layers, self.caches)):
             ws = self.ws[l & 1]
             if pre is not None:
                 pre(l)
+            if self.chunk and write:
+                if chunk_events is not None:
+                    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    c0.record()
+                pk.write_paged(cache, self.x_chunk, self.chunk_pos, self.chunk_slots)
+                n += 1
+                if chunk_events is not None:
+                    c1.record()
+                    chunk_events.append((c0, c1))
             fused = write and not self.simt and self.fused_prologue
             inline = fused and self.inline_absorb and not scores_only
             if inline:                                                # the write alone; attention absorbs the raw queries
@@ -218,10 +248,10 @@ class Stack:
             if inline:
                 # the queries of the step exist before the layer's first launch: attention starts with the write,
                 # streams pages and absorbs at once, and waits for the write only before the page being written
-                pk.attend_q_step(cache, self.q[l], self.qpos, ws, early=events is None, tail_written=True, query_ready=True)
+                pk.attend_q_step(cache, self.q[l], self.qpos, ws, early=chained, tail_written=True, query_ready=True)
             else:
-                pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=events is None and not fused,
-                               after_prologue=events is None and fused)
+                pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=chained and not fused,
+                               after_prologue=chained and fused)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
@@ -271,6 +301,38 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
+def profile_traffic_base():
+    """DRAM bytes read per launch and the tokens of that launch, from the ncu summary kept under profiles/
+    (the line `dram_bytes_read_per_launch: <bytes> for <tokens> tokens`); None if it is not there."""
+    import re
+    p = os.path.join(ROOT, "profiles", "pkv_attn_tc__cfg2_b16_t8192.md")
+    try:
+        m = re.search(r"dram_bytes_read_per_launch:\s*([0-9.e+]+)\s*for\s*(\d+)\s*tokens", open(p).read())
+        return (float(m.group(1)), int(m.group(2))) if m else None
+    except OSError:
+        return None
+
+
+def read_probe_gbs(device, n_bytes=2 << 30, reps=5):
+    """Bandwidth of the library's plain read-only stream kernel over a buffer far larger than L2."""
+    from phasorkv_b200 import _lib
+    lib = _lib.load()
+    buf = torch.empty(n_bytes, dtype=torch.uint8, device=device)
+    buf.random_(0, 255)
+    sink = torch.zeros(1, dtype=torch.int32, device=device)
+    best = 0.0
+    for i in range(reps + 2):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(lib.pkv_read_probe(_lib.ptr(buf), n_bytes, _lib.ptr(sink), _lib.current_stream()), "pkv_read_probe")
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            best = max(best, n_bytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del buf
+    return round(best, 1)
+
+
 def run_b200(args):
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -290,9 +352,34 @@ def run_b200(args):
     from phasorkv_b200 import _lib
     _lib.check(_lib.load().pkv_device_check(), "pkv_device_check")
 
-    st = Stack(args.workload, args.layers, device, args.algo, seed=1234 + rank, batch=args.batch, context=args.context,
-               n_split=args.splits)
+    sharded_headline = args.workload == "cfg4"          # the token-sharded step is the line; its pools are cfg2's
+    st = Stack("cfg2" if sharded_headline else args.workload, args.layers, device, args.algo, seed=1234 + rank,
+               batch=args.batch, context=args.context, n_split=args.splits, chunk_write=not args.no_chunk_write)
     torch.cuda.synchronize()
+    pk, src = peaks()
+    L = args.layers
+    if sharded_headline:
+        sampler = ClockSampler(local)
+        sampler.start()
+        sh = run_sharded(st, args, dist, world, want_e2e=True)
+        clocks = sampler.stop()
+        line = {
+            "metric": "decode tokens/s (token-sharded B=4, T=131072, %d layers)" % L,
+            "value": sh["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": sh["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V", "data": "synthetic",
+            "config": {"workload": sh["workload"], "algo": args.algo, "parallelism": "token-sharded x%d" % world,
+                       "l2": "inputs larger than L2 (%.2f GB streamed per GPU per layer)" % (sh["bytes_per_gpu_per_layer"] / 1e9)},
+            "roofline": sh.pop("roofline"), "e2e": sh.pop("e2e"), "gpu_launches": sh["gpu_launches"], "clocks": clocks,
+            "seq_sharded": sh,
+        }
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- device-resident timing of exactly K steps
     sampler = ClockSampler(local)
@@ -305,26 +392,35 @@ def run_b200(args):
     # ---- the same K steps once more with CUDA events around every attention launch: the per-launch
     # duration the roofline is computed from (the events sit between kernels of the chain, so this pass
     # is kept apart from the one that gives `value`)
-    events = []
-    ms_step_ev = timed(lambda: st.step(events=events), args.steps, 1, dist)
+    events, chunk_events = [], []
+    ms_step_ev = timed(lambda: st.step(events=events, chunk_events=chunk_events), args.steps, 1, dist)
     clocks = sampler.stop()
-    timed_events = events[-args.steps * args.layers:]
+    timed_events = events[-args.steps * L:]
     attn_ms = sum(a.elapsed_time(b) for a, b in timed_events) / len(timed_events)
-    gpu_launches = st.launches_per_layer * args.layers * args.steps
+    gpu_launches = st.launches_per_layer * L * args.steps
 
-    # ---- K path only (logits + log-sum-exp, V never read): the "K-path us/layer" of the metric
+    # ---- K path only (logits + log-sum-exp, V never read): the "K-path us/layer" of the metric.
+    # (1) the scores-only attention launch between CUDA events; (2) the whole K path of a step -- absorb,
+    # scores-only attention, log-sum-exp merge -- as a dependent-launch chain without events, per layer
+    nk = max(2, args.steps // 2)
     ev_k = []
-    ms_k = timed(lambda: st.step(events=ev_k, scores_only=True, write=False), max(2, args.steps // 2), 2, dist)
-    k_events = ev_k[-max(2, args.steps // 2) * args.layers:]
+    timed(lambda: st.step(events=ev_k, scores_only=True, write=False), nk, 2, dist)
+    k_events = ev_k[-nk * L:]
     attn_k_ms = sum(a.elapsed_time(b) for a, b in k_events) / len(k_events)
+    ms_kstep = timed(lambda: st.step(scores_only=True, write=False), nk, 2, dist)
+
+    peak_read = read_probe_gbs(device) if args.algo == "tc" else None
 
     # ---- end to end through the host API: pinned host inputs in, outputs back, every step
-    L = args.layers
     hx = torch.empty(st.x_new.shape, dtype=st.x_new.dtype).pin_memory()
     hv = torch.empty(st.v_new.shape, dtype=st.v_new.dtype).pin_memory()
     hq = torch.empty(st.q.shape, dtype=st.q.dtype).pin_memory()
     ho = torch.empty(st.out.shape, dtype=st.out.dtype).pin_memory()
     hx.copy_(st.x_new); hv.copy_(st.v_new); hq.copy_(st.q)
+    hc = None
+    if st.chunk:                                        # the chunk's hidden states come from the host as well
+        hc = torch.empty(st.x_chunk.shape, dtype=st.x_chunk.dtype).pin_memory()
+        hc.copy_(st.x_chunk)
 
     # Host copies ride on their own streams in groups of layers, so that the inputs of the next group
     # arrive and the outputs of the previous one leave while a group computes; every byte still crosses
@@ -339,6 +435,8 @@ def run_b200(args):
         main = torch.cuda.current_stream()
         s_in.wait_stream(main)                      # the previous step has consumed its inputs
         with torch.cuda.stream(s_in):
+            if hc is not None:
+                st.x_chunk.copy_(hc, non_blocking=True)
             for gi, (a, b_) in enumerate(groups):
                 st.x_new[a:b_].copy_(hx[a:b_], non_blocking=True)
                 st.v_new[a:b_].copy_(hv[a:b_], non_blocking=True)
@@ -361,6 +459,8 @@ def run_b200(args):
         main.wait_stream(s_out)
     ms_e2e = timed(e2e_step, args.steps, args.warmup, dist)
     h2d = hx.numel() * hx.element_size() + hv.numel() * hv.element_size() + hq.numel() * hq.element_size()
+    if hc is not None:
+        h2d += hc.numel() * hc.element_size()
     d2h = ho.numel() * ho.element_size()
 
     # ---- token-sharded long context (cfg4): the same pools viewed as B=4, T=131072/world per rank
@@ -368,17 +468,18 @@ def run_b200(args):
     if not args.no_sharded and args.workload == "cfg2" and not args.batch and not args.context:
         try:
             sharded = run_sharded(st, args, dist, world)
+            sharded.pop("roofline", None)
         except Exception as e:                       # the headline line is still reported
             sys.stderr.write("token-sharded run failed: %r\n" % (e,))
             sharded = {"workload": "cfg4", "error": repr(e)[:300]}
 
-    pk, src = peaks()
-    # DRAM traffic per launch: an ncu capture of this kernel at B=16, T=8192 (W=256, 8 kv heads) read
-    # 287.82 MB for 131072 tokens, 1.002 x the algorithmic bytes; reads scale with the tokens streamed, the
-    # split partials written (B x n_split x 32 x 130 floats) do not.
+    # DRAM traffic per launch: the reads of an ncu capture of this kernel on a smaller case of the same
+    # shape (kept under profiles/) scaled by the tokens streamed -- reads grow in proportion to them -- plus
+    # the split partials written (B x n_split x 32 x 130 floats), which do not.
     traffic = None
-    if args.algo == "tc" and st.W == 256 and st.n_kv == 8:
-        traffic = int(287.82e6 * (st.B * st.T) / 131072 + st.B * st.n_split * 32 * 130 * 4)
+    base = profile_traffic_base()
+    if base and args.algo == "tc" and st.W == 256 and st.n_kv == 8:
+        traffic = int(base[0] * (st.B * st.T) / base[1] + st.B * st.n_split * 32 * 130 * 4)
     achieved = st.bytes_full() / (attn_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
             "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": traffic, "peak_source": src,
@@ -386,20 +487,25 @@ def run_b200(args):
             "us_per_launch": round(attn_ms * 1e3, 2),
             "timed_over": "%d launches of a second pass of the same %d steps with CUDA events around each attention "
                           "launch (%.4f ms per step in that pass)" % (len(timed_events), args.steps, ms_step_ev)}
+    if peak_read:
+        roof["peak_read_gbs"] = peak_read              # a read-only stream kernel of the library, same run
+        roof["frac_of_read_peak"] = round(achieved / peak_read, 4)
     line = {
         "metric": "decode tokens/s (B=%d, T=%d, %d layers; K-path us/layer and HBM GB/s beside it)" % (st.B, st.T, L),
         "value": round(world * st.B / (ms_step * 1e-3), 2), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V",
         "data": "synthetic",
-        "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers"
+        "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers%s"
                    % (args.workload, "7B multi-head-attention" if st.n_kv == st.n_q else "Llama-3.1-8B", st.B, st.T, st.W,
-                      st.n_kv, st.d, L),
+                      st.n_kv, st.d, L, (", plus a %d-token chunk write per sequence per layer" % st.chunk) if st.chunk else ""),
                    "algo": args.algo, "n_split": st.n_split, "parallelism": "batch-parallel x%d" % world,
                    "l2": "inputs larger than L2 (%.2f GB streamed per layer, %.1f GB per step)"
                          % (st.bytes_full() / 1e9, L * st.bytes_full() / 1e9)},
         "k_path_us_per_layer": round(attn_k_ms * 1e3, 2),
         "k_path_gbs": round(st.bytes_k() / (attn_k_ms * 1e-3) / 1e9, 1),
+        "k_path_step_us_per_layer": round(ms_kstep * 1e3 / L, 2),
+        "k_path_step_note": "absorb + scores-only attention + log-sum-exp merge per layer, one dependent-launch chain, no events",
         "full_us_per_layer": round(ms_step * 1e3 / L, 2),
         "hbm_gbs": round(achieved, 1),
         "roofline": roof,
@@ -408,10 +514,25 @@ def run_b200(args):
         "gpu_launches": gpu_launches,
         "clocks": clocks,
     }
+    if st.chunk and chunk_events:
+        ce = chunk_events[-args.steps * L:]
+        cw_ms = sum(a.elapsed_time(b) for a, b in ce) / len(ce)
+        n_tok = st.B * st.chunk
+        Wp = 128 if st.W <= 128 else 256
+        useful = 2.0 * n_tok * D_MODEL * st.W
+        cw_bytes = n_tok * D_MODEL * 2 + n_tok * (st.W // 2 + st.W // 16) + 3 * Wp * D_MODEL * 2
+        line["chunk_write"] = {
+            "tokens_per_launch": n_tok, "us_per_launch": round(cw_ms * 1e3, 2),
+            "tflops_useful": round(useful / (cw_ms * 1e-3) / 1e12, 1),
+            "tflops_mma": round(3 * useful / (cw_ms * 1e-3) / 1e12, 1),        # the factors are three bf16 terms
+            "frac_of_bf16_sustained": round(3 * useful / (cw_ms * 1e-3) / 1e12 / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]), 4),
+            "gbs": round(cw_bytes / (cw_ms * 1e-3) / 1e9, 1), "frac_of_hbm": round(cw_bytes / (cw_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+            "kernel": "pkv_cache_write_tc (latent of the chunk; V rows are not part of PhasorKey.write)"}
     if sharded is not None:
         line["seq_sharded"] = sharded
     if rank == 0 and not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=15.0)
+        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
+        line["cpu_baseline_cfg1"] = cpu_baseline_cfg1(budget_s=6.0)
     sys.stdout.flush()
     os.dup2(real_stdout, 1)
     if rank == 0:
@@ -420,25 +541,29 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
-def run_sharded(st, args, dist, world):
-    """cfg4: B=4, T=131072 with the token axis split evenly over the ranks; one all-gather per layer."""
+def run_sharded(st, args, dist, world, want_e2e=False):
+    """cfg4: B=4, T=131072 with the token axis split evenly over the ranks; the partial triples of a layer
+    are exchanged once. Timed as one CUDA graph per step, then checked (see `check` in the result)."""
+    from phasorkv_b200.sharded import ShardExchange, owner_of
     B4, T4 = 4, 131072
     Tl = T4 // world
     pages = Tl // 128
     dev = st.device
+    L = args.layers
+    rank = int(os.environ.get("RANK", 0))
     pt = torch.arange(B4 * pages, dtype=torch.int32, device=dev).reshape(B4, pages)
     seqlens = torch.full((B4,), Tl, dtype=torch.int32, device=dev)
     pk0 = st.layers[0]
-    n_split = max(1, min(pages, (torch.cuda.get_device_properties(dev).multi_processor_count * (3 if st.simt else 1)) // B4))
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    n_split = max(1, min(pages, (sms * (3 if st.simt else 1)) // B4))
     ws = pk0.workspace(B4, n_split)
     gathered = torch.empty((world, B4, st.n_q, st.d + 2), dtype=torch.float32, device=dev)
-    out = torch.empty((B4, st.n_q, st.d), dtype=torch.float32, device=dev)
+    out = torch.empty((L, B4, st.n_q, st.d), dtype=torch.float32, device=dev)
     qpos = torch.full((B4,), T4, dtype=torch.int32, device=dev)
     saved = [(c.page_table, c.seqlens, c.max_pages) for c in st.caches]
     ex = None
     if world > 1 and args.collective == "p2p":
         # peer buffers in torch symmetric memory; if any rank cannot set them up, every rank takes the NCCL route
-        from phasorkv_b200.sharded import ShardExchange
         ok = 1
         try:
             ex = ShardExchange.from_process_group(dist.group.WORLD, B4, st.n_q, st.d, dev, n_cta=B4 * st.n_q)
@@ -450,39 +575,50 @@ def run_sharded(st, args, dist, world):
         if int(agreed.item()) == 0:
             ex = None
     # the newest token (global position T-1) belongs to the last rank: only that rank writes it
-    from phasorkv_b200.sharded import owner_of
-    owner = int(os.environ.get("RANK", 0)) == owner_of(T4 - 1, world, T4) and not st.simt
+    owner = rank == owner_of(T4 - 1, world, T4) and not st.simt
     wpos = torch.full((B4,), T4 - 1, dtype=torch.int32, device=dev)
     wslots = (pt[:, (Tl - 1) // 128] * 128 + (Tl - 1) % 128).to(torch.int32).contiguous()
-
     inline = st.inline_absorb and not st.simt
 
-    def attend(pk, cache, l, **out_kw):
+    def attend(pk, cache, l, events=None, **out_kw):
         """attention of layer l on this rank's shard: raw queries absorbed in the kernel, or absorb launch + operand"""
+        chained = events is None
         if inline:
             if owner:                                       # the write alone; attention waits for it before the last page only
                 pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, None, None, ws, v=st.v_new[l, :B4])
-            pk.attend_q_step(cache, st.q[l, :B4], qpos, ws, early=True, tail_written=owner, query_ready=True, **out_kw)
+            pk.attend_q_step(cache, st.q[l, :B4], qpos, ws, early=chained, tail_written=owner, query_ready=True, **out_kw)
+            return
+        if owner:
+            pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4])
         else:
-            if owner:
-                pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4])
-            else:
-                pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
-            early = dict(after_prologue=True) if owner else dict(after_absorb=True)
-            pk.attend_step(cache, ws, simt=st.simt, **early, **out_kw)
+            pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
+        early = {} if not chained else (dict(after_prologue=True) if owner else dict(after_absorb=True))
+        if events is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        pk.attend_step(cache, ws, simt=st.simt, **early, **out_kw)
+        if events is not None:
+            e1.record()
+            events.append((e0, e1))
+
+    def layer(l, route, events=None):
+        pk, cache = st.layers[l], st.caches[l]
+        if world == 1:
+            attend(pk, cache, l, events, out=out[l])
+        elif route == "p2p":
+            attend(pk, cache, l, events)
+            ex.run_parts(ws.partials, ws.n_split, out[l])           # local merge + peer stores + merge, one kernel
+        else:
+            attend(pk, cache, l, events, packed_out=ws.packed)      # local splits merged by a launch behind
+            dist.all_gather_into_tensor(gathered, ws.packed)
+            pk.merge_gathered(gathered, out[l])
+
+    route = "p2p" if ex is not None else "nccl"
 
     def step():
-        for l, (pk, cache) in enumerate(zip(st.layers, st.caches)):
-            if world > 1:
-                if ex is not None:
-                    attend(pk, cache, l)
-                    ex.run_parts(ws.partials, ws.n_split, out)      # local merge + peer stores + merge, one kernel
-                else:
-                    attend(pk, cache, l, packed_out=ws.packed)      # local splits merged by a launch behind
-                    dist.all_gather_into_tensor(gathered, ws.packed)
-                    pk.merge_gathered(gathered, out)
-            else:
-                attend(pk, cache, l, out=out)
+        for l in range(L):
+            layer(l, route)
+    per_layer_launches = 2 if world == 1 else (3 if route == "p2p" else 4)
     for c in st.caches:
         c.page_table, c.seqlens, c.max_pages = pt, seqlens, pages
     graphed = False
@@ -490,7 +626,7 @@ def run_sharded(st, args, dist, world):
         fn = step
         if not args.no_graph:
             # at 1/8 of the tokens per GPU a layer lasts tens of microseconds: the step is replayed as one
-            # CUDA graph (kernels, all-gather and all) so that the host is out of the loop, as the
+            # CUDA graph (kernels, exchange and all) so that the host is out of the loop, as the
             # reference times its kernels (scripts/bench_decode.py:29-49)
             try:
                 side = torch.cuda.Stream()
@@ -508,17 +644,108 @@ def run_sharded(st, args, dist, world):
                 sys.stderr.write("graph capture of the sharded step failed: %r\n" % (e,))
                 torch.cuda.synchronize()
         ms = timed(fn, args.steps, args.warmup, dist)
+        torch.cuda.synchronize()
+        out_timed = out.clone()                                     # what the timed replays left behind
+        per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
+        res = {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, L),
+               "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
+               "us_per_layer": round(ms * 1e3 / L, 2),
+               "scaling": "strong", "cuda_graph": graphed, "newest_token_written_by": "rank %d (fused prologue)" % (world - 1),
+               "collective": "none" if world == 1 else ("local merge + exchange + merge in one kernel over NVLink peer memory, [B,H,d+2] fp32 per layer"
+                                                        if ex is not None else "NCCL all_gather of [B,H,d+2] fp32 per layer + merge"),
+               "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
+               "bytes_per_gpu_per_layer": per_gpu_bytes,
+               "hbm_gbs_per_gpu": round(per_gpu_bytes * L / (ms * 1e-3) / 1e9, 1),
+               "gpu_launches": per_layer_launches * L * args.steps}
+
+        # ---- the check: nothing above looked at a result
+        chk = {"status_attention": [int(v) for v in ws.status.cpu()],
+               "status_exchange": [int(v) for v in ex.status.cpu()] if ex is not None else None}
+        ok = not any(chk["status_attention"]) and not (chk["status_exchange"] and any(chk["status_exchange"]))
+
+        def relerr(a, b):
+            return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-300))
+        check_layers = sorted({0, L - 1})
+        if world > 1:
+            # (1) the exchange routes against each other: peer-store kernel vs NCCL all-gather + merge
+            other = "nccl" if route == "p2p" else ("p2p" if ex is not None else None)
+            if other is not None:
+                worst = 0.0
+                for l in check_layers:
+                    layer(l, other)
+                    torch.cuda.synchronize()
+                    worst = max(worst, relerr(out[l], out_timed[l]))
+                chk["rel_p2p_vs_nccl"] = worst
+                ok = ok and worst <= 1e-5
+        if not st.simt:
+            # (2) every rank forms its shard's triples with the CUDA-core kernel; gathered, merged, compared with the
+            # tensor-core result of the timed step (tolerance of the attention output: 2e-3)
+            ws_s = pk0.workspace(B4, max(1, min(pages, (sms * 3) // B4)))
+            worst = 0.0
+            for l in check_layers:
+                pkl, cache = st.layers[l], st.caches[l]
+                pkl.absorb_step(st.q[l, :B4], qpos, ws_s, operand=False)
+                o_s = torch.empty((B4, st.n_q, st.d), dtype=torch.float32, device=dev)
+                if world == 1:
+                    pkl.attend_step(cache, ws_s, simt=True, out=o_s)
+                else:
+                    pkl.attend_step(cache, ws_s, simt=True, packed_out=ws_s.packed)
+                    dist.all_gather_into_tensor(gathered, ws_s.packed)
+                    pkl.merge_gathered(gathered, o_s)
+                torch.cuda.synchronize()
+                worst = max(worst, relerr(out_timed[l], o_s))
+            chk["rel_tc_vs_simt"] = worst
+            ok = ok and worst <= 2e-3
+        if dist is not None:                                        # every rank must agree that it is fine
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(int(flag.item()))
+        chk["ok"] = ok
+        chk["bounds"] = {"rel_p2p_vs_nccl": 1e-5, "rel_tc_vs_simt": 2e-3, "status": "all zero"}
+        res["check"] = chk
+        if not ok:
+            res["failed"] = "correctness check of the token-sharded step failed: value withdrawn"
+            res["value_unchecked"], res["value"] = res["value"], None
+
+        # ---- roofline of the attention launch on this rank's shard, eager with events (for --workload cfg4)
+        ev = []
+        for _ in range(3):
+            for l in range(L):
+                layer(l, route, ev)
+        torch.cuda.synchronize()
+        sel = ev[-L:]
+        a_ms = sum(a.elapsed_time(b) for a, b in sel) / len(sel)
+        pk_, src = peaks()
+        ach = per_gpu_bytes / (a_ms * 1e-3) / 1e9
+        res["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk_["hbm_gbs"], "unit": "GB/s",
+                           "frac": round(ach / pk_["hbm_gbs"], 4), "traffic": None, "peak_source": src,
+                           "kernel": "pkv_attn_%s" % args.algo, "bytes_per_launch": per_gpu_bytes,
+                           "us_per_launch": round(a_ms * 1e3, 2), "timed_over": "%d launches, eager, CUDA events" % len(sel)}
+        res["attention_us_per_layer"] = round(a_ms * 1e3, 2)
+
+        if want_e2e:
+            # through the host API with pinned host buffers: this step's hidden states, value rows and queries
+            # in, every layer's output back, inside the timed region
+            hx = torch.empty((L, B4, D_MODEL), dtype=st.x_new.dtype).pin_memory()
+            hv = torch.empty((L, B4, st.n_kv * st.d), dtype=st.v_new.dtype).pin_memory()
+            hq = torch.empty((L, B4, st.n_q, st.d), dtype=st.q.dtype).pin_memory()
+            ho = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+            hx.copy_(st.x_new[:, :B4]); hv.copy_(st.v_new[:, :B4]); hq.copy_(st.q[:, :B4])
+
+            def e2e_step():
+                st.x_new[:, :B4].copy_(hx, non_blocking=True)
+                st.v_new[:, :B4].copy_(hv, non_blocking=True)
+                st.q[:, :B4].copy_(hq, non_blocking=True)
+                fn()
+                ho.copy_(out, non_blocking=True)
+            ms_e = timed(e2e_step, args.steps, args.warmup, dist)
+            res["e2e"] = {"value": round(B4 / (ms_e * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms_e, 4),
+                          "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in (hx, hv, hq)),
+                          "d2h_bytes_per_step": ho.numel() * ho.element_size()}
     finally:
-        for c, s in zip(st.caches, saved):
-            c.page_table, c.seqlens, c.max_pages = s
-    per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
-    return {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, args.layers),
-            "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
-            "scaling": "strong", "cuda_graph": graphed, "newest_token_written_by": "rank %d (fused prologue)" % (world - 1),
-            "collective": "none" if world == 1 else ("local merge + exchange + merge in one kernel over NVLink peer memory, [B,H,d+2] fp32 per layer"
-                                                     if ex is not None else "NCCL all_gather of [B,H,d+2] fp32 per layer + merge"),
-            "allgather_bytes_per_gpu_per_layer": B4 * st.n_q * (st.d + 2) * 4 if world > 1 else 0,
-            "hbm_gbs_per_gpu": round(per_gpu_bytes * args.layers / (ms * 1e-3) / 1e9, 1)}
+        for c, s_ in zip(st.caches, saved):
+            c.page_table, c.seqlens, c.max_pages = s_
+    return res
 
 
 # ------------------------------------------------------------------------------------------------
@@ -569,6 +796,44 @@ def cpu_baseline(workload: str, budget_s: float = 15.0) -> dict:
             "sample": "1 layer x 1 sequence of T=%d (absorb + scores + softmax + P.V, fp32 on the dequantised latent, "
                       "bf16 V), median of %d runs = %.2f ms, scaled x%d sequences x%d layers"
                       % (c["context"], len(ts), t_unit * 1e3, c["batch"], N_LAYERS)}
+
+
+def cpu_baseline_cfg1(budget_s: float = 6.0) -> dict:
+    """BASELINE configuration 1 in full on the host cores, nothing scaled: one layer, B=1, T=4096, fp32 latent
+    without quantisation -- PhasorKey.write of the whole context, then absorb + scores + softmax + P.V of one
+    decode step at position 4096 (phasorkv/latent.py:61-88 through the oracle port)."""
+    from oracle import phasor_oracle as po
+    from phasorkv_b200 import synth
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    T = synth.CONFIGS["cfg1"]["context"]
+    spec = synth.make_layer("cfg1", 0)
+    pk = po.PhasorKeyOracle.from_spec(spec)
+    gen = torch.Generator().manual_seed(101)
+    x = synth.make_hidden(gen, T)
+    V = synth.make_values(gen, T, spec.n_kv, spec.head_dim)
+    q = synth.make_query(gen, 1, spec.n_q, spec.head_dim)[0]
+    ph_k = po.rope_phasors(spec.inv_freq, torch.arange(T))
+    ph_q = po.rope_phasors(spec.inv_freq, torch.tensor([T]))
+
+    def unit():
+        t0 = time.perf_counter()
+        rows = pk.write(x, ph_k)
+        t1 = time.perf_counter()
+        po.decode_step(pk, q, ph_q, rows, V, spec.head_dim)
+        return t1 - t0, time.perf_counter() - t1
+    unit(); unit()
+    tw, td = [], []
+    t_end = time.perf_counter() + budget_s
+    while len(tw) < 5 or (time.perf_counter() < t_end and len(tw) < 200):
+        a, b = unit()
+        tw.append(a); td.append(b)
+    tw.sort(); td.sort()
+    w_ms, d_ms = tw[len(tw) // 2] * 1e3, td[len(td) // 2] * 1e3
+    return {"write_ms": round(w_ms, 3), "decode_ms": round(d_ms, 3), "value": round(1.0 / (d_ms * 1e-3), 2),
+            "unit": "tokens/s (one layer, B=1)", "cores": cores, "kind": "port",
+            "sample": "cfg1 in full, median of %d runs: write of T=%d tokens %.2f ms; one decode step (absorb + scores + "
+                      "softmax + P.V, fp32, no quantisation) %.2f ms; nothing scaled" % (len(tw), T, w_ms, d_ms)}
 
 
 def run_reference(args):

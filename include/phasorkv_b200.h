@@ -353,6 +353,11 @@ int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache_t* cache, 
                             const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
                             int32_t batch, int32_t n_split, float* out_dev, int32_t* status_dev, void* stream);
 
+/* Measurement aid (no counterpart in the reference): reads `bytes` (16-byte aligned buffer) once with plain
+ * 16-byte loads from every SM and discards them; sink_dev is one uint32 the kernel may add to.  Timed by
+ * the benchmark beside the attention kernel: the bandwidth a pure reader gets on this GPU. */
+int pkv_read_probe(const void* src_dev, int64_t bytes, uint32_t* sink_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

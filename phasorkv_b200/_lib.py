@@ -92,6 +92,7 @@ SIGNATURES = {
                                      c_void_p, c_void_p]),
     "pkv_absorb_rows_f64": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                       c_int32, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
+    "pkv_read_probe": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),
 }

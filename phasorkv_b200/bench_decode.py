@@ -65,30 +65,42 @@ def result_key(name: str, T: int, B: int, opts: Dict[str, object]) -> str:
     return f"{name}|T{T}|B{B}|" + ",".join(f"{k}={v}" for k, v in opts.items())
 
 
-def graph_time(fn, iters: int = 20, warmup: int = 3) -> float:
-    """ms per call of `fn` replayed as one CUDA graph (the reference's timing method)."""
-    import torch
-    s = torch.cuda.Stream()
-    s.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(s):
-        for _ in range(warmup):
-            fn()
-    torch.cuda.current_stream().wait_stream(s)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        fn()
-    for _ in range(warmup):
-        g.replay()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        g.replay()
-    b.record()
-    torch.cuda.synchronize()
-    del g
-    return a.elapsed_time(b) / iters
+class StepGraph:
+    """A decode step captured once as a CUDA graph, replayed for timing: the host is out of the loop, which
+    is how the reference times its kernels too (one graph over all layers, scripts/bench_decode.py:29-49)."""
+
+    def __init__(self, step_fn, eager_calls: int = 2):
+        import torch
+        self._torch = torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(eager_calls):                # lazy initialisation happens outside the capture
+                step_fn()
+        side.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=side):
+            step_fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+    def median_ms(self, replays: int = 20, rounds: int = 5) -> float:
+        """Median over `rounds` event pairs, each around replays / rounds back-to-back replays."""
+        torch = self._torch
+        per = max(1, replays // rounds)
+        self.graph.replay()
+        self.graph.replay()
+        pairs = []
+        for _ in range(rounds):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(per):
+                self.graph.replay()
+            t1.record()
+            pairs.append((t0, t1))
+        torch.cuda.synchronize()
+        ms = sorted(a.elapsed_time(b) / per for a, b in pairs)
+        return ms[len(ms) // 2]
 
 
 def bench_latent(config: str, n_layers: int, B: int, T: int, algo: str, n_split: int = 0, iters: int = 20):
@@ -117,35 +129,36 @@ def bench_latent(config: str, n_layers: int, B: int, T: int, algo: str, n_split:
             w = ws[l & 1]
             pk.absorb_step(q[l], pos, w, operand=not simt)
             pk.attend_step(c, w, simt=simt, out=outs[l], after_absorb=True)
-    ms = graph_time(step, iters=iters)
+    ms = StepGraph(step).median_ms(replays=iters)
     assert all(int(w.status.abs().sum()) == 0 for w in ws), "a kernel reported a give-up"
     del caches
     torch.cuda.empty_cache()
     return ms, dict(algo=algo, n_split=ns)
 
 
-def bench_sdpa(B: int, T: int, n_layers: int, n_q: int, n_kv: int, d: int, budget: float) -> Optional[float]:
-    """torch's bf16 SDPA on a dense GQA cache: as many layers as fit the budget, scaled to the depth."""
+def dense_sdpa_ms(B: int, T: int, n_layers: int, n_q: int, n_kv: int, d: int, budget_bytes: float) -> Optional[float]:
+    """Yardstick: torch's bf16 scaled-dot-product attention (a library kernel) decoding over a dense grouped-query
+    cache of the same shape. One allocation holds as many layers as the budget allows; the time is scaled to
+    the full depth. None when not even one layer fits or the backend refuses the call."""
     import torch
-    per_layer = 2 * B * T * n_kv * d * 2
-    L = int(min(n_layers, budget // per_layer))
-    if L < 1:
+    layer_bytes = 2 * 2 * B * T * n_kv * d                 # keys and values, two bytes each
+    fit = min(n_layers, int(budget_bytes // layer_bytes))
+    if fit <= 0:
         return None
-    kv = [(torch.randn(B, n_kv, T, d, device="cuda").to(torch.bfloat16),
-           torch.randn(B, n_kv, T, d, device="cuda").to(torch.bfloat16)) for _ in range(L)]
-    q = torch.randn(B, n_q, 1, d, device="cuda").to(torch.bfloat16)
+    dense = torch.empty((fit, 2, B, n_kv, T, d), dtype=torch.bfloat16, device="cuda").normal_()
+    query = torch.empty((B, n_q, 1, d), dtype=torch.bfloat16, device="cuda").normal_()
 
-    def run():
-        for k, v in kv:
-            torch.nn.functional.scaled_dot_product_attention(q, k, v, enable_gqa=True)
+    def step():
+        for layer in dense:
+            torch.nn.functional.scaled_dot_product_attention(query, layer[0], layer[1], enable_gqa=True)
+    ms = None
     try:
-        t = graph_time(run) * n_layers / L
-    except Exception as e:                              # backend without GQA / graph capture
-        print("  sdpa failed:", type(e).__name__, str(e)[:120], flush=True)
-        t = None
-    del kv
+        ms = StepGraph(step).median_ms() * n_layers / fit
+    except RuntimeError as err:
+        print(f"  dense SDPA yardstick skipped ({type(err).__name__}: {str(err)[:100]})", flush=True)
+    del dense
     torch.cuda.empty_cache()
-    return t
+    return ms
 
 
 def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
@@ -191,8 +204,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         shape = shapes[name]
         bpt, flops = bytes_per_token(shape), flops_per_token(shape)
         l0 = shape["layers"]["0"]
-        # the tensor-core attention kernel needs 4 or 8 query heads per kv head; MHA runs the CUDA-core kernel
-        algo = args.algo if l0["n_q"] // l0["n_kv"] in (4, 8) else "simt"
+        # the tensor-core attention kernel takes 1, 4 or 8 query heads per kv head; other groupings run the CUDA-core kernel
+        rep = l0["n_q"] // l0["n_kv"]
+        algo = args.algo if rep in (1, 4, 8) else "simt"
+        groups = 4 if (rep == 1 and algo == "tc") else 1       # one query head per kv head: 4 CTAs per (sequence, split)
         print(f"{name}: {bpt / 1024:.1f} KiB/token (NVFP4 latent + bf16 V, {args.layers} layers), "
               f"{flops / 1e6:.2f} MFLOP/token", flush=True)
         for T in lens:
@@ -203,7 +218,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                 ns = args.splits
                 if not ns:                                # the key must be known before the run: same rule as default_splits
                     sms = torch.cuda.get_device_properties(0).multi_processor_count
-                    ns = max(1, min((T + 127) // 128, (sms * (3 if algo == "simt" else 1)) // B))
+                    ns = max(1, min((T + 127) // 128, (sms * (3 if algo == "simt" else 1)) // (B * groups)))
                 key = result_key(name, T, B, dict(algo=algo, n_split=ns))
                 if key in res:
                     continue
@@ -220,7 +235,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                     key = f"sdpa-bf16|T{T}|B{B}"
                     if key in res:
                         continue
-                    t = bench_sdpa(B, T, args.layers, l0["n_q"], l0["n_kv"], l0["head_dim"], budget)
+                    t = dense_sdpa_ms(B, T, args.layers, l0["n_q"], l0["n_kv"], l0["head_dim"], budget)
                     if t is None:
                         continue
                     dense_bpt = args.layers * 2 * l0["n_kv"] * l0["head_dim"] * 2
