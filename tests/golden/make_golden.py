@@ -6,6 +6,7 @@ sizes are small so the fixtures stay a few hundred KB.
 
   PHASORKV_REFERENCE=<checkout of PhasorKV> python tests/golden/make_golden.py
   PHASORKV_SCALE_UP=1 PHASORKV_REFERENCE=<checkout> python tests/golden/make_golden.py   # nvfp4_cases_scale_up.npz
+  PHASORKV_REFERENCE=<checkout> python tests/golden/make_golden.py attend_merge          # only the named fixtures
 """
 import os
 import sys
@@ -209,9 +210,67 @@ def phasorkey_factorized():
     print("phasorkey_factorized")
 
 
+def attend_merge():
+    """Softmax . V as the reference forms it (metrics.LayerReference: logits * d^-0.5, log_softmax, P @ V with
+    the kv heads repeated over their query heads, phasorkv/metrics.py:23,29-35) for one decode query over T
+    tokens, and the split-T combine: the three statements that close dense_decode
+    (phasorkv/kernels/dense_attn.py:72-74) are taken from its source and executed here on per-split
+    (max, sum, output) triples in base 2, which is how its kernel leaves them (LOG2E in qk_scale, :68)."""
+    import inspect
+    import textwrap
+    from phasorkv import metrics
+    from phasorkv.kernels import dense_attn
+    g = torch.Generator().manual_seed(4404)
+    D, n_q, n_kv, d, T = 64, 8, 2, 32, 96
+    h = d // 2
+    inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(h, dtype=torch.float64) / d)
+    ph = rope_phasors(_Rotary(inv_freq, 1.0), torch.arange(T))
+    x = torch.randn(T, D, generator=g)
+    Wq = torch.randn(n_q * d, D, generator=g) * 0.6 / D ** 0.5            # peaked enough that the split maxima differ
+    Wk = torch.randn(n_kv * d, D, generator=g) * 4.0 / D ** 0.5
+    Wv = torch.randn(n_kv * d, D, generator=g) / D ** 0.5
+    qpos = torch.tensor([T - 1])                                           # one query row that sees every token
+    ref = metrics.LayerReference([x], Wq, Wk, Wv, ph.to(torch.complex64), qpos, n_kv, d)
+    it = ref.items[0]
+    S_scaled = it["S"][:, 0]                                               # [H, T] logits * d^-0.5
+    O = it["O"][:, 0]                                                      # [H, d]
+    V = (x @ Wv.T).reshape(T, n_kv, d)                                     # [T, n_kv, d] before the head expansion
+    S_unscaled = S_scaled / ref.scale
+    # per-split triples in base 2 over ragged splits, then the reference's own merge statements
+    bounds = [0, 17, 48, 49, T]
+    s2 = S_scaled.double() * dense_attn.LOG2E
+    Vh = it["v"].double()                                                  # [H, T, d]
+    om, ol, oo = [], [], []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        m = s2[:, lo:hi].amax(-1)
+        p = torch.exp2(s2[:, lo:hi] - m[:, None])
+        om.append(m); ol.append(p.sum(-1)); oo.append(torch.einsum("ht,htd->hd", p, Vh[:, lo:hi]))
+    om, ol, oo = torch.stack(om)[None].float(), torch.stack(ol)[None].float(), torch.stack(oo)[None].float()   # [1, S, H(, d)]
+    tail = inspect.getsource(dense_attn.dense_decode).rstrip().splitlines()[-3:]
+    code = textwrap.dedent("\n".join(tail)).replace("return ", "merged = ")
+    assert code.count("merged = ") == 1 and "torch.exp2(om - M)" in code, code
+    ns = dict(torch=torch, om=om, ol=ol, oo=oo)
+    exec(code, ns)
+    merged = ns["merged"][0]                                               # [H, d]
+    err = ((merged.double() - O.double()).norm() / O.double().norm()).item()
+    print("attend_merge: merged splits vs LayerReference O", err)
+    assert err < 1e-5
+    np.savez_compressed(os.path.join(HERE, "attend_merge.npz"), S_unscaled=S_unscaled.numpy(), S_scaled=S_scaled.numpy(),
+                        V=V.numpy(), O=O.numpy(), lp=it["lp"][:, 0].numpy(), bounds=np.array(bounds), om=om[0].numpy(),
+                        ol=ol[0].numpy(), oo=oo[0].numpy(), merged=merged.numpy(), dims=np.array([D, n_q, n_kv, d, T]))
+    print("attend_merge")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
-    nvfp4_cases()
+    only = set(sys.argv[1:])                                  # optional: names of the fixtures to (re)write
+    want = lambda name: not only or name in only
+    if want("nvfp4_cases"):
+        nvfp4_cases()
     if not quant.SCALE_UP:                                    # PHASORKV_SCALE_UP=1: only the quantiser vectors differ
-        phasorkey_injected()
-        phasorkey_factorized()
+        if want("phasorkey_injected"):
+            phasorkey_injected()
+        if want("phasorkey_factorized"):
+            phasorkey_factorized()
+        if want("attend_merge"):
+            attend_merge()

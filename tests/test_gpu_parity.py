@@ -226,10 +226,23 @@ def test_fused_write_against_oracle(config, x_dtype):
         assert (got != ref_codes).float().mean() < 2e-3
         assert (scales.cpu() != ref_scales).float().mean() < 2e-3
         assert rel(xhat.cpu(), ref_hat) < 5e-3
+        # ... and where a code differs it is the neighbouring E2M1 level, never further (signed level index)
+        level = lambda c: torch.where((c & 8) != 0, -(c & 7).to(torch.int32), (c & 7).to(torch.int32))
+        assert int((level(got) - level(ref_codes)).abs().max()) <= 1
+        sb, rb = scales.cpu().to(torch.int32), ref_scales.to(torch.int32)
+        assert int((sb - rb).abs().max()) <= 1                               # neighbouring E4M3 bytes at most
         out = torch.empty((sc.seqlens[b], sc.spec.cache_width), device="cuda")
         sc.pk.write_paged(sc.cache, sc.x[b].cuda(), sc.pos[b].to(torch.int32).cuda(), sc.slots_of(b), latent_out=out)
         # fp32 x: CUDA-core FMA chain; bf16 x: tensor cores, factors as three bf16 terms, fp32 accumulation in TMEM
         assert rel(out.cpu(), sc.rows_ref[b]) < (5e-6 if x_dtype == torch.float32 else 3e-5)
+        # The stored bits are exactly the reference quantiser's bits of the fp32 rows the kernel itself reports:
+        # the bit-exact quantiser (checked against the reference's vectors) fed with them gives the same bytes,
+        # and so does the oracle. What differs from the oracle's write is only the summation order of x . B^T.
+        _, codes2, scales2 = sc.cache.read(sc.slots_of(b), sc.second)
+        _, q_codes, q_scales = _quantise_and_read(out, sc.second)
+        assert torch.equal(codes2.cpu(), q_codes) and torch.equal(scales2.cpu(), q_scales)
+        o_codes, o_scales, _ = po.nvfp4_quantize(out.cpu(), torch.tensor([sc.second]))
+        assert torch.equal(codes2.cpu(), po.pack_nibbles(o_codes)) and torch.equal(scales2.cpu(), o_scales)
 
 
 def test_absorb_batch_against_oracle():
@@ -729,7 +742,7 @@ def test_hf_llama_attention_patch_decodes_like_the_model():
     print("decode logits rel errors", errs)
     assert all(int(st.ws.status.abs().sum()) == 0 for st in patch.states.values())
     assert patch.states[0].length == 204
-    assert max(errs) < 1e-2                                                    # measured 2.4e-3
+    assert max(errs) < 5e-3                                                    # measured 2.4e-3
     for u in undos:
         u()
     assert "forward" not in model.model.layers[0].self_attn.__dict__ and not patch.states

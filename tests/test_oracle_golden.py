@@ -133,3 +133,27 @@ def test_split_merge_equals_unsplit():
     parts = [po.partial_attend(S[:, a:b], V[a:b], n_kv, d) for a, b in ((0, 7), (7, 128), (128, 300))]
     m, l, o = (torch.stack(t) for t in zip(*parts))
     assert torch.allclose(po.merge_partials(m, l, o), full, rtol=2e-5, atol=1e-6)
+
+
+def test_attend_and_split_merge_against_reference_vectors():
+    """softmax . V and the split-T combine of the oracle against what the reference's own code produced:
+    `metrics.LayerReference` for the attention output of one decode query, and the closing statements of
+    `dense_decode` (executed from its source by the generator) for the merge of ragged splits."""
+    g = _load("attend_merge.npz")
+    D, n_q, n_kv, d, T = (int(v) for v in g["dims"])
+    S, V = torch.from_numpy(g["S_unscaled"]), torch.from_numpy(g["V"])
+    O = po.attend(S, V, n_kv, d)
+    assert float((O - torch.from_numpy(g["O"])).norm() / torch.from_numpy(g["O"]).norm()) < 2e-6
+    bounds = g["bounds"].tolist()
+    ms, ls, os_ = [], [], []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        m, l, o = po.partial_attend(S[:, lo:hi], V[lo:hi], n_kv, d)
+        ms.append(m); ls.append(l); os_.append(o)
+    m, l, o = torch.stack(ms), torch.stack(ls), torch.stack(os_)
+    assert torch.allclose(m, torch.from_numpy(g["om"]), rtol=0, atol=2e-5)          # base-2 maxima of each split
+    assert torch.allclose(l, torch.from_numpy(g["ol"]), rtol=2e-5, atol=0)
+    assert torch.allclose(o, torch.from_numpy(g["oo"]), rtol=1e-4, atol=1e-5)
+    # the merge itself on the reference's own triples: same statements, same bits
+    merged = po.merge_partials(torch.from_numpy(g["om"]), torch.from_numpy(g["ol"]), torch.from_numpy(g["oo"]))
+    assert torch.equal(merged, torch.from_numpy(g["merged"]))
+    assert float((po.merge_partials(m, l, o) - O).norm() / O.norm()) < 2e-6
