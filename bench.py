@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-chunk-write", action="store_true", help="cfg5 without its 2048-token chunk write per step")
+    ap.add_argument("--v-format", default="bf16", choices=["bf16", "q3", "q2"],
+                    help="V pages: bf16 (the configurations as stated) or per-token 3-bit / 2-bit tiers (quantised V)")
     ap.add_argument("--algo", default=os.environ.get("PKV_BENCH_ALGO", "tc"), choices=["tc", "simt"])
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--batch", type=int, default=0, help="override the configuration's batch (profiling)")
@@ -119,7 +121,7 @@ class Stack:
     """32 layers of one configuration with their caches filled by real writes of seeded hidden states."""
 
     def __init__(self, config: str, n_layers: int, device, algo: str, seed: int, batch: int = 0, context: int = 0,
-                 n_split: int = 0, chunk_write: bool = True):
+                 n_split: int = 0, chunk_write: bool = True, v_bits: int = 0):
         from phasorkv_b200 import synth
         from phasorkv_b200.latent import PhasorKey
         c = synth.CONFIGS[config]
@@ -159,7 +161,8 @@ class Stack:
             pk.calibrate_second(rows)
         del rows, xc
         for pk in self.layers:
-            self.caches.append(pk.new_cache(self.B, self.T))
+            self.caches.append(pk.new_cache(self.B, self.T, v_bits=v_bits))
+        self.v_bits = v_bits
         chunk = 16384
         for b in range(self.B):
             for t0 in range(0, self.T, chunk):
@@ -234,7 +237,7 @@ class Stack:
                 n += 1
             elif fused:                                               # newest token's write + absorb: one launch
                 pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l])
-                n += 1
+                n += 2 if self.v_bits else 1                          # quantised V pages: their own writer launch
             else:
                 if write:
                     pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
@@ -266,8 +269,12 @@ class Stack:
     def bytes_k(self):
         return self.B * self.T * (self.W // 2 + self.W // 16)
 
+    def bytes_v_per_token(self):
+        # bf16 rows, or per kv head 64 bytes of codes + one bf16 scale
+        return self.n_kv * (66 if self.v_bits else self.d * 2)
+
     def bytes_full(self):
-        return self.bytes_k() + self.B * self.T * self.n_kv * self.d * 2
+        return self.bytes_k() + self.B * self.T * self.bytes_v_per_token()
 
 
 def timed(fn, steps, warmup, dist=None):
@@ -354,7 +361,8 @@ def run_b200(args):
 
     sharded_headline = args.workload == "cfg4"          # the token-sharded step is the line; its pools are cfg2's
     st = Stack("cfg2" if sharded_headline else args.workload, args.layers, device, args.algo, seed=1234 + rank,
-               batch=args.batch, context=args.context, n_split=args.splits, chunk_write=not args.no_chunk_write)
+               batch=args.batch, context=args.context, n_split=args.splits, chunk_write=not args.no_chunk_write,
+               v_bits={"bf16": 0, "q3": 3, "q2": 2}[args.v_format])
     torch.cuda.synchronize()
     pk, src = peaks()
     L = args.layers
@@ -465,7 +473,7 @@ def run_b200(args):
 
     # ---- token-sharded long context (cfg4): the same pools viewed as B=4, T=131072/world per rank
     sharded = None
-    if not args.no_sharded and args.workload == "cfg2" and not args.batch and not args.context:
+    if not args.no_sharded and args.workload == "cfg2" and not args.batch and not args.context and not st.v_bits:
         try:
             sharded = run_sharded(st, args, dist, world)
             sharded.pop("roofline", None)
@@ -478,7 +486,7 @@ def run_b200(args):
     # the split partials written (B x n_split x 32 x 130 floats), which do not.
     traffic = None
     base = profile_traffic_base()
-    if base and args.algo == "tc" and st.W == 256 and st.n_kv == 8:
+    if base and args.algo == "tc" and st.W == 256 and st.n_kv == 8 and not st.v_bits:
         traffic = int(base[0] * (st.B * st.T) / base[1] + st.B * st.n_split * 32 * 130 * 4)
     achieved = st.bytes_full() / (attn_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -490,15 +498,17 @@ def run_b200(args):
     if peak_read:
         roof["peak_read_gbs"] = peak_read              # a read-only stream kernel of the library, same run
         roof["frac_of_read_peak"] = round(achieved / peak_read, 4)
+    v_desc = "bf16 V" if not st.v_bits else "V as per-token %d-bit codes + bf16 scale per (token, kv head)" % st.v_bits
     line = {
         "metric": "decode tokens/s (B=%d, T=%d, %d layers; K-path us/layer and HBM GB/s beside it)" % (st.B, st.T, L),
         "value": round(world * st.B / (ms_step * 1e-3), 2), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V",
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; %s" % v_desc,
         "data": "synthetic",
-        "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, bf16 V %dx%d, %d layers%s"
+        "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, %s %dx%d, %d layers%s"
                    % (args.workload, "7B multi-head-attention" if st.n_kv == st.n_q else "Llama-3.1-8B", st.B, st.T, st.W,
-                      st.n_kv, st.d, L, (", plus a %d-token chunk write per sequence per layer" % st.chunk) if st.chunk else ""),
+                      v_desc, st.n_kv, st.d, L, (", plus a %d-token chunk write per sequence per layer" % st.chunk) if st.chunk else ""),
                    "algo": args.algo, "n_split": st.n_split, "parallelism": "batch-parallel x%d" % world,
                    "l2": "inputs larger than L2 (%.2f GB streamed per layer, %.1f GB per step)"
                          % (st.bytes_full() / 1e9, L * st.bytes_full() / 1e9)},

@@ -47,7 +47,7 @@ class LayerHost(ctypes.Structure):
 
 class Cache(ctypes.Structure):
     _fields_ = [("latent_dev", c_void_p), ("v_dev", c_void_p), ("n_pages", c_int32), ("W", c_int32),
-                ("n_kv", c_int32), ("head_dim", c_int32)]
+                ("n_kv", c_int32), ("head_dim", c_int32), ("vq_dev", c_void_p), ("v_bits", c_int32)]
 
 
 #: name -> (restype, argtypes); the complete exported surface of include/phasorkv_b200.h
@@ -92,6 +92,9 @@ SIGNATURES = {
                                      c_void_p, c_void_p]),
     "pkv_absorb_rows_f64": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                       c_int32, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
+    "pkv_vq_page_bytes": (c_int64, [c_int32, c_int32]),
+    "pkv_vq_write": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p]),
+    "pkv_vq_read": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_read_probe": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p]),
     "pkv_merge": (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                             c_void_p]),

@@ -244,7 +244,8 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
         return PKV_ERR_INVALID;
     if (layer->n_q != NQ || layer->head_dim != DH) return PKV_ERR_UNSUPPORTED;
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
-    if (with_v && !cache->v_dev) return PKV_ERR_INVALID;
+    if (with_v && !(cache->v_bits ? cache->vq_dev : cache->v_dev)) return PKV_ERR_INVALID;
+    if (with_v && cache->v_bits && (flags & PKV_ATTN_SIMT)) return PKV_ERR_UNSUPPORTED;   // quantised V pages: tensor-core kernel only
     if (batch == 0) return PKV_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (!(flags & PKV_ATTN_SIMT))
@@ -294,7 +295,7 @@ extern "C" int pkv_decode_attn_q(const pkv_layer_t* layer, const pkv_cache_t* ca
         return PKV_ERR_INVALID;
     if (layer->n_q != NQ || layer->head_dim != DH) return PKV_ERR_UNSUPPORTED;
     if (flags & PKV_ATTN_SIMT) return PKV_ERR_UNSUPPORTED;             // the CUDA-core kernel takes the fp32 absorbed query
-    if (!(flags & PKV_ATTN_SCORES_ONLY) && !cache->v_dev) return PKV_ERR_INVALID;
+    if (!(flags & PKV_ATTN_SCORES_ONLY) && (cache->v_bits || !cache->v_dev)) return cache->v_bits ? PKV_ERR_UNSUPPORTED : PKV_ERR_INVALID;
     return pkv_attn_tc_launch(layer, cache, nullptr, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, partials_dev,
                               scores_out_dev, scores_stride, status_dev, out_dev, (cudaStream_t)stream, q_dev,
                               query_positions_dev);

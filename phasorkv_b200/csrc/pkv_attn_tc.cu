@@ -33,11 +33,17 @@ using namespace pkv;
 
 constexpr int NQ = 32, DH = 128;
 constexpr int NK_STAGES = 2, NV_STAGES = 4;
+// quantised V pages: raw tiles (codes + scales of one page and kv head) land in a ring of NVR stages; four
+// converter warps turn each into the bf16 operand tile, of which NVB_Q stages are kept
+constexpr int NVR = 4, NVB_Q = 3;
+constexpr int RAW_BYTES = PKV_VQ_TILE_BYTES;
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
 constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
 constexpr int NTHREADS_SCORES = 11 * 32;      // scores only: two softmax groups that take alternate pages
+constexpr int NTHREADS_VQ = 12 * 32;          // quantised V: warps 0-2 as always (3 idle), 4-7 softmax, 8-11 converters
+template <bool WV, bool VQ> constexpr int n_threads() { return VQ ? NTHREADS_VQ : (WV ? NTHREADS : NTHREADS_SCORES); }
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -52,8 +58,9 @@ constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set
 constexpr uint32_t TM_SFB = 432;      // 16 per MMA issuer (two in scores-only mode): query scale factors, a 4-column group per K step
 constexpr uint32_t TM_COLS = 512;
 
-template <int WP>
+template <int WP, bool VQ = false>
 struct Cfg {
+    static constexpr int NVS = VQ ? NVB_Q : NV_STAGES;           // bf16 V stages
     static constexpr int RB = WP / 2;                          // code bytes per row
     static constexpr int KB = WP / 64;                         // K = 64 MMA steps
     static constexpr int CODES = PKV_PAGE_TOKENS * RB;
@@ -62,7 +69,8 @@ struct Cfg {
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = ((QBLOB + 1023) / 1024) * 1024;
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
-    static constexpr int P_OFF = V_OFF + NV_STAGES * V_STAGE_BYTES;
+    static constexpr int R_OFF = V_OFF + NVS * V_STAGE_BYTES;    // raw tiles of quantised V pages
+    static constexpr int P_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
     static constexpr int SMEM = X_OFF + 4096;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
@@ -72,6 +80,7 @@ struct Cfg {
 struct Extra {                       // lives at X_OFF
     uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_STAGES], v_empty[NV_STAGES];
     uint64_t s_full[NSB_S], s_empty[NSB_S], p_full[2], pv_done[2];
+    uint64_t vr_full[NVR], vr_empty[NVR];                        // raw tiles of quantised V pages
     uint64_t sm_bar;                 // rendezvous of the 128 softmax threads (bounded, unlike bar.sync)
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -99,14 +108,27 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
 }
 
 
-template <int WP, int REP, bool WV, bool INLQ>
-__global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_tc_kernel(
+// Build with -DPKV_TIMELINE to turn `scores_out` into a table of time stamps, 16 per CTA (clock64 unless noted):
+// 0 entry, 1 entry (globaltimer ns), 2 set-up done, 3 lengths known, 4 first page asked for, 5 query asked for,
+// 6 last page asked for, 7 query there, 8 first page there, 9 last scores committed, 10 first scores seen,
+// 11 last page reduced, 12 partial written, 13 all roles done, 14 exit (globaltimer ns), 15 SM id.
+// A development aid for the fixed cost of a launch; the library is never shipped with it.
+#ifdef PKV_TIMELINE
+#define PKV_TL(slot) do { tl_buf[slot] = clock64(); } while (0)
+__device__ __forceinline__ long long pkv_globaltimer() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#else
+#define PKV_TL(slot) do { } while (0)
+#endif
+
+template <int WP, int REP, bool WV, bool INLQ, bool VQ>
+__global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap kmap,
     const __grid_constant__ CUtensorMap qmap, const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
     int32_t* __restrict__ status, const pkv_absorb_impl::Args qa) {
-    using C = Cfg<WP>;
+    using C = Cfg<WP, VQ>;
+    static_assert(!VQ || WV, "quantised V pages only matter when V is read");
     // qa.q set: the kernel absorbs the raw queries itself (softmax group 0, pkv_absorb_impl::body_tile) instead
     // of loading the operand a pkv_absorb launch left in global memory
     constexpr bool inline_q = INLQ;                  // a separate instantiation: the plain kernels do not carry this code
@@ -123,13 +145,19 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     Extra* X = reinterpret_cast<Extra*>(smem + C::X_OFF);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y;
+#ifdef PKV_TIMELINE
+    long long* tl_buf = reinterpret_cast<long long*>(scores_out) + ((size_t)(blockIdx.z * gridDim.y + b) * gridDim.x + split) * 16;
+    scores_out = nullptr;
+    if (tid == 0) { PKV_TL(0); tl_buf[1] = pkv_globaltimer(); uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); tl_buf[15] = sm; }
+#endif
     pkv_grid_launch_dependents();
 
     // ---- prologue that touches no global memory: barriers, tensor memory
     if (tid == 0) {
         mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
-        for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
+        for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], VQ ? 128 : 1); mbar_init(&X->v_empty[s], 1); }
+        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 128); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], 1); }
         mbar_init(&X->sm_bar, WV ? 128 : 256);
@@ -142,6 +170,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     tc_fence_after_sync();
     const uint32_t tb = X->tmem_base;
     const uint32_t sbase = smem_u32(smem);
+    if (tid == 0) PKV_TL(2);
 
     // Normally everything waits here for the kernel launched before this one. With PKV_ATTN_EARLY_STREAM the
     // caller vouches that that kernel only produces the query operand (it is pkv_absorb): the cache, the
@@ -154,6 +183,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
     if (!early) pkv_grid_wait();
 
     const int T = seqlens[b];
+    if (tid == 0) PKV_TL(3);
     const int npages = min((T + PKV_PAGE_TOKENS - 1) / PKV_PAGE_TOKENS, max_pages);
     const int pps = (npages + n_split - 1) / n_split;
     const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
@@ -176,6 +206,14 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         return;
     }
 
+    // Quantised V: the three warpgroups (producers + MMA issuer | softmax | converters) re-divide the register
+    // file: the softmax warps keep 32 heads' statistics in registers, the others need few
+    constexpr int W_SM = VQ ? 4 : 3;                  // first softmax warp
+    if constexpr (VQ) {
+        if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        else if (warp < 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 248;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 128;");
+    }
     if (warp == 0) {
         // ================================================================== K producer
         // The page indices are fetched 32 at a time by the whole warp (one coalesced load, one round trip per
@@ -196,6 +234,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                         mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
                         tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
                         q_sent = true;
+                        PKV_TL(5);
                     }
                     if (!waited && tail_written && i < P && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                     if (i < P) {
@@ -212,6 +251,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                             // measured at ~16 GB/s per SM, tiled loads are not limited that way)
                             tma_load_2d(smem + C::K_OFF + s * C::PAGE, &kmap, 0, pidx * (C::PAGE / 128), &X->k_full[s]);
                             issued = i + 1;
+                            if (i == 0) PKV_TL(4);
+                            if (i == P - 1) PKV_TL(6);
                         }
                     }
                 }
@@ -239,6 +280,15 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                         } else {
                             if (!waited && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                             for (int g = 0; g < NKV; ++g) {
+                                if constexpr (VQ) {                  // the tile as stored: codes and scales of (page, kv head)
+                                    const int j = i * NKV + g, s = j % NVR;
+                                    if (j >= NVR && !wait_or_abort(&X->vr_empty[s], ((j / NVR) - 1) & 1, X, status, 21)) { stop = true; break; }
+                                    mbar_arrive_expect_tx(&X->vr_full[s], RAW_BYTES);
+                                    tma_load_2d(smem + C::R_OFF + s * RAW_BYTES, &vmap, 0, (pidx * (NQ / REP) + g_base + g) * (RAW_BYTES / 128),
+                                                &X->vr_full[s]);
+                                    issued = j + 1;
+                                    continue;
+                                }
                                 const int j = i * NKV + g, s = j % NV_STAGES;
                                 if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }
                                 uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
@@ -252,9 +302,14 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                     stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
                 }
             }
-            if (lane == 0 && X->abort_flag)
-                for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
-                    mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
+            if (lane == 0 && X->abort_flag) {
+                if constexpr (VQ) {
+                    for (int j = max(0, issued - NVR); j < issued; ++j) mbar_wait(&X->vr_full[j % NVR], (j / NVR) & 1, 1u << 16);
+                } else {
+                    for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
+                        mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
+                }
+            }
         }
     } else if (warp == 2 || warp == 1) {
         // ================================================================== MMA issuer
@@ -270,6 +325,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
             constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
             bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
+            if (warp == 2) PKV_TL(7);
             if (ok) {
                 tc_fence_after_sync();
                 for (int k = 0; k < C::KB; ++k)
@@ -281,8 +337,8 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 if (!wait_or_abort(&X->p_full[pb], (i >> 1) & 1, X, status, 31)) return false;
                 tc_fence_after_sync();
                 for (int g = 0; g < NKV; ++g) {
-                    const int j = i * NKV + g, s = j % NV_STAGES;
-                    if (!wait_or_abort(&X->v_full[s], (j / NV_STAGES) & 1, X, status, 32)) return false;
+                    const int j = i * NKV + g, s = j % C::NVS;
+                    if (!wait_or_abort(&X->v_full[s], (j / C::NVS) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
                     const uint32_t va = sbase + C::V_OFF + s * V_STAGE_BYTES;
                     // B operand: 16 rows = the hi weights of the 8-head group holding this kv head's heads, then their lo parts
@@ -306,6 +362,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 ok = wait_or_abort(&X->k_full[s], k_phase, X, status, 33);
                 if (ok && s_round > 0) ok = wait_or_abort(&X->s_empty[buf], (s_round - 1) & 1, X, status, 34);
                 if (!ok) break;
+                if (i == 0) PKV_TL(8);
                 tc_fence_after_sync();
                 const uint32_t ka = sbase + C::K_OFF + s * C::PAGE;
                 // descriptors differ from page to page only in the start-address field (units of 16 bytes): the
@@ -323,6 +380,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                               sfb_tm + 4 * k, k != 0);
                 tc_commit(&X->k_empty[s]);
                 tc_commit(&X->s_full[buf]);
+                if (i + STEP >= P) PKV_TL(9);
                 if (with_v && i >= 1) ok = do_pv(i - 1);
                 s += STEP;
                 if (s >= nks) { s -= nks; k_phase ^= 1u; }
@@ -331,10 +389,75 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             }
             if (ok && with_v) do_pv(P - 1);
         }
+    } else if (VQ && warp == 3) {
+        // spare warp of the first warpgroup
+    } else if (VQ && warp >= 8) {
+        // ================================================================== V converter (quantised V pages)
+        // Thread = token row of the tile. A row is 64 bytes of E2M1 codes and one bf16 scale; it becomes 128
+        // bf16 values (code value times scale, rounded to bf16: exact unless the code is +-1.5, +-3 or +-6,
+        // then one rounding of at most 2^-9) in the 128-byte-swizzled layout a tensor tile load of a bf16
+        // V page would have produced, which is what the P.V descriptors expect.
+        const int r = (warp - 8) * 32 + lane;
+        const uint32_t sw = ((uint32_t)r >> 1) & 3u;
+        // bf16 bit patterns of the eight E2M1 magnitudes (0 .5 1 1.5 2 3 4 6) as byte tables for prmt
+        constexpr uint32_t LO_A = 0xC0800000u, LO_B = 0xC0804000u, HI_A = 0x3F3F3F00u, HI_B = 0x40404040u;
+        auto prmt = [](uint32_t a, uint32_t b, uint32_t c) -> uint32_t {
+            uint32_t d;
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+            return d;
+        };
+        bool ok = true;
+        for (int i = 0; i < P && ok; ++i) {
+            for (int g = 0; g < NKV; ++g) {
+                const int j = i * NKV + g, rs = j % NVR, bs = j % C::NVS;
+                ok = __all_sync(0xffffffffu, wait_or_abort(&X->vr_full[rs], (j / NVR) & 1, X, status, 50));
+                if (ok && j >= C::NVS) ok = __all_sync(0xffffffffu, wait_or_abort(&X->v_empty[bs], ((j / C::NVS) - 1) & 1, X, status, 51));
+                if (!ok) break;
+                const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
+                uint8_t* dst = smem + C::V_OFF + bs * V_STAGE_BYTES + r * 128;
+                const uint32_t sbits = *reinterpret_cast<const uint16_t*>(raw + PKV_PAGE_TOKENS * 64 + r * 2);
+                const uint32_t s2 = sbits | (sbits << 16);
+                const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 64 + ((c ^ sw) << 4));
+                    const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t w = wv[u], m = w & 0x77777777u, m2 = m >> 16, up = w << 4;
+                        uint32_t o[4];
+                        {
+                            const uint32_t lo = prmt(LO_A, LO_B, m);
+                            const uint32_t hi = prmt(HI_A, HI_B, m) | (prmt(up, w, 0xD9C8u) & 0x80808080u);
+                            o[0] = prmt(lo, hi, 0x5140u);
+                            o[1] = prmt(lo, hi, 0x7362u);
+                        }
+                        {
+                            const uint32_t lo = prmt(LO_A, LO_B, m2);
+                            const uint32_t hi = prmt(HI_A, HI_B, m2) | (prmt(up, w, 0xFBEAu) & 0x80808080u);
+                            o[2] = prmt(lo, hi, 0x5140u);
+                            o[3] = prmt(lo, hi, 0x7362u);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[k]), scale2);
+                            o[k] = *reinterpret_cast<const uint32_t*>(&pr);
+                        }
+                        const int chunk = 4 * c + u;                 // 8 dims = one 16-byte chunk of the row
+                        *reinterpret_cast<uint4*>(dst + (chunk >> 3) * (V_STAGE_BYTES / 2) + (((chunk & 7) ^ (r & 7)) << 4)) =
+                            make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+                fence_proxy_async_smem();                            // generic-proxy writes -> visible to the tensor core
+                mbar_arrive(&X->v_full[bs]);
+                mbar_arrive(&X->vr_empty[rs]);
+            }
+        }
     } else {
         // ================================================================== softmax (128 threads, one token row each)
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
-        const int sg = (warp - 3) >> 2;                     // softmax group: pages sg, sg + SG, ...
+        const int sg = VQ ? 0 : (warp - 3) >> 2;            // softmax group: pages sg, sg + SG, ...
+        (void)W_SM;
         const int row = quad * 32 + lane;
         const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
         const float* rs = reinterpret_cast<const float*>(smem + C::Q_OFF + C::PAGE);     // [head] tensor scale of the query operand
@@ -366,6 +489,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
             const int buf = i & 1;                          // P buffer and exchange slots
             ok = wait_all(&X->s_full[sb], (i / NSB) & 1, 41);
             if (!ok) break;
+            if (i == 0 && warp == W_SM && lane == 0) PKV_TL(10);
             tc_fence_after_sync();
             float s[HPC];
             {
@@ -477,6 +601,7 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
                 mbar_arrive(&X->p_full[buf]);
             }
         }
+        if (warp == W_SM && lane == 0) PKV_TL(11);
         // ---- epilogue: O^T back from TMEM, row sums reduced over the 128 token rows
         if (ok && with_v) ok = wait_all(&X->pv_done[(P - 1) & 1], ((P - 1) >> 1) & 1, 44);
         // A CTA that streamed early may never have waited for the launch before this one. It does so now, at no
@@ -526,10 +651,14 @@ __global__ void __launch_bounds__(WV ? NTHREADS : NTHREADS_SCORES, 1) pkv_attn_t
         } else {
             softmax_sync();                                 // keep the rendezvous count whole when a group gave up
         }
+        if (warp == W_SM && lane == 0) PKV_TL(12);
     }
     // ---- teardown: everyone meets, tensor memory goes back
     tc_fence_before_sync();
     __syncthreads();
+#ifdef PKV_TIMELINE
+    if (tid == 0) { PKV_TL(13); tl_buf[14] = pkv_globaltimer(); }
+#endif
     if (X->abort_flag) {
         // A role gave up (status says why). The slot of this CTA gets the neutral triple, so that a merge
         // enqueued behind this launch never folds in what an earlier call left in the partials.
@@ -581,12 +710,12 @@ int encode_rows128_map(CUtensorMap* map, const void* base, uint64_t rows, uint32
     return PKV_OK;
 }
 
-template <int WP, int REP, bool WV, bool INLQ>
+template <int WP, int REP, bool WV, bool INLQ, bool VQ = false>
 int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
               long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
-    auto kern = pkv_attn_tc_kernel<WP, REP, WV, INLQ>;
-    constexpr int smem = Cfg<WP>::SMEM;
+    auto kern = pkv_attn_tc_kernel<WP, REP, WV, INLQ, VQ>;
+    constexpr int smem = Cfg<WP, VQ>::SMEM;
     static pkv_attr_flags attr;                                     // per instantiation and device
     PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
     const float logit_scale = PKV_LOG2E / sqrtf((float)L->head_dim);
@@ -597,20 +726,26 @@ int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cach
     rc = qa.q ? encode_rows128_map(&qmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::QBLOB / 128)
               : encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
     if (rc) return rc;
-    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(WV ? NTHREADS : NTHREADS_SCORES), smem, st, vmap, kmap, qmap,
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(n_threads<WV, VQ>()), smem, st, vmap, kmap, qmap,
                                     pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
                                     1.0f / logit_scale, flags, partials, scores, scores_stride, status, qa));
     return PKV_OK;
 }
 
-template <int WP, int REP, bool WV>
+template <int WP, int REP, bool WV, bool VQ = false>
 int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
               long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
-    return qa.q ? launch_tc_impl<WP, REP, WV, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials, scores,
-                                                    scores_stride, status, qa, st)
-                : launch_tc_impl<WP, REP, WV, false>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
-                                                     scores, scores_stride, status, qa, st);
+    if constexpr (VQ) {                              // quantised V pages: the operand comes from pkv_absorb
+        if (qa.q) return PKV_ERR_UNSUPPORTED;
+        return launch_tc_impl<WP, REP, WV, false, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
+                                                        scores, scores_stride, status, qa, st);
+    } else {
+        return qa.q ? launch_tc_impl<WP, REP, WV, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials, scores,
+                                                        scores_stride, status, qa, st)
+                    : launch_tc_impl<WP, REP, WV, false>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
+                                                         scores, scores_stride, status, qa, st);
+    }
 }
 
 }  // namespace
@@ -639,8 +774,13 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
         int st = init_encoder();
         if (st) return st;
     }
-    if (with_v) {
-        if (((uintptr_t)cache->v_dev) & 15u) return PKV_ERR_INVALID;
+    const bool vq = with_v && cache->v_bits != 0;    // V pages hold per-token low-bit codes (pkv_vq_write)
+    if (vq) {
+        if (!cache->vq_dev || (((uintptr_t)cache->vq_dev) & 127u) || cache->head_dim != DH) return PKV_ERR_INVALID;
+        int st = encode_rows128_map(&vmap, cache->vq_dev, (uint64_t)cache->n_pages * cache->n_kv * (RAW_BYTES / 128), RAW_BYTES / 128);
+        if (st) return st;
+    } else if (with_v) {
+        if (!cache->v_dev || (((uintptr_t)cache->v_dev) & 15u)) return PKV_ERR_INVALID;
         int st = encode_v_map(&vmap, cache);
         if (st) return st;
     }
@@ -652,7 +792,14 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)       \
                 : launch_tc<WP_, R_, false>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
                                             flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
-    if (rep == 1 && with_v) {                       // one query head per kv head: 4 CTAs of 8 heads per (sequence, split)
+#define PKV_TC_VQ(WP_, R_)                                                                                                \
+    rc = launch_tc<WP_, R_, true, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
+                                        partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
+    if (vq) {
+        if (rep == 1) { if (wide) PKV_TC_VQ(256, 1); else PKV_TC_VQ(128, 1); }
+        else if (rep == 8) { if (wide) PKV_TC_VQ(256, 8); else PKV_TC_VQ(128, 8); }
+        else { if (wide) PKV_TC_VQ(256, 4); else PKV_TC_VQ(128, 4); }
+    } else if (rep == 1 && with_v) {                // one query head per kv head: 4 CTAs of 8 heads per (sequence, split)
         rc = wide ? launch_tc<256, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
                                             partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
                   : launch_tc<128, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
@@ -660,6 +807,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     } else if (rep == 8) { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
     else { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }      // scores only never touches V: any grouping
 #undef PKV_TC_CASE
+#undef PKV_TC_VQ
     if (rc == PKV_OK && out_dev) {                  // the merge of the splits: a second, latency-tuned launch
         const int64_t pw = DH + 2;
         const bool packed = (flags & PKV_ATTN_PACKED_OUT) != 0;

@@ -58,7 +58,7 @@ extern "C" int pkv_decode_attn_noalloc(const pkv_layer_t* layer, const pkv_cache
     if (batch < 0 || n_split <= 0 || max_pages <= 0) return PKV_ERR_INVALID;
     if (batch == 0) return PKV_OK;
     if ((int64_t)batch * n_split > PKV_NOALLOC_MAX_PARTS) return PKV_ERR_UNSUPPORTED;     // beyond the built-in scratch
-    if (!qop_dev || !page_table_dev || !seqlens_dev || !out_dev || !cache->v_dev) return PKV_ERR_INVALID;
+    if (!qop_dev || !page_table_dev || !seqlens_dev || !out_dev || !(cache->v_bits ? cache->vq_dev : cache->v_dev)) return PKV_ERR_INVALID;
     if (cache->W != 2 * layer->R + layer->R_s || cache->n_kv != layer->n_kv || cache->head_dim != layer->head_dim)
         return PKV_ERR_INVALID;
     if (layer->n_q != NQ || layer->head_dim != DH) return PKV_ERR_UNSUPPORTED;

@@ -5,7 +5,7 @@
 
 thread_local int g_pkv_last_cuda_error = 0;
 
-extern "C" int pkv_abi_version(void) { return 1; }
+extern "C" int pkv_abi_version(void) { return 2; }
 
 extern "C" const char* pkv_status_string(int s) {
     switch (s) {

@@ -41,7 +41,7 @@ class PagedLatentCache:
     """
 
     def __init__(self, W: int, n_kv: int, head_dim: int, batch: int, max_tokens: int, device="cuda",
-                 with_v: bool = True, n_pages: Optional[int] = None):
+                 with_v: bool = True, n_pages: Optional[int] = None, v_bits: int = 0):
         lib = _lib.load()
         self.W, self.n_kv, self.head_dim, self.batch = W, n_kv, head_dim, batch
         self.max_pages = (max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS
@@ -52,14 +52,24 @@ class PagedLatentCache:
         self.device = torch.device(device)
         self.latent = _aligned_bytes(self.n_pages * self.page_bytes, self.device)
         # V pages are head-major: the tile of one (page, kv head) is one contiguous block of 128 x head_dim values
+        # v_bits = 3 or 2: V pages hold per-token low-bit codes (phasorkv/kernels/nvfp4.py:58-67) instead of bf16
+        self.v_bits = int(v_bits) if with_v else 0
+        if self.v_bits not in (0, 2, 3):
+            raise ValueError("v_bits must be 0 (bf16 V pages), 3 or 2")
         self.v = (torch.zeros((self.n_pages, n_kv, PAGE_TOKENS, head_dim), dtype=torch.bfloat16, device=self.device)
-                  if with_v else None)
+                  if with_v and not self.v_bits else None)
+        self.vq = None
+        if self.v_bits:
+            tile = int(lib.pkv_vq_page_bytes(n_kv, head_dim))
+            if tile <= 0:
+                raise _lib.PhasorKVError("quantised V pages need head_dim 128")
+            self.vq = _aligned_bytes(self.n_pages * tile, self.device)
         # contiguous default mapping: sequence b owns pages [b*max_pages, (b+1)*max_pages)
         pt = torch.arange(batch * self.max_pages, dtype=torch.int32).reshape(batch, self.max_pages)
         self.page_table = (pt % self.n_pages).to(self.device)
         self.seqlens = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.c = _lib.Cache(self.latent.data_ptr(), 0 if self.v is None else self.v.data_ptr(), self.n_pages, W,
-                            n_kv, head_dim)
+                            n_kv, head_dim, 0 if self.vq is None else self.vq.data_ptr(), self.v_bits)
 
     def slots(self, seq: torch.Tensor, local_pos: torch.Tensor) -> torch.Tensor:
         """Slot (page * 128 + row) of token `local_pos` of sequence `seq`; int32 tensors on the device."""
@@ -67,20 +77,38 @@ class PagedLatentCache:
         return (page * PAGE_TOKENS + (local_pos % PAGE_TOKENS).to(torch.int32)).to(torch.int32)
 
     def v_rows(self, slots: torch.Tensor) -> torch.Tensor:
-        """Value rows [n, n_kv, head_dim] stored at `slots` (page * 128 + row)."""
+        """Value rows [n, n_kv, head_dim] stored at `slots` (page * 128 + row); quantised pages: dequantised fp32."""
+        if self.v_bits:
+            return self.read_vq(slots)[0]
         s = slots.long()
         return self.v[s // PAGE_TOKENS, :, s % PAGE_TOKENS, :]
 
     def set_v_rows(self, slots: torch.Tensor, rows: torch.Tensor) -> None:
-        """Store value rows [n, n_kv, head_dim] (or [n, n_kv * head_dim]) at `slots` with torch indexing."""
+        """Store value rows [n, n_kv, head_dim] (or [n, n_kv * head_dim]) at `slots`."""
+        if self.v_bits:
+            return self.write_v(rows, slots)
         s = slots.long()
         self.v[s // PAGE_TOKENS, :, s % PAGE_TOKENS, :] = rows.reshape(-1, self.v.shape[1], self.v.shape[3]).to(self.v.dtype)
 
     def write_v(self, v: torch.Tensor, slots: torch.Tensor) -> None:
-        """bf16 value rows [n, n_kv, head_dim] into the V pages."""
-        v = v.to(torch.bfloat16).contiguous()
+        """bf16 value rows [n, n_kv, head_dim] into the V pages (quantised per (token, kv head) if v_bits)."""
+        v = v.to(device=self.device, dtype=torch.bfloat16).contiguous()
+        if self.v_bits:
+            _lib.check(_lib.load().pkv_vq_write(ctypes.byref(self.c), _lib.ptr(v), _lib.ptr(slots), v.shape[0],
+                                                _lib.current_stream()), "pkv_vq_write")
+            return
         _lib.check(_lib.load().pkv_v_write(ctypes.byref(self.c), _lib.ptr(v), _lib.ptr(slots), v.shape[0],
                                            _lib.current_stream()), "pkv_v_write")
+
+    def read_vq(self, slots: torch.Tensor):
+        """Quantised V pages -> (rows fp32 [n, n_kv, d] = value * scale, codes uint8 [n, n_kv, d], scales bf16 [n, n_kv])."""
+        n = slots.numel()
+        rows = torch.empty((n, self.n_kv, self.head_dim), dtype=torch.float32, device=self.device)
+        codes = torch.empty((n, self.n_kv, self.head_dim), dtype=torch.uint8, device=self.device)
+        scales = torch.empty((n, self.n_kv), dtype=torch.bfloat16, device=self.device)
+        _lib.check(_lib.load().pkv_vq_read(ctypes.byref(self.c), _lib.ptr(slots), n, _lib.ptr(rows), _lib.ptr(codes),
+                                           _lib.ptr(scales), _lib.current_stream()), "pkv_vq_read")
+        return rows, codes, scales
 
     def quantize_rows(self, rows: torch.Tensor, slots: torch.Tensor, second: float) -> None:
         """Given fp32 latent rows [n, W] -> NVFP4 codes + scales in the pages (bit-exact quantiser)."""
@@ -292,8 +320,9 @@ class PhasorKey:
         self.set_second(float(32.0 * var.max().clamp_min(1e-30).sqrt() / (448.0 * 6.0)))
         return self.second
 
-    def new_cache(self, batch: int, max_tokens: int, with_v: bool = True) -> PagedLatentCache:
-        return PagedLatentCache(self.cache_width, self.n_kv, self.head_dim, batch, max_tokens, self.device, with_v)
+    def new_cache(self, batch: int, max_tokens: int, with_v: bool = True, v_bits: int = 0) -> PagedLatentCache:
+        return PagedLatentCache(self.cache_width, self.n_kv, self.head_dim, batch, max_tokens, self.device, with_v,
+                                v_bits=v_bits)
 
     def write_paged(self, cache: PagedLatentCache, x: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
                     v: Optional[torch.Tensor] = None, latent_out: Optional[torch.Tensor] = None,
@@ -303,6 +332,9 @@ class PhasorKey:
         self._need_inv_freq("write_paged")
         L = self._layer()
         x = self._x(x)
+        if v is not None and cache is not None and cache.v_bits:       # quantised V pages have their own writer
+            cache.write_v(v, slots)
+            v = None
         if v is not None:
             v = v.to(torch.bfloat16).contiguous()
         _lib.check(_lib.load().pkv_cache_write(ctypes.byref(L), None if cache is None else ctypes.byref(cache.c),
@@ -348,6 +380,9 @@ class PhasorKey:
         self._need_inv_freq("prologue_step")
         L = self._layer()
         x = self._x(x)
+        if v is not None and cache.v_bits:                              # quantised V pages have their own writer
+            cache.write_v(v, slots)
+            v = None
         if v is not None:
             v = v.to(torch.bfloat16).contiguous()
         _lib.check(_lib.load().pkv_decode_prologue(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(x), self._xdt(x),

@@ -261,6 +261,33 @@ def attend_merge():
     print("attend_merge")
 
 
+def v_tiers():
+    """Per-token low-bit tiers of the reference (kernels/nvfp4.quantize_per_token) on rows of 128 values, the
+    shape of one (token, kv head) value row: 3-bit and 2-bit, with ties, an all-zero row, a row below the
+    1e-5 floor, large and tiny magnitudes."""
+    g = torch.Generator().manual_seed(4405)
+    rows = [torch.randn(128, generator=g) * m for m in (1.0, 0.02, 37.0, 1e-3, 4e3)]
+    rows += [torch.zeros(128), torch.full((128,), 3e-6)]
+    tie = torch.zeros(128)
+    tie[0] = 3.0                                               # scale exactly 1: x / s lands on .5 ties and the clamp
+    tie[1:9] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, -3.5, -4.2])
+    rows.append(tie)
+    tie2 = torch.zeros(128)
+    tie2[0] = 1.5
+    tie2[1:7] = torch.tensor([1.0, -1.0, 0.999, 1.001, 0.0, -0.0])
+    rows.append(tie2)
+    x = torch.cat([torch.stack(rows), torch.randn(64, 128, generator=g) * torch.exp(torch.randn(64, 1, generator=g) * 2)])
+    x = x.to(torch.bfloat16).float()                           # value rows are bf16 where this format is used
+    out = dict(x=x.numpy())
+    for nbits in (3, 2):
+        codes, scale, xhat = nvfp4.quantize_per_token(x, nbits)
+        out[f"codes{nbits}"] = codes.numpy()
+        out[f"scale{nbits}"] = scale.view(torch.int16).numpy()          # bf16 bit patterns
+        out[f"xhat{nbits}"] = xhat.numpy()
+    np.savez_compressed(os.path.join(HERE, "v_tiers.npz"), **out)
+    print("v_tiers", x.shape)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
     only = set(sys.argv[1:])                                  # optional: names of the fixtures to (re)write
@@ -274,3 +301,5 @@ if __name__ == "__main__":
             phasorkey_factorized()
         if want("attend_merge"):
             attend_merge()
+        if want("v_tiers"):
+            v_tiers()

@@ -13,7 +13,7 @@ from phasorkv_b200.latent import PhasorKey
 
 class Scenario:
     def __init__(self, config="cfg2", seqlens=(300,), layer=0, gain=1.0, seed=11, d_model=4096, pos0=0,
-                 fused_write=True, x_dtype=torch.float32):
+                 fused_write=True, x_dtype=torch.float32, v_bits=0):
         self.spec = synth.make_layer(config, layer, d_model=d_model, factor_gain=gain)
         self.pk = PhasorKey.from_spec(self.spec, device="cuda")
         self.opk = po.PhasorKeyOracle.from_spec(self.spec)
@@ -27,7 +27,7 @@ class Scenario:
         self.second = float(po.nv_static_second(rows_c.var(0)))
         self.pk.set_second(self.second)
         Tmax = max(max(self.seqlens), 1)
-        self.cache = self.pk.new_cache(self.B, Tmax)
+        self.cache = self.pk.new_cache(self.B, Tmax, v_bits=v_bits)
         self.x, self.v, self.pos, self.rows_ref = [], [], [], []
         for b, T in enumerate(self.seqlens):
             x = synth.make_hidden(gen, T, d_model).to(x_dtype)
@@ -60,12 +60,14 @@ class Scenario:
         rows, _, _ = self.cache.read(self.slots_of(b), self.second, codes=False)
         return rows.cpu()
 
-    def oracle_scores_and_output(self, b, rows):
+    def oracle_scores_and_output(self, b, rows, V=None):
+        """Oracle absorbed query, scores and output of sequence b on the given cache rows (and value rows V
+        [T, n_kv, d]; default: the values the scenario wrote)."""
         spec = self.spec
         ph = po.rope_phasors(spec.inv_freq, self.qpos[b:b + 1], spec.attn_scale)
         qa = self.opk.absorb(self.q[b][:, None, :], ph)[:, 0]
         S = self.opk.scores(qa, rows)
-        O = po.attend(S, self.v[b], spec.n_kv, spec.head_dim)
+        O = po.attend(S, self.v[b] if V is None else V, spec.n_kv, spec.head_dim)
         return qa, S, O
 
 

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(lib):
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert declared == set(_lib.SIGNATURES), "ctypes table and header disagree"
-    assert lib.pkv_abi_version() == 1
+    assert lib.pkv_abi_version() == 2          # 2: pkv_cache_t grew vq_dev, v_bits
 
 
 def test_sizes_and_status_strings(lib):

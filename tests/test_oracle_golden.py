@@ -157,3 +157,15 @@ def test_attend_and_split_merge_against_reference_vectors():
     merged = po.merge_partials(torch.from_numpy(g["om"]), torch.from_numpy(g["ol"]), torch.from_numpy(g["oo"]))
     assert torch.equal(merged, torch.from_numpy(g["merged"]))
     assert float((po.merge_partials(m, l, o) - O).norm() / O.norm()) < 2e-6
+
+
+def test_per_token_v_tiers_bit_exact():
+    """The oracle's per-token 3-bit and 2-bit tiers against the reference's quantize_per_token output."""
+    g = _load("v_tiers.npz")
+    x = torch.from_numpy(g["x"])
+    for nbits in (3, 2):
+        codes, scale, xhat = po.quantize_per_token(x, nbits)
+        assert np.array_equal(codes.numpy(), g[f"codes{nbits}"])
+        assert np.array_equal(scale.view(torch.int16).numpy(), g[f"scale{nbits}"])
+        assert np.array_equal(xhat.numpy(), g[f"xhat{nbits}"])
+        assert torch.equal(po.e2m1_decode(codes) * scale.float()[:, None], xhat)
