@@ -66,7 +66,14 @@ __device__ __forceinline__ float4 load_x4(const XT* src) {
     }
 }
 
-template <typename XT>
+// SMALL: at most PTS tokens (a token-sharded sequence set, a batch of a few sequences). The same tiles, but a
+// thread owns one pair column and one sixteenth of the chunk's k range for ALL tokens, so that a factor value
+// read from shared memory feeds PTS multiply-adds instead of one: the loop is no longer bound by shared-memory
+// bandwidth (6 reads of 16 bytes per 32 multiply-adds instead of 3 per 8). The k slices are added in ascending
+// order; the sum order differs from the general path, so the two paths may differ in the last bit of a sum.
+constexpr int PTS = 4;
+
+template <typename XT, bool SMALL>
 __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x;
@@ -84,7 +91,7 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     const XT* x = reinterpret_cast<const XT*>(A.x);
     const int t = tid >> 4, c = tid & 15;
     constexpr int NVB = 2 * PC * (KC / 4) / NT;     // 16-byte vectors per thread: factor tile (16)
-    constexpr int NVX = PT * (KC / 4) / NT;         // ... and token tile (8)
+    constexpr int NVX = (SMALL ? PTS : PT) * (KC / 4) / NT;       // ... and token tile (8; 2 for the small path)
 
     for (int t0 = 0; t0 < n_tokens; t0 += PT) {
         const int my_tok = t0 + ks * TPR + (tid >> 4);              // for tid < TPR * PC: the token this thread rotates
@@ -109,6 +116,7 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                 xv[n] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (t0 + tt < n_tokens && k4 * 4 < kc) xv[n] = load_x4<XT>(x + (size_t)(t0 + tt) * D + k0 + k4 * 4);
             }
+            (void)t;
             if (ch == 0) {
                 // while the tiles are in flight: the V rows of this CTA's tokens, and the phasors it will need
                 if (ct == 0 && A.v_rows) {
@@ -141,6 +149,48 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                 *reinterpret_cast<float4*>(xs + (i / (KC / 4)) * KC + (i % (KC / 4)) * 4) = xv[n];
             }
             __syncthreads();
+            if constexpr (SMALL) {
+                // thread = (pair column c2, k slice kq of KC / 16 values); all PTS tokens
+                const int c2 = tid & 15, kq = tid >> 4;
+                constexpr int KS = KC / 16;
+                float re[PTS][4], im[PTS][4];
+#pragma unroll
+                for (int tt = 0; tt < PTS; ++tt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) re[tt][e] = im[tt][e] = 0.0f;
+                const float* ar = bs + c2 * BP + kq * KS;
+                const float* br = bs + (PC + c2) * BP + kq * KS;
+                const float* xr = xs + kq * KS;
+#pragma unroll
+                for (int k = 0; k < KS; k += 4) {
+                    const float4 av = *reinterpret_cast<const float4*>(ar + k);
+                    const float4 bq = pair ? *reinterpret_cast<const float4*>(br + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int tt = 0; tt < PTS; ++tt) {
+                        const float4 xq = *reinterpret_cast<const float4*>(xr + tt * KC + k);
+                        re[tt][0] = fmaf(xq.x, av.x, re[tt][0]); re[tt][1] = fmaf(xq.y, av.y, re[tt][1]);
+                        re[tt][2] = fmaf(xq.z, av.z, re[tt][2]); re[tt][3] = fmaf(xq.w, av.w, re[tt][3]);
+                        im[tt][0] = fmaf(xq.x, bq.x, im[tt][0]); im[tt][1] = fmaf(xq.y, bq.y, im[tt][1]);
+                        im[tt][2] = fmaf(xq.z, bq.z, im[tt][2]); im[tt][3] = fmaf(xq.w, bq.w, im[tt][3]);
+                    }
+                }
+                __syncthreads();                                    // every thread is done with the token tile: it becomes the exchange area
+                float* red = xs;                                    // [16 k slices][PTS][2][PC]
+#pragma unroll
+                for (int tt = 0; tt < PTS; ++tt) {
+                    red[((kq * PTS + tt) * 2 + 0) * PC + c2] = (re[tt][0] + re[tt][1]) + (re[tt][2] + re[tt][3]);
+                    red[((kq * PTS + tt) * 2 + 1) * PC + c2] = (im[tt][0] + im[tt][1]) + (im[tt][2] + im[tt][3]);
+                }
+                __syncthreads();
+                if (tid < PTS * 2 * PC) {
+                    const int tt = tid >> 5, half = (tid >> 4) & 1, cc = tid & 15;
+                    float v = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) v += red[((q * PTS + tt) * 2 + half) * PC + cc];
+                    part[((ch * 2 + half) * PT + tt) * PC + cc] = v;
+                }
+                continue;                                           // next chunk (its first barrier protects `red`)
+            }
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
             const float* xr = xs + t * KC;
             const float* ar = bs + c * BP;
@@ -222,7 +272,7 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     }
 }
 
-template <typename XT>
+template <typename XT, bool SMALL>
 __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs Wa, const pkv_absorb_impl::Args Aa, int batch) {
     extern __shared__ __align__(16) float sm[];
     // Wait first, trigger second (as pkv_absorb does): the attention kernel behind this one streams cache
@@ -236,12 +286,12 @@ __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs W
         if (a < batch * n_hg) pkv_absorb_impl::body(Aa, a / n_hg, a % n_hg, sm);
         return;
     }
-    write_role<XT>(Wa, sm);
+    write_role<XT, SMALL>(Wa, sm);
 }
 
-template <typename XT>
+template <typename XT, bool SMALL>
 cudaError_t launch_prologue(const WriteArgs& Wa, const pkv_absorb_impl::Args& Aa, int batch, size_t smem, cudaStream_t st) {
-    auto kern = pkv_step_prologue_kernel<XT>;
+    auto kern = pkv_step_prologue_kernel<XT, SMALL>;
     static pkv_attr_flags smem_set;                      // per instantiation and device
     {
         cudaError_t e = pkv_set_max_smem(kern, (int)smem, smem_set);
@@ -308,7 +358,14 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     const size_t absorb_smem = pkv_absorb_impl::smem_bytes(layer->head_dim, WP);
     if (absorb_smem > smem) smem = absorb_smem;
     const int absorb_batch = q_dev ? batch : 0;                      // no queries: the write role alone
-    PKV_CUDA_TRY(x_dtype == PKV_F32 ? launch_prologue<float>(Wa, Aa, absorb_batch, smem, (cudaStream_t)stream)
-                                    : launch_prologue<uint16_t>(Wa, Aa, absorb_batch, smem, (cudaStream_t)stream));
+    const cudaStream_t cst = (cudaStream_t)stream;
+    cudaError_t le;
+    if (batch <= PTS)                                                 // a few tokens: the register-tiled projection
+        le = x_dtype == PKV_F32 ? launch_prologue<float, true>(Wa, Aa, absorb_batch, smem, cst)
+                                : launch_prologue<uint16_t, true>(Wa, Aa, absorb_batch, smem, cst);
+    else
+        le = x_dtype == PKV_F32 ? launch_prologue<float, false>(Wa, Aa, absorb_batch, smem, cst)
+                                : launch_prologue<uint16_t, false>(Wa, Aa, absorb_batch, smem, cst);
+    PKV_CUDA_TRY(le);
     return PKV_OK;
 }

@@ -367,12 +367,15 @@ def test_decode_time_write_path(config, n):
     assert rel(b.cpu(), a.cpu()) < 5e-3
 
 
-@pytest.mark.parametrize("config,n", [("cfg2", 16), ("cfg2", 1), ("cfg2", 37), ("cfg5", 64), ("cfg3", 5)])
+@pytest.mark.parametrize("config,n", [("cfg2", 16), ("cfg2", 1), ("cfg2", 4), ("cfg2", 5), ("cfg2", 37), ("cfg5", 64), ("cfg5", 3),
+                                      ("cfg3", 5)])
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
 def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
     """The one-launch step prologue (write of the newest tokens + absorb) leaves the bits of the two
     separate calls: cache codes and scales, V rows, unquantised rows, absorbed queries, operand.
-    cfg3 (R = 120, not a multiple of 16) takes the entry point's two-launch route."""
+    cfg3 (R = 120, not a multiple of 16) takes the entry point's two-launch route. Up to 4 tokens the
+    prologue projects with a register tile that adds the d_model slices in another order: there the rows
+    agree to fp32 rounding, and the stored bits are the reference quantiser's bits of the prologue's own rows."""
     sc = Scenario(config, seqlens=(n,), pos0=32767)
     pk, W = sc.pk, sc.spec.cache_width
     x = sc.x[0].cuda().to(x_dtype)
@@ -396,9 +399,16 @@ def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
             pk.absorb_step(q, qpos, ws)
         torch.cuda.synchronize()
         caches.append(cache), outs.append(out), wss.append(ws)
-    assert torch.equal(outs[0], outs[1])
     assert float(outs[1].abs().max()) > 0
-    assert torch.equal(caches[0].latent, caches[1].latent)
+    small = n <= 4 and config != "cfg3"                      # the register-tiled projection of the one-launch prologue
+    if small:
+        assert rel(outs[1], outs[0]) < 2e-6 and rel(outs[1].cpu(), sc.rows_ref[0]) < 5e-6
+        _, codes, scales = caches[1].read(slots, sc.second)
+        _, q_codes, q_scales = _quantise_and_read(outs[1], sc.second)
+        assert torch.equal(codes.cpu(), q_codes) and torch.equal(scales.cpu(), q_scales)
+    else:
+        assert torch.equal(outs[0], outs[1])
+        assert torch.equal(caches[0].latent, caches[1].latent)
     assert torch.equal(caches[0].v, caches[1].v)
     assert torch.equal(caches[1].v_rows(slots).cpu(), sc.v[0])
     assert torch.equal(wss[0].qabs, wss[1].qabs) and float(wss[1].qabs.abs().max()) > 0
