@@ -25,8 +25,10 @@ module (``hidden_states, position_embeddings, attention_mask, past_key_values, *
                                        ``o_proj``: keys are never rebuilt, the Hugging Face KV cache
                                        is not touched.
 
-Positions are counted by the layer's own cache (``seqlens``), so the caller runs the model with
-``use_cache=False`` and feeds one new token per decode call. ``undo`` restores the original forward
+Positions are counted by the layer's own cache (``seqlens``, one length per sequence), so the caller runs
+the model with ``use_cache=False`` and feeds one new token per sequence and decode call. A ragged batch is
+prefilled right-padded with ``attn.kv_lengths`` set to the valid token counts, the contract of the reference's
+runner (phasorkv/runner.py:94-99); a decode step then places every sequence's token at its own position. ``undo`` restores the original forward
 and drops the caches.
 """
 from __future__ import annotations
@@ -41,53 +43,70 @@ NVFP4_BITS = 4.5          # E2M1 code + one E4M3 scale per 16 codes (phasorkv/qu
 
 
 class LayerDecodeState:
-    """Paged caches, workspace and position bookkeeping of one patched attention layer."""
+    """Paged caches, workspace and position bookkeeping of one patched attention layer.
+
+    Every sequence of the batch has its own length (the reference's runner hands ragged batches to a
+    patched layer as ``attn.kv_lengths``, phasorkv/runner.py:94-99): ``lengths[b]`` tokens of sequence b are
+    cached, the next token of b is written at position ``lengths[b]`` and attends to positions
+    ``0 .. lengths[b]``."""
 
     def __init__(self, pk: PhasorKey, batch: int, max_tokens: int, write_chunk: int = 4096):
         self.pk, self.batch, self.max_tokens, self.write_chunk = pk, batch, max_tokens, write_chunk
         self.cache = pk.new_cache(batch, max_tokens)
         self.ws = pk.workspace(batch, pk.default_splits(batch, max_tokens))
         self.seq = torch.arange(batch, dtype=torch.int32, device=pk.device)
-        self.length = 0                                     # tokens cached per sequence (all sequences advance together)
+        self.lengths = [0] * batch                          # tokens cached per sequence (host copy of cache.seqlens)
         self.calibrated = False
 
+    @property
+    def length(self) -> int:
+        """Longest cached sequence."""
+        return max(self.lengths)
+
     def reset(self) -> None:
-        self.length = 0
+        self.lengths = [0] * self.batch
         self.cache.seqlens.zero_()
 
-    def _need(self, n: int) -> None:
-        if self.length + n > self.max_tokens:
-            raise RuntimeError(f"latent cache holds {self.max_tokens} tokens per sequence; {self.length + n} asked")
+    def _need(self, b: int, n: int) -> None:
+        if self.lengths[b] + n > self.max_tokens:
+            raise RuntimeError(f"latent cache holds {self.max_tokens} tokens per sequence; {self.lengths[b] + n} asked")
 
-    def prefill(self, x: torch.Tensor, v: torch.Tensor) -> None:
-        """x [B, T, D] layer input, v [B, T, n_kv, d] value rows: append T tokens to every sequence."""
+    def prefill(self, x: torch.Tensor, v: torch.Tensor, lengths=None) -> None:
+        """x [B, T, D] layer input, v [B, T, n_kv, d] value rows: append the first ``lengths[b]`` (default: all T)
+        tokens of row b to sequence b (rows are right-padded, as the reference's batches are)."""
         B, T = x.shape[0], x.shape[1]
-        self._need(T)
+        n_new = [T] * B if lengths is None else [int(n) for n in lengths]
+        if len(n_new) != B or min(n_new) < 0 or max(n_new) > T:
+            raise ValueError(f"lengths must give 0 .. {T} valid tokens for each of the {B} sequences")
         pk = self.pk
         if not self.calibrated:                             # static tensor scale from the first tokens seen (phasorkv/quant.py:119-124)
-            n = min(T, 4096)
-            pos = torch.arange(self.length, self.length + n, dtype=torch.int32, device=pk.device)
-            rows = torch.empty((n, pk.cache_width), dtype=torch.float32, device=pk.device)
-            pk.write_paged(None, x[0, :n].contiguous(), pos, None, latent_out=rows)
-            pk.calibrate_second(rows)
-            self.calibrated = True
+            b0 = max(range(B), key=lambda b: n_new[b])
+            n = min(n_new[b0], 4096)
+            if n:
+                pos = torch.arange(self.lengths[b0], self.lengths[b0] + n, dtype=torch.int32, device=pk.device)
+                rows = torch.empty((n, pk.cache_width), dtype=torch.float32, device=pk.device)
+                pk.write_paged(None, x[b0, :n].contiguous(), pos, None, latent_out=rows)
+                pk.calibrate_second(rows)
+                self.calibrated = True
         for b in range(B):
-            for t0 in range(0, T, self.write_chunk):
-                n = min(self.write_chunk, T - t0)
-                lp = torch.arange(self.length + t0, self.length + t0 + n, dtype=torch.int32, device=pk.device)
+            self._need(b, n_new[b])
+            for t0 in range(0, n_new[b], self.write_chunk):
+                n = min(self.write_chunk, n_new[b] - t0)
+                lp = torch.arange(self.lengths[b] + t0, self.lengths[b] + t0 + n, dtype=torch.int32, device=pk.device)
                 slots = self.cache.slots(torch.full((n,), b, dtype=torch.int32, device=pk.device), lp)
                 pk.write_paged(self.cache, x[b, t0:t0 + n].contiguous(), lp, slots, v=v[b, t0:t0 + n].contiguous())
-        self.length += T
-        self.cache.seqlens.fill_(self.length)
+            self.lengths[b] += n_new[b]
+        self.cache.seqlens.copy_(torch.tensor(self.lengths, dtype=torch.int32))
 
     def decode(self, x: torch.Tensor, q: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-        """x [B, D], q [B, n_q, d] pre-RoPE, v [B, n_kv, d] of the one new token -> O [B, n_q, d] fp32."""
-        self._need(1)
+        """x [B, D], q [B, n_q, d] pre-RoPE, v [B, n_kv, d] of the one new token of every sequence -> O [B, n_q, d] fp32."""
+        for b in range(self.batch):
+            self._need(b, 1)
         pk = self.pk
-        pos = torch.full((self.batch,), self.length, dtype=torch.int32, device=pk.device)
+        pos = torch.tensor(self.lengths, dtype=torch.int32, device=pk.device)      # each sequence at its own position
         slots = self.cache.slots(self.seq, pos)
-        self.length += 1
-        self.cache.seqlens.fill_(self.length)
+        self.lengths = [n + 1 for n in self.lengths]
+        self.cache.seqlens.copy_(pos + 1)
         # the newest token attends to itself too: query position = its own position
         pk.prologue_step(self.cache, x.contiguous(), pos, slots, q.float().contiguous(), pos, self.ws, v=v)
         pk.attend_step(self.cache, self.ws, out=self.ws.out, after_prologue=True)
@@ -103,7 +122,8 @@ def _patched_forward(attn, state_of, original):
         if T > 1:
             out = original(hidden_states, position_embeddings=position_embeddings, attention_mask=attention_mask,
                            past_key_values=None, **kwargs)
-            st.prefill(hidden_states, v)
+            # ragged batch: the runner's per-sequence token counts (phasorkv/runner.py:94-99); rows are right-padded
+            st.prefill(hidden_states, v, lengths=getattr(attn, "kv_lengths", None))
             return out
         q = attn.q_proj(hidden_states).view(B, -1, d)
         o = st.decode(hidden_states[:, 0], q, v[:, 0])

@@ -760,6 +760,49 @@ def test_hf_llama_attention_patch_decodes_like_the_model():
         assert rel(model(input_ids=ids).logits, ref(input_ids=ids).logits) < 1e-6
 
 
+def test_patched_layer_state_keeps_one_length_per_sequence():
+    """A ragged batch through the decode state of a patched layer (prefill right-padded with per-sequence
+    token counts, as the reference's runner passes them in attn.kv_lengths, phasorkv/runner.py:94-99; then two
+    decode steps): every sequence is written and attended at its own positions, so each gives what it gives
+    alone in a batch of one, and what the oracle gives."""
+    from phasorkv_b200.patch import LayerDecodeState
+    spec = synth.make_layer("cfg2", 0)
+    pk = PhasorKey.from_spec(spec, device="cuda")
+    pk.set_second(0.02)
+    g = torch.Generator().manual_seed(31)
+    lens, T, steps = [200, 77, 129], 200, 2
+    B = len(lens)
+    x = synth.make_hidden(g, B * (T + steps), 4096).view(B, T + steps, 4096).cuda()
+    v = synth.make_values(g, B * (T + steps), spec.n_kv, spec.head_dim).view(B, T + steps, spec.n_kv, spec.head_dim).cuda()
+    q = torch.randn((B, steps, spec.n_q, spec.head_dim), generator=g).cuda()
+
+    def run(rows):
+        st = LayerDecodeState(pk, len(rows), 512)
+        st.calibrated = True                                  # keep the tensor scale set above
+        xs = torch.stack([x[b, :T] for b in rows]); vs = torch.stack([v[b, :T] for b in rows])
+        st.prefill(xs, vs, lengths=[lens[b] for b in rows])
+        outs = []
+        for k in range(steps):                                # token k of a sequence follows its own last token
+            xn = torch.stack([x[b, T + k] for b in rows]); vn = torch.stack([v[b, T + k] for b in rows])
+            outs.append(st.decode(xn, torch.stack([q[b, k] for b in rows]), vn).clone())
+        assert st.lengths == [lens[b] + steps for b in rows]
+        return st, outs
+    st, outs = run(list(range(B)))
+    opk = po.PhasorKeyOracle.from_spec(spec)
+    for b in range(B):
+        _, alone = run([b])
+        for k in range(steps):
+            assert rel(outs[k][b], alone[k][0]) < 1e-5, (b, k)
+        # the oracle on what the cache holds: tokens 0 .. lens[b] + steps - 1 at positions 0 .., query at the last one
+        n = lens[b] + steps
+        slots = st.cache.slots(torch.full((n,), b, dtype=torch.int32, device="cuda"), torch.arange(n, dtype=torch.int32, device="cuda"))
+        rows_hat, _, _ = st.cache.read(slots, pk.second, codes=False)
+        ph_q = po.rope_phasors(spec.inv_freq, torch.tensor([n - 1]), spec.attn_scale)
+        qa = opk.absorb(q[b, steps - 1].cpu()[:, None, :], ph_q)[:, 0]
+        O_ref = po.attend(opk.scores(qa, rows_hat.cpu()), st.cache.v_rows(slots).cpu().float(), spec.n_kv, spec.head_dim)
+        assert rel(outs[steps - 1][b].cpu(), O_ref) < OUT_TOL, b
+
+
 @pytest.mark.parametrize("config,n_sink,n_recent", [("cfg2", 4, 128), ("cfg3", 4, 128), ("cfg5", 2, 37), ("cfg2", 0, 0)])
 def test_exact_token_side_path(config, n_sink, n_recent):
     """Attention sinks and a recent window kept as rotated bf16 keys join the softmax of the latent
