@@ -206,14 +206,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         return;
     }
 
-    // Quantised V: the three warpgroups (producers + MMA issuer | softmax | converters) re-divide the register
-    // file: the softmax warps keep 32 heads' statistics in registers, the others need few
     constexpr int W_SM = VQ ? 4 : 3;                  // first softmax warp
-    if constexpr (VQ) {
-        if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-        else if (warp < 8) asm volatile("setmaxnreg.inc.sync.aligned.u32 248;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 128;");
-    }
     if (warp == 0) {
         // ================================================================== K producer
         // The page indices are fetched 32 at a time by the whole warp (one coalesced load, one round trip per
@@ -473,7 +466,16 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // Per head (all kept in registers, identical in every thread that shares statistics): the
         // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
         // this thread's share of the sum of 2^(s - m).
-        float cs[HPC], m[HPC], l[HPC];
+        // (With quantised V the CTA has 12 warps and 168 registers per thread. The column scales then stay in
+        // shared memory, where the query operand's tail holds them, and are read as broadcasts; the reference
+        // maxima, identical in every lane, are kept one per lane -- lane h holds head h's -- and fetched by
+        // shuffle; so are the rescale factors.)
+        float cs[VQ ? 1 : HPC], m[VQ ? 1 : HPC], l[HPC];
+        float m_lane = -INFINITY;
+        auto m_of = [&](int h) -> float {
+            if constexpr (VQ) return __shfl_sync(0xffffffffu, m_lane, h);
+            else return m[VQ ? 0 : h];
+        };
         if constexpr (INLQ) if (sg == 0) {
             // the query may come from the launch before this one unless the caller says it was ready earlier
             if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
@@ -483,7 +485,11 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         }
         bool ok = wait_all(&X->q_full, 0, 40);
 #pragma unroll
-        for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
+        for (int h = 0; h < HPC; ++h) {
+            if constexpr (!VQ) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; }
+            l[h] = 0.0f;
+        }
+        (void)cs; (void)m;
         for (int i = sg; i < P && ok; i += SG) {
             const int sb = i % NSB;                         // score buffer
             const int buf = i & 1;                          // P buffer and exchange slots
@@ -505,7 +511,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < HPC; ++h) s[h] *= cs[h];
+                for (int h = 0; h < HPC; ++h) s[h] *= VQ ? rs[h_base + h] * col_scale : cs[VQ ? 0 : h];
             }
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
             const bool valid = token < T;
@@ -518,7 +524,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
                 if (!valid) s[h] = -INFINITY;
-                exc = fmaxf(exc, s[h] - m[h]);              // +inf while the head has no reference yet
+                exc = fmaxf(exc, s[h] - m_of(h));           // +inf while the head has no reference yet
             }
             bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
             if (with_v) {                                   // P.V needs one reference per head for all 128 rows
@@ -548,14 +554,28 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         tc_fence_after_sync();
                     }
                 }
-                float corr[HPC];
+                float corr[VQ ? 1 : HPC];
+                float corr_lane = 1.0f;
+                auto corr_of = [&](int h) -> float {
+                    if constexpr (VQ) return __shfl_sync(0xffffffffu, corr_lane, h);
+                    else return corr[VQ ? 0 : h];
+                };
+                if constexpr (VQ) {                         // lane h: head h
+                    const float m_new = fmaxf(m_lane, tm);
+                    corr_lane = m_lane > -INFINITY ? exp2f(m_lane - m_new) : 1.0f;
+                    m_lane = m_new;
 #pragma unroll
-                for (int h = 0; h < HPC; ++h) {
-                    const float m_new = fmaxf(m[h], __shfl_sync(0xffffffffu, tm, h));
-                    corr[h] = m[h] > -INFINITY ? exp2f(m[h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
-                    m[h] = m_new;
-                    l[h] *= corr[h];
+                    for (int h = 0; h < HPC; ++h) l[h] *= corr_of(h);
+                } else {
+#pragma unroll
+                    for (int h = 0; h < HPC; ++h) {
+                        const float m_new = fmaxf(m[VQ ? 0 : h], __shfl_sync(0xffffffffu, tm, h));
+                        corr[VQ ? 0 : h] = m[VQ ? 0 : h] > -INFINITY ? exp2f(m[VQ ? 0 : h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
+                        m[VQ ? 0 : h] = m_new;
+                        l[h] *= corr[VQ ? 0 : h];
+                    }
                 }
+                (void)corr;
                 if (with_v && i > 0) {
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
@@ -566,7 +586,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
-                            r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[((g * REP) >> 3) * 8 + (c & 7)]);
+                            r[c] = __float_as_uint(__uint_as_float(r[c]) * corr_of(((g * REP) >> 3) * 8 + (c & 7)));
                         tmem_st16(tl + TM_O + 16 * g, r);
                     }
                     tmem_st_wait();
@@ -583,7 +603,8 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * PGS + (row & 7) * 2;
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
-                float p = exp2f(s[h] - (m[h] > -INFINITY ? m[h] : 0.0f));             // exp2(-inf) = 0 for masked rows
+                const float mh = m_of(h);
+                float p = exp2f(s[h] - (mh > -INFINITY ? mh : 0.0f));                 // exp2(-inf) = 0 for masked rows
                 if (with_v) {
                     // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
                     // that value, so numerator and denominator of softmax . V carry the same rounding
@@ -632,7 +653,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 float v = l[h];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == h) { lw = v; mw = m[h]; }
+                if (lane == h) { lw = v; mw = VQ ? m_lane : m[VQ ? 0 : h]; }
             }
             X->lsum[sg][quad][lane] = lw;
             X->mfin[sg][quad][lane] = mw;                   // per warp in scores-only mode, identical otherwise

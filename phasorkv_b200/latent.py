@@ -189,6 +189,35 @@ class PhasorKey:
         return self
 
     @classmethod
+    def with_mean_direction(cls, A, B, freq, mu, kbar, n_q, n_kv, head_dim, inv_freq, A_s=None, B_s=None, slow=None,
+                            attn_scale: float = 1.0, device="cuda") -> "PhasorKey":
+        """The mean-direction split of the reference's latent projections (phasorkv/kvmethods.py:895-899:
+        ``k = A Q(B x) + alpha * W mu`` with ``alpha = x . mu / |mu|^2`` and ``B`` folded with the projection
+        that removes the mean direction) in rotated-latent form.
+
+        After RoPE the mean term of token t is ``alpha_t * kbar_j * e^{i theta_j t}`` at every frequency j
+        (``kbar = W mu`` [n_kv * d] in the rotate-half layout): not one cached number per token but one rank-1
+        component per frequency, i.e. ``d/2`` further complex latent dims with ``A[:, j] = kbar_j`` and the
+        same row ``B[j] = mu / |mu|^2``. This constructor appends them to the given factors (whose ``B`` it
+        first makes blind to the mean direction) and returns an ordinary PhasorKey: write, absorb and the decode
+        kernels run unchanged; the cache grows by ``d`` reals per token. (The reference keeps alpha in bf16; here
+        it is part of the NVFP4 latent.)"""
+        h = int(head_dim) // 2
+        mu = mu.to(torch.float64)
+        mu_scaled = mu / mu.dot(mu)
+        Bc = B.to(torch.complex128)
+        B_perp = Bc - (Bc @ mu.to(torch.complex128))[:, None] * mu_scaled.to(torch.complex128)[None, :]
+        kb = kbar.to(torch.float64).reshape(n_kv, head_dim)
+        A_mean = torch.complex(kb[:, :h], kb[:, h:])                                     # [n_kv, h]
+        B_mean = mu_scaled.to(torch.complex128)[None, :].expand(h, -1)
+        A_all = torch.cat([A.to(torch.complex128), A_mean], dim=1)
+        B_all = torch.cat([B_perp, B_mean], dim=0)
+        freq_all = torch.cat([freq.long(), torch.arange(h)])
+        if B_s is not None:                                                              # the slow block sees no mean either
+            B_s = B_s.to(torch.float64) - (B_s.to(torch.float64) @ mu)[:, None] * mu_scaled[None, :]
+        return cls.from_factors(A_all, B_all, freq_all, n_q, n_kv, head_dim, inv_freq, A_s, B_s, slow, None, attn_scale, device)
+
+    @classmethod
     def from_spec(cls, spec, device="cuda") -> "PhasorKey":
         return cls.from_factors(spec.A, spec.B, spec.freq, spec.n_q, spec.n_kv, spec.head_dim, spec.inv_freq,
                                 spec.A_s, spec.B_s, spec.slow, None, spec.attn_scale, device)

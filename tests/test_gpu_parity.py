@@ -402,7 +402,9 @@ def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
     assert float(outs[1].abs().max()) > 0
     small = n <= 4 and config != "cfg3"                      # the register-tiled projection of the one-launch prologue
     if small:
-        assert rel(outs[1], outs[0]) < 2e-6 and rel(outs[1].cpu(), sc.rows_ref[0]) < 5e-6
+        assert rel(outs[1], outs[0]) < 2e-6
+        if x_dtype == torch.float32:                           # rows_ref is the oracle's write of the fp32 hidden states
+            assert rel(outs[1].cpu(), sc.rows_ref[0]) < 5e-6
         _, codes, scales = caches[1].read(slots, sc.second)
         _, q_codes, q_scales = _quantise_and_read(outs[1], sc.second)
         assert torch.equal(codes.cpu(), q_codes) and torch.equal(scales.cpu(), q_scales)
@@ -758,6 +760,52 @@ def test_hf_llama_attention_patch_decodes_like_the_model():
     assert "forward" not in model.model.layers[0].self_attn.__dict__ and not patch.states
     with torch.no_grad():
         assert rel(model(input_ids=ids).logits, ref(input_ids=ids).logits) < 1e-6
+
+
+def test_mean_direction_split_through_the_kernels():
+    """The mean-direction split (k = A Q(B_perp x) + alpha * W mu, phasorkv/kvmethods.py:895-899) as a PhasorKey
+    with d/2 further latent dims: the CUDA write / absorb / scores reproduce 'rebuild the split keys, rotate with
+    HF rotary' on hidden states with a strong mean component, and the tensor-core decode meets the oracle on
+    the dequantised cache."""
+    spec = synth.make_layer("cfg2", 1)
+    g = torch.Generator().manual_seed(41)
+    A, B, freq = spec.A[:, ::2], spec.B[::2], spec.freq[::2]                   # rank 1 per frequency: 64 complex dims
+    mu = torch.randn(4096, generator=g, dtype=torch.float64) * 0.3 + 1.0
+    kbar = torch.randn(spec.n_kv * spec.head_dim, generator=g, dtype=torch.float64) * 0.05
+    pk = PhasorKey.with_mean_direction(A, B, freq, mu, kbar, spec.n_q, spec.n_kv, spec.head_dim, spec.inv_freq)
+    assert pk.cache_width == 256
+    T, pos0 = 300, 7000
+    x = synth.make_hidden(g, T, 4096) * 0.2 + (torch.rand(T, 1, generator=g) + 0.5) * mu.float()[None, :]   # alpha in 0.5 .. 1.5
+    v = synth.make_values(g, T, spec.n_kv, spec.head_dim)
+    q = synth.make_query(g, 1, spec.n_q, spec.head_dim)
+    pos = torch.arange(T) + pos0
+    ph_k = po.rope_phasors(spec.inv_freq, pos)
+    ph_q = po.rope_phasors(spec.inv_freq, torch.tensor([T + pos0]))
+    # exact (unquantised) rows and scores against the split keys rebuilt densely
+    mu_scaled = mu / mu.dot(mu)
+    Bc = B.to(torch.complex128)
+    B_perp = Bc - (Bc @ mu.to(torch.complex128))[:, None] * mu_scaled.to(torch.complex128)[None, :]
+    W_split = po.w_hat(A, B_perp, freq, spec.n_kv, spec.head_dim)
+    W_mean = kbar[:, None] * mu_scaled[None, :]                                # alpha * kbar as a dense rank-1 projection
+    S_split = po.rebuilt_scores(W_split + W_mean, x, q[0][:, None, :], ph_k, ph_q, spec.n_q, spec.n_kv, spec.head_dim)[:, 0]
+    rows, qabs = pk.write(x, ph_k), pk.absorb(q[0][:, None, :], ph_q)
+    S = PhasorKey.scores(qabs, rows)[:, 0].cpu()
+    assert rel(S, S_split) < 2e-5
+    # quantised cache, tensor-core decode, oracle on the dequantised rows
+    pk.calibrate_second(rows)
+    cache = pk.new_cache(1, T)
+    lp = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = cache.slots(torch.zeros_like(lp), lp)
+    pk.write_paged(cache, x.cuda(), pos.to(torch.int32).cuda(), slots, v=v.cuda())
+    cache.seqlens.fill_(T)
+    ws = pk.workspace(1, 2)
+    Sd = torch.zeros((1, spec.n_q, T), device="cuda")
+    pk.absorb_step(q.cuda(), torch.tensor([T + pos0], dtype=torch.int32, device="cuda"), ws)
+    pk.attend_step(cache, ws, scores_out=Sd, out=ws.out, after_absorb=True)
+    hat, _, _ = cache.read(slots, pk.second, codes=False)
+    S_ref = PhasorKey.scores(qabs.float(), hat)[:, 0].cpu()
+    assert rel(Sd[0].cpu(), S_ref) < LOGIT_TOL
+    assert rel(ws.out[0].cpu(), po.attend(S_ref, v, spec.n_kv, spec.head_dim)) < OUT_TOL
 
 
 def test_patched_layer_state_keeps_one_length_per_sequence():

@@ -187,3 +187,28 @@ def test_token_ranges():
             assert owner_of(T - 1, world, T) == world - 1
     with pytest.raises(ValueError):
         token_range(2, 2, 10)
+
+
+def test_mean_direction_split_is_a_factor_augmentation():
+    """k = A (B_perp x) + alpha * kbar (phasorkv/kvmethods.py:895-899) equals the dense keys of the PhasorKey
+    that `with_mean_direction` builds: its W_hat applied to x gives W_hat(A, B_perp) x + alpha kbar, for every
+    token, before any rotation (rotation then acts on both alike)."""
+    from oracle import phasor_oracle as po
+    g = torch.Generator().manual_seed(8)
+    n_kv, d, D, n_q, r = 2, 16, 40, 4, 2
+    h = d // 2
+    freq = torch.arange(h).repeat_interleave(r)
+    A = torch.complex(torch.randn(n_kv, h * r, generator=g, dtype=torch.float64), torch.randn(n_kv, h * r, generator=g, dtype=torch.float64))
+    B = torch.complex(torch.randn(h * r, D, generator=g, dtype=torch.float64), torch.randn(h * r, D, generator=g, dtype=torch.float64))
+    mu = torch.randn(D, generator=g, dtype=torch.float64) + 2.0
+    kbar = torch.randn(n_kv * d, generator=g, dtype=torch.float64)
+    pk = PhasorKey.with_mean_direction(A, B, freq, mu, kbar, n_q, n_kv, d, torch.ones(h, dtype=torch.float64), device="cpu")
+    assert pk.R == h * r + h and pk.cache_width == 2 * (h * r + h)
+    x = torch.randn(7, D, generator=g, dtype=torch.float64)
+    alpha = x @ mu / mu.dot(mu)
+    mu_scaled = mu / mu.dot(mu)
+    B_perp = B - (B @ mu.to(B.dtype))[:, None] * mu_scaled.to(B.dtype)[None, :]
+    assert float((B_perp @ mu.to(B.dtype)).abs().max()) < 1e-12                       # blind to the mean direction
+    k_split = x @ po.w_hat(A, B_perp, freq, n_kv, d).T + alpha[:, None] * kbar[None, :]
+    k_aug = x @ po.w_hat(pk.A, pk.B, pk.freq, n_kv, d).T
+    assert torch.allclose(k_aug, k_split, rtol=1e-12, atol=1e-12)
