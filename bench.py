@@ -142,6 +142,9 @@ class Stack:
         # PKV_BENCH_INLINE_ABSORB=1: the write alone as prologue and pkv_decode_attn_q (absorption inside the attention
         # kernel). Measured slower at present (251 against 196 us per layer): the default keeps the fused prologue.
         self.inline_absorb = os.environ.get("PKV_BENCH_INLINE_ABSORB", "0") == "1"
+        # PKV_BENCH_POLLED=0: the attention waits for the whole launch before it instead of polling the
+        # operand-ready counters that launch raises
+        self.polled = os.environ.get("PKV_BENCH_POLLED", "1") == "1"
         self.layers, self.caches = [], []
         g = torch.Generator(device=device).manual_seed(seed)
         for l in range(n_layers):
@@ -236,13 +239,14 @@ class Stack:
                 pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], None, None, ws, v=self.v_new[l])
                 n += 1
             elif fused:                                               # newest token's write + absorb: one launch
-                pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l])
+                pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l],
+                                 signal=self.polled and chained and not self.simt)
                 n += 2 if self.v_bits else 1                          # quantised V pages: their own writer launch
             else:
                 if write:
                     pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
                     n += 2
-                pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
+                pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt, signal=self.polled and chained and not self.simt)
                 n += 1
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
@@ -254,7 +258,7 @@ class Stack:
                 pk.attend_q_step(cache, self.q[l], self.qpos, ws, early=chained, tail_written=True, query_ready=True)
             else:
                 pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=chained and not fused,
-                               after_prologue=chained and fused)
+                               after_prologue=chained and fused, polled=self.polled and chained and not self.simt)
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
@@ -631,11 +635,12 @@ def run_sharded(st, args, dist, world, want_e2e=False):
                 pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, None, None, ws, v=st.v_new[l, :B4])
             pk.attend_q_step(cache, st.q[l, :B4], qpos, ws, early=chained, tail_written=owner, query_ready=True, **out_kw)
             return
+        sig = chained and st.polled and not st.simt
         if owner:
-            pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4])
+            pk.prologue_step(cache, st.x_new[l, :B4], wpos, wslots, st.q[l, :B4], qpos, ws, v=st.v_new[l, :B4], signal=sig)
         else:
-            pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt)
-        early = {} if not chained else (dict(after_prologue=True) if owner else dict(after_absorb=True))
+            pk.absorb_step(st.q[l, :B4], qpos, ws, operand=not st.simt, signal=sig)
+        early = {} if not chained else (dict(after_prologue=True, polled=sig) if owner else dict(after_absorb=True, polled=sig))
         if events is not None:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -280,6 +280,30 @@ int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cache, const vo
                     float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
                     void* stream);
 
+/* Operand-ready counters: the three calls of a decode step with one more argument, qsync_dev -- int32
+ * [2 * batch] in device memory, zero before its first use, owned by the caller, one array per operand buffer.
+ * pkv_absorb_sync / pkv_decode_prologue_sync raise qsync_dev[b] once for each group of 8 query heads of
+ * sequence b whose operand rows are in place; pkv_decode_attn_sync (tensor-core kernel, PKV_ATTN_EARLY_STREAM
+ * required, launched directly behind one of the two on the same stream) then polls that counter (bounded; a
+ * give-up is status 1 / where 11) instead of waiting for the whole launch before it: the attention starts as
+ * soon as the queries are absorbed, while e.g. the prologue's cache write of the newest token still runs
+ * (the last page of a sequence is still only fetched after that launch has completed, PKV_ATTN_TAIL_WRITTEN).
+ * The attention launch clears the counters when its last CTA of a sequence is done with the operand.
+ * qsync_dev NULL: exactly the plain calls.  No counterpart in the reference (its host waits for whole
+ * launches). */
+int pkv_absorb_sync(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev, const float* phasors_dev,
+                    int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev, int32_t* qsync_dev, void* stream);
+int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
+                             const int32_t* write_positions_dev, const int32_t* slots_dev, const void* v_rows_dev,
+                             const float* q_dev, const int32_t* query_positions_dev, int32_t batch,
+                             float* latent_out_dev, float* scratch_dev, float* qabs_out_dev, uint8_t* qop_out_dev,
+                             int32_t* qsync_dev, int32_t* status_dev, void* stream);
+int pkv_decode_attn_sync(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev, int32_t* qsync_dev,
+                         const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
+                         int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
+                         float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
+                         void* stream);
+
 /* pkv_decode_attn on RAW queries: q_dev [B, n_q, head_dim] fp32 pre-RoPE at query_positions_dev [B].
  * The tensor-core kernel absorbs them itself (every CTA forms the NVFP4 operand of its sequence in
  * shared memory with the arithmetic of pkv_absorb: same bits, same results) - no pkv_absorb launch, no

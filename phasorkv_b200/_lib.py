@@ -77,6 +77,12 @@ SIGNATURES = {
                                       c_void_p]),
     "pkv_decode_attn": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                   c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "pkv_absorb_sync": (c_int32, [POINTER(Layer), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "pkv_decode_prologue_sync": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p]),
+    "pkv_decode_attn_sync": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int32,
+                                       c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_q": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_void_p, c_int32, c_void_p, c_int32,
                                     c_int32, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "pkv_decode_attn_noalloc": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_int32,

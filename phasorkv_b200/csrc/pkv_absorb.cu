@@ -24,6 +24,12 @@ extern "C" int64_t pkv_query_operand_bytes(int32_t W) {
 extern "C" int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
                           const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev,
                           void* stream) {
+    return pkv_absorb_sync(layer, q_dev, positions_dev, phasors_dev, batch, qabs_out_dev, qop_out_dev, nullptr, stream);
+}
+
+extern "C" int pkv_absorb_sync(const pkv_layer_t* layer, const float* q_dev, const int32_t* positions_dev,
+                               const float* phasors_dev, int32_t batch, float* qabs_out_dev, uint8_t* qop_out_dev,
+                               int32_t* qsync_dev, void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     if (batch < 0) return PKV_ERR_INVALID;
@@ -37,7 +43,9 @@ extern "C" int pkv_absorb(const pkv_layer_t* layer, const float* q_dev, const in
         if (((uintptr_t)qop_out_dev) & 1023u) return PKV_ERR_INVALID;
     }
     if (batch == 0) return PKV_OK;
-    const Args P = make_args(layer, q_dev, positions_dev, phasors_dev, qabs_out_dev, qop_out_dev);
+    if (qsync_dev && !qop_out_dev) return PKV_ERR_INVALID;          // the signal says "operand in place"
+    Args P = make_args(layer, q_dev, positions_dev, phasors_dev, qabs_out_dev, qop_out_dev);
+    P.qsync = qsync_dev;
     PKV_CUDA_TRY(pkv_launch_chained(pkv_absorb_kernel, dim3(batch, (layer->n_q + HG - 1) / HG), dim3(NT),
                                     smem_bytes(layer->head_dim, Wp), (cudaStream_t)stream, P));   // < 48 KB: no opt-in needed
     return PKV_OK;

@@ -48,6 +48,7 @@ struct Args {
     float* qabs_out;                // [batch][n_q][W] or null
     uint8_t* qop_out;               // operand blobs or null
     long qop_bytes;
+    int32_t* qsync;                 // [2 * batch] or null: qsync[b] counts the head groups of sequence b whose operand rows are in place
 };
 
 inline Args make_args(const pkv_layer_t* L, const float* q, const int32_t* positions, const float* phasors, float* qabs_out,
@@ -60,6 +61,7 @@ inline Args make_args(const pkv_layer_t* L, const float* q, const int32_t* posit
     P.attn_scale = L->attn_scale;
     P.qabs_out = qabs_out; P.qop_out = qop_out;
     P.qop_bytes = pkv_page_bytes(2 * L->R + L->R_s) + 512;
+    P.qsync = nullptr;
     return P;
 }
 
@@ -208,6 +210,13 @@ __device__ __forceinline__ void body(const Args& P, int b, int hg, float* sm) {
             blob[codes_bytes + pkv_scale_offset(n, j)] = sb;
             if (j == 0 && term == 0) row_scale[h0 + h] = second;
         }
+    }
+    // Operand-ready signal for an attention launch that polls instead of waiting for this whole grid: the rows
+    // of this head group are made visible device-wide, then the sequence's counter goes up by one.
+    if (P.qsync) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(P.qsync + b, 1);
     }
 }
 

@@ -11,7 +11,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
                        int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream,
-                       const float* q_raw_dev = nullptr, const int32_t* q_positions_dev = nullptr);
+                       const float* q_raw_dev = nullptr, const int32_t* q_positions_dev = nullptr, int32_t* qsync_dev = nullptr);
 
 namespace {
 
@@ -233,6 +233,15 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
                                int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
                                float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
                                void* stream) {
+    return pkv_decode_attn_sync(layer, cache, q_dev, nullptr, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
+                                partials_dev, scores_out_dev, scores_stride, status_dev, out_dev, stream);
+}
+
+extern "C" int pkv_decode_attn_sync(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* q_dev, int32_t* qsync_dev,
+                                    const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev,
+                                    int32_t batch, int32_t n_split, uint32_t flags, float* partials_dev,
+                                    float* scores_out_dev, int64_t scores_stride, int32_t* status_dev, float* out_dev,
+                                    void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     st = pkv_check_cache(cache);
@@ -250,7 +259,8 @@ extern "C" int pkv_decode_attn(const pkv_layer_t* layer, const pkv_cache_t* cach
     cudaStream_t s = (cudaStream_t)stream;
     if (!(flags & PKV_ATTN_SIMT))
         return pkv_attn_tc_launch(layer, cache, q_dev, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
-                                  partials_dev, scores_out_dev, scores_stride, status_dev, out_dev, s);
+                                  partials_dev, scores_out_dev, scores_stride, status_dev, out_dev, s, nullptr, nullptr, qsync_dev);
+    if (qsync_dev) return PKV_ERR_INVALID;                 // the CUDA-core kernel waits for the whole launch before it
     if (((uintptr_t)q_dev) & 15u) return PKV_ERR_INVALID;
     const int rep = layer->n_q / layer->n_kv;
     const bool wide = pkv_padded_width(cache->W) == 256;

@@ -194,7 +194,20 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     constexpr int nks = WV ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
 
+    // Operand-ready counters (qa.qsync, the qsync_dev of pkv_decode_attn_sync): every CTA of a sequence, when it no longer
+    // needs the operand, counts itself in qsync[batch + b]; the last one clears both counters for the next use.
+    auto operand_released = [&]() {
+        if (qa.qsync && tid == 0) {
+            const int n_cta = (int)(gridDim.x * gridDim.z), nb = (int)gridDim.y;
+            if (atomicAdd(qa.qsync + nb + b, 1) == n_cta - 1) {
+                qa.qsync[b] = 0;
+                qa.qsync[nb + b] = 0;
+                __threadfence();
+            }
+        }
+    };
     if (P <= 0) {                                  // this split has no token: the neutral partial
+        operand_released();
         if (early) pkv_grid_wait();                // the partials may still be read by the launches before (see the epilogue)
         for (int i = tid; i < NQ * (DH + 2); i += blockDim.x) {
             int c = i % (DH + 2);
@@ -223,14 +236,37 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 if (lane == 0) {
                     // early mode: first fill the latent stages (but never with a page that is still being written)
                     if (!q_sent && (!early || i == min(P, nks) || (tail_written && p_lo + i == npages - 1))) {
-                        if (!waited) { pkv_grid_wait(); waited = true; }
+                        if (qa.qsync && early) {
+                            // the launch before signals each sequence's operand as soon as it is in place (it may
+                            // still be busy with other work, e.g. the cache write of the newest token): poll
+                            // the counter instead of waiting for that whole grid
+                            const int need = (NQ + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
+                            bool there = false;
+                            for (uint32_t it = 0; it < (WAIT_LIMIT >> 2) && !there; ++it) {    // about a second, then give up
+                                int v;
+                                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(qa.qsync + b) : "memory");
+                                there = v >= need;
+                                if (!there) {
+                                    if ((it & 63u) == 63u && X->abort_flag) break;
+                                    __nanosleep(40);
+                                }
+                            }
+                            if (!there) {
+                                if (!X->abort_flag && status) { atomicExch(&status[0], 1); atomicExch(&status[1], 11); }
+                                X->abort_flag = 1;
+                                stop = true;
+                            }
+                            asm volatile("fence.proxy.async;" ::: "memory");    // the operand was written by ordinary stores, the tile load reads it
+                        } else if (!waited) { pkv_grid_wait(); waited = true; }
+                        if (!stop) {
                         mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
                         tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
                         q_sent = true;
                         PKV_TL(5);
+                        }
                     }
                     if (!waited && tail_written && i < P && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
-                    if (i < P) {
+                    if (i < P && !stop) {
                         const int s = i % nks;
                         if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) {
                             stop = true;
@@ -680,6 +716,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #ifdef PKV_TIMELINE
     if (tid == 0) { PKV_TL(13); tl_buf[14] = pkv_globaltimer(); }
 #endif
+    operand_released();
     if (X->abort_flag) {
         // A role gave up (status says why). The slot of this CTA gets the neutral triple, so that a merge
         // enqueued behind this launch never folds in what an earlier call left in the partials.
@@ -775,7 +812,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
                        int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream,
-                       const float* q_raw_dev, const int32_t* q_positions_dev) {
+                       const float* q_raw_dev, const int32_t* q_positions_dev, int32_t* qsync_dev) {
     const int rep = layer->n_q / layer->n_kv;
     pkv_absorb_impl::Args qa;
     memset(&qa, 0, sizeof(qa));
@@ -785,6 +822,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
         qa = pkv_absorb_impl::make_args(layer, q_raw_dev, q_positions_dev, nullptr, nullptr, nullptr);
     } else if (!q_dev) {
         return PKV_ERR_INVALID;
+    }
+    if (qsync_dev) {                                // operand-ready counters: only with the operand of a launch directly before
+        if (q_raw_dev || !(flags & PKV_ATTN_EARLY_STREAM)) return PKV_ERR_INVALID;
+        qa.qsync = qsync_dev;
     }
     if (rep != 1 && rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;
     if (q_dev && (((uintptr_t)q_dev) & 15u)) return PKV_ERR_INVALID;

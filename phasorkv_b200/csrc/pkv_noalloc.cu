@@ -15,7 +15,7 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
                        const int32_t* page_table_dev, int32_t max_pages, const int32_t* seqlens_dev, int32_t batch,
                        int32_t n_split, uint32_t flags, float* partials_dev, float* scores_out_dev,
                        int64_t scores_stride, int32_t* status_dev, float* out_dev, cudaStream_t stream,
-                       const float* q_raw_dev = nullptr, const int32_t* q_positions_dev = nullptr);
+                       const float* q_raw_dev = nullptr, const int32_t* q_positions_dev = nullptr, int32_t* qsync_dev = nullptr);
 
 namespace {
 

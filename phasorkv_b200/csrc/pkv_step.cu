@@ -322,6 +322,16 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
                                    const float* q_dev, const int32_t* query_positions_dev, int32_t batch,
                                    float* latent_out_dev, float* scratch_dev, float* qabs_out_dev, uint8_t* qop_out_dev,
                                    int32_t* status_dev, void* stream) {
+    return pkv_decode_prologue_sync(layer, cache, x_dev, x_dtype, write_positions_dev, slots_dev, v_rows_dev, q_dev,
+                                    query_positions_dev, batch, latent_out_dev, scratch_dev, qabs_out_dev, qop_out_dev, nullptr,
+                                    status_dev, stream);
+}
+
+extern "C" int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
+                                        const int32_t* write_positions_dev, const int32_t* slots_dev, const void* v_rows_dev,
+                                        const float* q_dev, const int32_t* query_positions_dev, int32_t batch,
+                                        float* latent_out_dev, float* scratch_dev, float* qabs_out_dev, uint8_t* qop_out_dev,
+                                        int32_t* qsync_dev, int32_t* status_dev, void* stream) {
     int st = pkv_check_layer(layer);
     if (st) return st;
     if (batch < 0) return PKV_ERR_INVALID;
@@ -340,7 +350,7 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
         st = pkv_cache_write(layer, cache, x_dev, x_dtype, write_positions_dev, nullptr, slots_dev, batch, latent_out_dev,
                              scratch_dev, v_rows_dev, status_dev, stream);
         if (st || !q_dev) return st;
-        return pkv_absorb(layer, q_dev, query_positions_dev, nullptr, batch, qabs_out_dev, qop_out_dev, stream);
+        return pkv_absorb_sync(layer, q_dev, query_positions_dev, nullptr, batch, qabs_out_dev, qop_out_dev, qsync_dev, stream);
     }
     WriteArgs Wa;
     Wa.Bw = layer->Bw_dev; Wa.x = x_dev; Wa.n_tokens = batch; Wa.D = D; Wa.W = W; Wa.WP = WP; Wa.R = layer->R;
@@ -353,7 +363,9 @@ extern "C" int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* 
     Wa.v_vecs = with_v ? cache->n_kv * cache->head_dim * 2 / 16 : 0;
     Wa.n_kv = cache->n_kv;
     Wa.n_tiles = layer->R / PC + (WP - 2 * layer->R) / PC;
-    const pkv_absorb_impl::Args Aa = pkv_absorb_impl::make_args(layer, q_dev, query_positions_dev, nullptr, qabs_out_dev, qop_out_dev);
+    if (qsync_dev && !(q_dev && qop_out_dev)) return PKV_ERR_INVALID;
+    pkv_absorb_impl::Args Aa = pkv_absorb_impl::make_args(layer, q_dev, query_positions_dev, nullptr, qabs_out_dev, qop_out_dev);
+    Aa.qsync = qsync_dev;
     size_t smem = WRITE_SMEM;
     const size_t absorb_smem = pkv_absorb_impl::smem_bytes(layer->head_dim, WP);
     if (absorb_smem > smem) smem = absorb_smem;

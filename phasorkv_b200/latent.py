@@ -142,6 +142,9 @@ class DecodeWorkspace:
         self.packed = torch.empty((batch, n_q, head_dim + 2), dtype=torch.float32, device=device)
         self.out = torch.empty((batch, n_q, head_dim), dtype=torch.float32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        # operand-ready counters of this workspace's query operand (absorb_step / prologue_step with signal=True,
+        # attend_step with polled=True): [ready per sequence | consumers done per sequence]
+        self.qsync = torch.zeros(2 * batch, dtype=torch.int32, device=device)
         self.wscratch = None                                                  # decode-time write, see write_scratch()
         self.exact = None                                                     # exact-token partial, see exact_step()
 
@@ -391,21 +394,23 @@ class PhasorKey:
         groups = 4 if (not simt and self.n_kv == self.n_q) else 1
         return max(1, min(pages, (sms * per_sm) // max(1, batch * groups)))
 
-    def absorb_step(self, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace, operand: bool = True) -> None:
-        """q [B, H, d] fp32 at `positions` [B] -> ws.qabs (fp32) and, if asked, ws.qop (operand form)."""
+    def absorb_step(self, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace, operand: bool = True,
+                    signal: bool = False) -> None:
+        """q [B, H, d] fp32 at `positions` [B] -> ws.qabs (fp32) and, if asked, ws.qop (operand form).
+        `signal`: raise the workspace's operand-ready counters (for ``attend_step(polled=True)`` right behind)."""
         self._need_inv_freq("absorb_step")
         L = self._layer()
-        _lib.check(_lib.load().pkv_absorb(ctypes.byref(L), _lib.ptr(q), _lib.ptr(positions), None, q.shape[0],
-                                          _lib.ptr(ws.qabs), _lib.ptr(ws.qop) if operand else None,
-                                          _lib.current_stream()), "pkv_absorb")
+        _lib.check(_lib.load().pkv_absorb_sync(ctypes.byref(L), _lib.ptr(q), _lib.ptr(positions), None, q.shape[0],
+                                               _lib.ptr(ws.qabs), _lib.ptr(ws.qop) if operand else None,
+                                               _lib.ptr(ws.qsync) if signal else None, _lib.current_stream()), "pkv_absorb")
 
     def prologue_step(self, cache: PagedLatentCache, x: torch.Tensor, write_positions: torch.Tensor, slots: torch.Tensor,
                       q: Optional[torch.Tensor], query_positions: Optional[torch.Tensor], ws: DecodeWorkspace,
                       v: Optional[torch.Tensor] = None, latent_out: Optional[torch.Tensor] = None,
-                      operand: bool = True) -> None:
+                      operand: bool = True, signal: bool = False) -> None:
         """`write_paged` of the newest token of every sequence and `absorb_step` of the step's queries
         as one launch (same bits as the two calls). `q=None`: the write alone (the queries then go to
-        `attend_q_step`)."""
+        `attend_q_step`). `signal`: as for `absorb_step`."""
         self._need_inv_freq("prologue_step")
         L = self._layer()
         x = self._x(x)
@@ -414,12 +419,14 @@ class PhasorKey:
             v = None
         if v is not None:
             v = v.to(torch.bfloat16).contiguous()
-        _lib.check(_lib.load().pkv_decode_prologue(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(x), self._xdt(x),
-                                                   _lib.ptr(write_positions), _lib.ptr(slots), _lib.ptr(v), _lib.ptr(q),
-                                                   _lib.ptr(query_positions), x.shape[0], _lib.ptr(latent_out),
-                                                   _lib.ptr(getattr(ws, "wscratch", None)), _lib.ptr(ws.qabs),
-                                                   _lib.ptr(ws.qop) if operand else None, _lib.ptr(self._dev["status"]),
-                                                   _lib.current_stream()), "pkv_decode_prologue")
+        _lib.check(_lib.load().pkv_decode_prologue_sync(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(x), self._xdt(x),
+                                                        _lib.ptr(write_positions), _lib.ptr(slots), _lib.ptr(v), _lib.ptr(q),
+                                                        _lib.ptr(query_positions), x.shape[0], _lib.ptr(latent_out),
+                                                        _lib.ptr(getattr(ws, "wscratch", None)), _lib.ptr(ws.qabs),
+                                                        _lib.ptr(ws.qop) if operand else None,
+                                                        _lib.ptr(ws.qsync) if (signal and q is not None and operand) else None,
+                                                        _lib.ptr(self._dev["status"]), _lib.current_stream()),
+                   "pkv_decode_prologue")
 
     def attend_q_step(self, cache: PagedLatentCache, q: torch.Tensor, positions: torch.Tensor, ws: DecodeWorkspace,
                       scores_only: bool = False, scores_out: Optional[torch.Tensor] = None,
@@ -447,9 +454,11 @@ class PhasorKey:
     def attend_step(self, cache: PagedLatentCache, ws: DecodeWorkspace, simt: bool = False, scores_only: bool = False,
                     scores_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                     packed_out: Optional[torch.Tensor] = None, after_absorb: bool = False,
-                    after_prologue: bool = False) -> None:
+                    after_prologue: bool = False, polled: bool = False) -> None:
         """Split-T attention of the absorbed queries in `ws` over `cache` -> ws.partials; with `out`
-        [B, H, d] the splits are merged as well (a merge launch enqueued right behind)."""
+        [B, H, d] the splits are merged as well (a merge launch enqueued right behind). `polled` (with
+        `after_absorb` / `after_prologue`, whose launch was made with ``signal=True``): the kernel polls the
+        workspace's operand-ready counters instead of waiting for that whole launch."""
         L = self._layer()
         flags = (_lib.ATTN_SIMT if simt else 0) | (_lib.ATTN_SCORES_ONLY if scores_only else 0)
         if after_absorb and not simt:                   # the launch enqueued just before was absorb_step: stream pages early
@@ -460,11 +469,13 @@ class PhasorKey:
             out, flags = packed_out, flags | _lib.ATTN_PACKED_OUT
         qsrc = ws.qabs if simt else ws.qop
         stride = 0 if scores_out is None else scores_out.shape[-1]
-        _lib.check(_lib.load().pkv_decode_attn(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(qsrc),
-                                               _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
-                                               ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
-                                               stride, _lib.ptr(ws.status), _lib.ptr(out),
-                                               _lib.current_stream()), "pkv_decode_attn")
+        poll = polled and not simt and (after_absorb or after_prologue)
+        _lib.check(_lib.load().pkv_decode_attn_sync(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(qsrc),
+                                                    _lib.ptr(ws.qsync) if poll else None,
+                                                    _lib.ptr(cache.page_table), cache.max_pages, _lib.ptr(cache.seqlens),
+                                                    ws.batch, ws.n_split, flags, _lib.ptr(ws.partials), _lib.ptr(scores_out),
+                                                    stride, _lib.ptr(ws.status), _lib.ptr(out),
+                                                    _lib.current_stream()), "pkv_decode_attn")
 
     def exact_step(self, q: torch.Tensor, positions: torch.Tensor, k_exact: torch.Tensor, v_exact: torch.Tensor,
                    ws: DecodeWorkspace, n_exact: Optional[torch.Tensor] = None) -> torch.Tensor:

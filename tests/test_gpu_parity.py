@@ -448,6 +448,72 @@ def test_attention_behind_prologue_sees_the_newest_token(n_split):
         assert rel(out_early[b].cpu(), O_ref) < OUT_TOL
 
 
+@pytest.mark.parametrize("producer", ["absorb", "prologue"])
+def test_attention_polls_operand_ready_counters(producer):
+    """pkv_decode_attn_sync: the attention polls the counters its producer raises per sequence instead of waiting for
+    the whole launch before it. Same result as the plain, fully ordered launches, round after round (the counters
+    are cleared by the attention itself), scores-only mode included."""
+    sc = Scenario("cfg2", seqlens=(300, 129, 128, 1), pos0=5000)
+    pk, B = sc.pk, sc.B
+    g = torch.Generator().manual_seed(78)
+    lens = torch.tensor(sc.seqlens, dtype=torch.int32, device="cuda")
+    slots = sc.cache.slots(torch.arange(B, dtype=torch.int32, device="cuda"), lens - 1)
+    wpos = (lens - 1 + 5000).contiguous()
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    ws = pk.workspace(B, 3)
+    outs = torch.zeros((3, B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
+    refs = torch.zeros_like(outs)
+    xs = [(synth.make_hidden(g, B, 4096) * (k + 1.0)).cuda() for k in range(3)]
+    vs = [(synth.make_values(g, B, sc.spec.n_kv, sc.spec.head_dim) * (k + 1.0)).cuda() for k in range(3)]
+    for k in range(3):
+        if producer == "absorb":
+            pk.absorb_step(q, qpos, ws, signal=True)
+            pk.attend_step(sc.cache, ws, out=outs[k], after_absorb=True, polled=True)
+        else:
+            pk.prologue_step(sc.cache, xs[k], wpos, slots, q, qpos, ws, v=vs[k], signal=True)
+            pk.attend_step(sc.cache, ws, out=outs[k], after_prologue=True, polled=True)
+        pk.attend_step(sc.cache, ws, out=refs[k])                         # waits for everything before it
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0 and int(ws.qsync.abs().sum()) == 0
+    for k in range(3):
+        assert torch.equal(outs[k], refs[k]), k
+    assert float(refs[0].abs().max()) > 0
+    if producer == "prologue":
+        assert not torch.equal(refs[0], refs[1])                          # the newest token really changed
+    # K path
+    pk.absorb_step(q, qpos, ws, signal=True)
+    pk.attend_step(sc.cache, ws, scores_only=True, after_absorb=True, polled=True)
+    pk.merge_step(ws, normalise=False, packed=True)
+    a = ws.packed.clone()
+    pk.attend_step(sc.cache, ws, scores_only=True)
+    pk.merge_step(ws, normalise=False, packed=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a[..., -2:], ws.packed[..., -2:]) and int(ws.qsync.abs().sum()) == 0
+
+
+def test_polling_attention_gives_up_when_nothing_signals():
+    """A polled attention launch whose producer never raises the counters: the bounded poll runs out, status says
+    so (1 = a wait gave up, where = 11: the operand), the outputs are zero (every CTA leaves the neutral partial),
+    the counters are clean again, and the next, properly signalled round is right."""
+    sc = Scenario("cfg2", seqlens=(200, 64))
+    pk = sc.pk
+    ws = pk.workspace(sc.B, 2)
+    q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    pk.absorb_step(q, qpos, ws)                                           # no signal
+    out = torch.ones((sc.B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
+    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True)
+    torch.cuda.synchronize()
+    assert ws.status[:2].tolist() == [1, 11]
+    assert float(out.abs().max()) == 0.0 and int(ws.qsync.abs().sum()) == 0
+    ws.status.zero_()
+    pk.absorb_step(q, qpos, ws, signal=True)
+    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True)
+    ref = torch.zeros_like(out)
+    pk.attend_step(sc.cache, ws, out=ref)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0 and torch.equal(out, ref) and float(ref.abs().max()) > 0
+
+
 def test_attention_behind_chunk_write_and_prologue():
     """The first decode step after a prefill, all on one stream with nothing in between: a chunk write
     of the cache (tensor-core kernel), the prologue of the newest token, the attention that streams pages
