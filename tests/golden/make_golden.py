@@ -261,6 +261,53 @@ def attend_merge():
     print("attend_merge")
 
 
+def phasorkey_llama_heads():
+    """A real Factorization(..., "band8", "xq") at the Llama-3.1-8B head shape (32 query heads, 8 kv heads,
+    head_dim 128, rope base 500000; d_model cut to 512 to keep the fixture small) with water-filled ranks at 25 %
+    of K: the arrays PhasorKey builds from it, its write / absorb / scores on seeded inputs at long positions, and
+    the scores from keys rebuilt with W_hat and rotated by HF's apply_rotary_pos_emb (slow band unrotated)."""
+    g = torch.Generator().manual_seed(4406)
+    D, n_q, n_kv, d = 512, 32, 8, 128
+    h = d // 2
+    T = 200
+    inv_freq = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -2.0 * torch.arange(h, dtype=torch.float64) / d)
+    W = torch.randn(n_kv * d, D, generator=g, dtype=torch.float64) / D ** 0.5
+    W *= torch.exp(-torch.arange(D, dtype=torch.float64) / 96.0)[None, :] * 4.0      # a falling spectrum: low ranks carry most
+    X = torch.randn(4 * D, D, generator=g, dtype=torch.float64)
+    Cx = X.T @ X / X.shape[0]
+    q2 = torch.rand(n_q, d, generator=g, dtype=torch.float64) + 0.1
+    fac = Factorization(W, Cx, q2, n_kv, d, "band8", "xq", device="cpu")
+    ranks = fac.ranks(fac.full_size // 4)
+    pk = PhasorKey(fac, ranks, n_q)
+    rot = _Rotary(inv_freq, 1.0)
+    pos_k = torch.arange(T) + 100000
+    pos_q = torch.tensor([100000 + T])
+    ph_k, ph_q = rope_phasors(rot, pos_k), rope_phasors(rot, pos_q)
+    x = torch.randn(T, D, generator=g, dtype=torch.float64)
+    q = torch.randn(n_q, 1, d, generator=g, dtype=torch.float64)
+    rows, qa = pk.write(x, ph_k), pk.absorb(q, ph_q)
+    S = pk.scores(qa, rows)
+    W_hat = fac.reconstruct(ranks)
+    pk_, pq_ = ph_k.clone(), ph_q.clone()
+    pk_[:, fac.nope] = pk_[0, 0].abs().to(pk_.dtype)
+    pq_[:, fac.nope] = pq_[0, 0].abs().to(pq_.dtype)
+    k = (x @ W_hat.T).reshape(T, n_kv, d).transpose(0, 1)[None]
+    cos_k, sin_k = torch.cat([pk_.real, pk_.real], -1)[None], torch.cat([pk_.imag, pk_.imag], -1)[None]
+    cos_q, sin_q = torch.cat([pq_.real, pq_.real], -1)[None], torch.cat([pq_.imag, pq_.imag], -1)[None]
+    _, kr = apply_rotary_pos_emb(k, k, cos_k, sin_k)
+    qr, _ = apply_rotary_pos_emb(q[None], q[None], cos_q, sin_q)
+    S2 = qr[0] @ kr[0].repeat_interleave(n_q // n_kv, dim=0).transpose(1, 2)
+    rel = ((S - S2).norm() / S2.norm()).item()
+    print("llama heads: ranks sum", sum(ranks), "R", pk.R, "R_s", pk.R_s, "width", pk.cache_width, "identity rel", rel)
+    assert rel < 1e-12 and pk.cache_width <= 256
+    np.savez_compressed(os.path.join(HERE, "phasorkey_llama_heads.npz"), dims=np.array([D, n_q, n_kv, d]), inv_freq=inv_freq.numpy(),
+                        ranks=np.array(ranks), A=pk.A.to(torch.complex64).numpy(), B=pk.B.to(torch.complex64).numpy(),
+                        freq=pk.freq.numpy(), slow=pk.slow.numpy(), A_s=pk.A_s.float().numpy(), B_s=pk.B_s.float().numpy(),
+                        x=x.float().numpy(), q=q.float().numpy(), pos_k=pos_k.numpy(), pos_q=pos_q.numpy(),
+                        rows=rows.float().numpy(), qabs=qa.float().numpy(), scores=S.float().numpy(), scores_hf=S2.float().numpy())
+    print("phasorkey_llama_heads")
+
+
 def v_tiers():
     """Per-token low-bit tiers of the reference (kernels/nvfp4.quantize_per_token) on rows of 128 values, the
     shape of one (token, kv head) value row: 3-bit and 2-bit, with ties, an all-zero row, a row below the
@@ -303,3 +350,5 @@ if __name__ == "__main__":
             attend_merge()
         if want("v_tiers"):
             v_tiers()
+        if want("phasorkey_llama_heads"):
+            phasorkey_llama_heads()

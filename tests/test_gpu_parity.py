@@ -828,6 +828,52 @@ def test_hf_llama_attention_patch_decodes_like_the_model():
         assert rel(model(input_ids=ids).logits, ref(input_ids=ids).logits) < 1e-6
 
 
+def test_real_factorization_at_llama_head_shape():
+    """Factors of a reference Factorization(W, Cx, q2, 8, 128, "band8", "xq") with water-filled ranks (32 query heads,
+    8 kv heads, head_dim 128, rope base 500000; energy-sorted dims, 110 complex + 36 slow reals = width 256), positions
+    beyond 100000: constructor arrays -> write -> absorb -> scores against the reference's own output and against keys
+    rebuilt from W_hat with HF's rotary (oracle #2); then the quantised cache through the tensor-core decode against
+    fp32 scoring on the dequantised cache (oracle #1)."""
+    g = _golden("phasorkey_llama_heads.npz")
+    D, n_q, n_kv, d = (int(v) for v in g["dims"])
+    t = lambda k: torch.from_numpy(g[k])
+    inv_freq = t("inv_freq")
+    pk = PhasorKey.from_factors(t("A"), t("B"), t("freq"), n_q, n_kv, d, inv_freq, t("A_s"), t("B_s"), t("slow"))
+    assert pk.cache_width == 256 and pk.R == 110 and pk.R_s == 36
+    x, q = t("x"), t("q")
+    ph_k, ph_q = po.rope_phasors(inv_freq, t("pos_k")), po.rope_phasors(inv_freq, t("pos_q"))
+    rows, qabs = pk.write(x, ph_k), pk.absorb(q, ph_q)
+    assert rel(rows.cpu(), t("rows")) < 1e-5 and rel(qabs.cpu(), t("qabs")) < 1e-5
+    S = PhasorKey.scores(qabs, rows).cpu()
+    assert rel(S, t("scores")) < 1e-5
+    assert rel(S, t("scores_hf")) < LOGIT_TOL
+    # quantised cache, decode on the tensor cores
+    T = x.shape[0]
+    pk.calibrate_second(rows)
+    cache = pk.new_cache(1, T)
+    lp = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = cache.slots(torch.zeros_like(lp), lp)
+    gen = torch.Generator().manual_seed(9)
+    v = synth.make_values(gen, T, n_kv, d)
+    pk.write_paged(cache, x.cuda(), t("pos_k").to(torch.int32).cuda(), slots, v=v.cuda())
+    cache.seqlens.fill_(T)
+    ws = pk.workspace(1, 2)
+    Sd = torch.zeros((1, n_q, T), device="cuda")
+    pk.absorb_step(q[:, 0][None].contiguous().cuda(), t("pos_q").to(torch.int32).cuda(), ws)
+    pk.attend_step(cache, ws, scores_out=Sd, out=ws.out, after_absorb=True)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    hat, codes, scales = cache.read(slots, pk.second)
+    # the stored bits are the reference quantiser's bits of the rows the write kernel itself produced
+    out = torch.empty((T, 256), device="cuda")
+    pk.write_paged(None, x.cuda(), t("pos_k").to(torch.int32).cuda(), None, latent_out=out)
+    o_codes, o_scales, _ = po.nvfp4_quantize(out.cpu(), torch.tensor([pk.second]))
+    assert torch.equal(codes.cpu(), po.pack_nibbles(o_codes)) and torch.equal(scales.cpu(), o_scales)
+    S_ref = PhasorKey.scores(qabs, hat)[:, 0].cpu()
+    assert rel(Sd[0].cpu(), S_ref) < LOGIT_TOL
+    assert rel(ws.out[0].cpu(), po.attend(S_ref, v, n_kv, d)) < OUT_TOL
+
+
 def test_mean_direction_split_through_the_kernels():
     """The mean-direction split (k = A Q(B_perp x) + alpha * W mu, phasorkv/kvmethods.py:895-899) as a PhasorKey
     with d/2 further latent dims: the CUDA write / absorb / scores reproduce 'rebuild the split keys, rotate with
