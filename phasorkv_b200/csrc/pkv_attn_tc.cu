@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                             // the counter instead of waiting for that whole grid
                             const int need = (NQ + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
                             bool there = false;
-                            for (uint32_t it = 0; it < (WAIT_LIMIT >> 2) && !there; ++it) {    // about a second, then give up
+                            for (uint32_t it = 0; it < (WAIT_LIMIT >> 4) && !there; ++it) {    // a fraction of a second, then give up
                                 int v;
                                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(qa.qsync + b) : "memory");
                                 there = v >= need;
@@ -374,10 +374,14 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                     const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + ((g * REP) >> 3) * 256;
                     const uint64_t v_desc = smem_desc(va, V_STAGE_BYTES / 2, 1024, SWZ_128B);
                     const uint64_t p_desc = smem_desc(pa, PGS, 128, SWZ_NONE);
+#ifndef PKV_VQ_SKIP_PV                                                // (development switch: no P.V MMAs)
 #pragma unroll
                     for (int k = 0; k < PKV_PAGE_TOKENS / 16; ++k)
                         mma_bf16(tb + TM_O + 16 * g, v_desc + (uint64_t)(k * 2048 / 16), p_desc + (uint64_t)(k * 2 * PGS / 16), idesc_o,
                                  !(i == 0 && k == 0));
+#else
+                    (void)v_desc; (void)p_desc;
+#endif
                     tc_commit(&X->v_empty[s]);
                 }
                 tc_commit(&X->pv_done[pb]);
@@ -447,6 +451,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 const uint32_t sbits = *reinterpret_cast<const uint16_t*>(raw + PKV_PAGE_TOKENS * 64 + r * 2);
                 const uint32_t s2 = sbits | (sbits << 16);
                 const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2);
+#ifndef PKV_VQ_SKIP_CONVERT                                           // (development switch: barrier traffic only)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 64 + ((c ^ sw) << 4));
@@ -477,6 +482,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                             make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
+#else
+                (void)dst; (void)scale2; (void)sw; (void)raw;
+#endif
                 fence_proxy_async_smem();                            // generic-proxy writes -> visible to the tensor core
                 mbar_arrive(&X->v_full[bs]);
                 mbar_arrive(&X->vr_empty[rs]);

@@ -503,7 +503,7 @@ def test_polling_attention_gives_up_when_nothing_signals():
     out = torch.ones((sc.B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
     pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True)
     torch.cuda.synchronize()
-    assert ws.status[:2].tolist() == [1, 11]
+    assert int(ws.status[0]) == 1 and int(ws.status[1]) in (11, 30)      # the poll, or the role that waits for the operand it feeds
     assert float(out.abs().max()) == 0.0 and int(ws.qsync.abs().sum()) == 0
     ws.status.zero_()
     pk.absorb_step(q, qpos, ws, signal=True)
