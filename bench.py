@@ -213,7 +213,7 @@ class Stack:
         x[:, self.outliers] *= 20.0
         return x
 
-    def step(self, events=None, scores_only=False, write=True, pre=None, post=None, chunk_events=None, chain=None):
+    def step(self, events=None, scores_only=False, write=True, pre=None, post=None, chunk_events=None, chain=None, merge=True):
         """One decode step over all layers. `events`: list receiving (start, end) CUDA events around
         each attention launch (`chunk_events`: around each chunk write). `pre(l)` / `post(l)` run on the
         host before / after layer l is enqueued. `chain`: launch the attention as part of the dependent-launch
@@ -262,8 +262,9 @@ class Stack:
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
-            pk.merge_step(ws, out=self.out[l])
-            n += 2
+            if merge:
+                pk.merge_step(ws, out=self.out[l])
+            n += 2 if merge else 1
             if post is not None:
                 post(l)
         self.launches_per_layer = n // len(self.layers)
@@ -446,9 +447,10 @@ def run_b200(args):
         for l, (pk_, cache) in enumerate(zip(st.layers, st.caches)):
             pk_.attend_step(cache, st.ws[l & 1], simt=st.simt, scores_only=True)
     st.step(scores_only=True, write=False)                     # operands of the last layers are in both workspaces
-    g_attn, g_step = capture(k_attention_only), capture(lambda: st.step(scores_only=True, write=False))
+    k_step = lambda: st.step(scores_only=True, write=False, merge=False)       # K2 + K3: absorb, then scores + log-sum-exp per split
+    g_attn, g_step = capture(k_attention_only), capture(k_step)
     attn_k_ms = timed(g_attn, 4 * nk, 3, dist) / L if g_attn else attn_k_eager_ms
-    ms_kstep = timed(g_step, 4 * nk, 3, dist) if g_step else timed(lambda: st.step(scores_only=True, write=False), nk, 2, dist)
+    ms_kstep = timed(g_step, 4 * nk, 3, dist) if g_step else timed(k_step, nk, 2, dist)
 
     peak_read = read_probe_gbs(device) if args.algo == "tc" else None
 
@@ -551,7 +553,7 @@ def run_b200(args):
         "k_path_step_us_per_layer": round(ms_kstep * 1e3 / L, 2),
         "k_path_eager_us_per_launch": round(attn_k_eager_ms * 1e3, 2),
         "k_path_note": "k_path_us_per_layer: scores-only attention, %d layers replayed as one CUDA graph; k_path_step: absorb + "
-                       "scores-only attention + log-sum-exp merge per layer as one dependent-launch chain in a CUDA graph; "
+                       "scores-only attention (logits and log-sum-exp per split) per layer as one dependent-launch chain in a CUDA graph; "
                        "eager: CUDA events around each scores-only launch enqueued from the host" % L,
         "full_us_per_layer": round(ms_step * 1e3 / L, 2),
         "hbm_gbs": round(achieved, 1),

@@ -156,10 +156,10 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     if (tid == 0) {
         mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
-        for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], VQ ? 128 : 1); mbar_init(&X->v_empty[s], 1); }
-        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 128); }
+        for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
+        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 1); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }   // quantised V: two P.V issuers
         mbar_init(&X->sm_bar, WV ? 128 : 256);
         X->abort_flag = 0;
         fence_barrier_init();
@@ -340,22 +340,26 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 }
             }
         }
-    } else if (warp == 2 || warp == 1) {
+    } else if (warp == 2 || warp == 1 || (VQ && warp == 3)) {
         // ================================================================== MMA issuer
         // One thread issues every tcgen05 instruction of its pages; what bounds it is the latency of its own
         // instruction chain (two satisfied barrier waits, 4 + 4 tcgen05 issues of ~75 cycles, two commits:
         // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V it is the longest
         // link, so the warp the V stream leaves idle becomes a second issuer: warp 2 takes the even pages,
         // warp 1 the odd ones (each feeds the softmax group of its parity).
+        // With quantised V a page's bytes last a third as long, and the P.V issue chain (8 MMAs, a wait and a commit per
+        // kv head) becomes the longest link: warp 3 then issues the P.V of the odd kv heads, warp 2 scores + even heads.
+        constexpr int PV_STEP = VQ ? 2 : 1;
         if (lane == 0) {
             const int first = (!WV && warp == 1) ? 1 : 0;
             constexpr int STEP = WV ? 1 : 2;
             const uint32_t sfb_tm = tb + TM_SFB + (first ? 16u : 0u);
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
             constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
-            bool ok = wait_or_abort(&X->q_full, 0, X, status, 30);
+            const bool pv_only = VQ && warp == 3;
+            bool ok = pv_only || wait_or_abort(&X->q_full, 0, X, status, 30);
             if (warp == 2) PKV_TL(7);
-            if (ok) {
+            if (ok && !pv_only) {
                 tc_fence_after_sync();
                 for (int k = 0; k < C::KB; ++k)
                     tmem_cp_32x128b_warpx4(sfb_tm + 4 * k, smem_desc(sbase + C::Q_OFF + C::CODES + k * 512, 0, 128, SWZ_NONE));
@@ -365,7 +369,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 const int pb = i & 1;
                 if (!wait_or_abort(&X->p_full[pb], (i >> 1) & 1, X, status, 31)) return false;
                 tc_fence_after_sync();
-                for (int g = 0; g < NKV; ++g) {
+                for (int g = pv_only ? 1 : 0; g < NKV; g += PV_STEP) {
                     const int j = i * NKV + g, s = j % C::NVS;
                     if (!wait_or_abort(&X->v_full[s], (j / C::NVS) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
@@ -389,9 +393,12 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             };
             // stage, buffer and their barrier phases advance by counters (this thread's instruction chain is the
             // critical path: no divisions by run-time values in it)
+            if (pv_only) {                                   // the second P.V issuer: every page, odd kv heads
+                for (int i = 0; i < P && ok; ++i) ok = do_pv(i);
+            }
             int s = first % nks, buf = first % NSB;
             uint32_t k_phase = 0, s_round = 0;               // s_round = i / NSB
-            for (int i = first; i < P && ok; i += STEP) {
+            for (int i = first; i < P && ok && !pv_only; i += STEP) {
                 ok = wait_or_abort(&X->k_full[s], k_phase, X, status, 33);
                 if (ok && s_round > 0) ok = wait_or_abort(&X->s_empty[buf], (s_round - 1) & 1, X, status, 34);
                 if (!ok) break;
@@ -420,18 +427,17 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 buf += STEP;
                 if (buf >= NSB) { buf -= NSB; ++s_round; }
             }
-            if (ok && with_v) do_pv(P - 1);
+            if (ok && with_v && !pv_only) do_pv(P - 1);
         }
-    } else if (VQ && warp == 3) {
-        // spare warp of the first warpgroup
     } else if (VQ && warp >= 8) {
         // ================================================================== V converter (quantised V pages)
         // Thread = token row of the tile. A row is 64 bytes of E2M1 codes and one bf16 scale; it becomes 128
         // bf16 values (code value times scale, rounded to bf16: exact unless the code is +-1.5, +-3 or +-6,
         // then one rounding of at most 2^-9) in the 128-byte-swizzled layout a tensor tile load of a bf16
         // V page would have produced, which is what the P.V descriptors expect.
-        const int r = (warp - 8) * 32 + lane;
-        const uint32_t sw = ((uint32_t)r >> 1) & 3u;
+        // Each converter warp owns every fourth tile (a lane takes four token rows of it), so that four tiles are in
+        // work at once and the waits of one hide behind the arithmetic of the others.
+        const int cw = warp - 8;
         // bf16 bit patterns of the eight E2M1 magnitudes (0 .5 1 1.5 2 3 4 6) as byte tables for prmt
         constexpr uint32_t LO_A = 0xC0800000u, LO_B = 0xC0804000u, HI_A = 0x3F3F3F00u, HI_B = 0x40404040u;
         auto prmt = [](uint32_t a, uint32_t b, uint32_t c) -> uint32_t {
@@ -440,18 +446,23 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             return d;
         };
         bool ok = true;
-        for (int i = 0; i < P && ok; ++i) {
-            for (int g = 0; g < NKV; ++g) {
-                const int j = i * NKV + g, rs = j % NVR, bs = j % C::NVS;
-                ok = __all_sync(0xffffffffu, wait_or_abort(&X->vr_full[rs], (j / NVR) & 1, X, status, 50));
-                if (ok && j >= C::NVS) ok = __all_sync(0xffffffffu, wait_or_abort(&X->v_empty[bs], ((j / C::NVS) - 1) & 1, X, status, 51));
-                if (!ok) break;
-                const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
-                uint8_t* dst = smem + C::V_OFF + bs * V_STAGE_BYTES + r * 128;
+        const int n_tiles = P * NKV;
+        for (int j = cw; j < n_tiles && ok; j += 4) {
+            const int rs = j % NVR, bs = j % C::NVS;
+            ok = __all_sync(0xffffffffu, wait_or_abort(&X->vr_full[rs], (j / NVR) & 1, X, status, 50));
+            if (ok && j >= C::NVS) ok = __all_sync(0xffffffffu, wait_or_abort(&X->v_empty[bs], ((j / C::NVS) - 1) & 1, X, status, 51));
+            if (!ok) break;
+            const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
+            uint8_t* stage = smem + C::V_OFF + bs * V_STAGE_BYTES;
+#ifndef PKV_VQ_SKIP_CONVERT                                           // (development switch: barrier traffic only)
+#pragma unroll 1
+            for (int rg = 0; rg < 4; ++rg) {
+                const int r = rg * 32 + lane;
+                const uint32_t sw = ((uint32_t)r >> 1) & 3u;
+                uint8_t* dst = stage + r * 128;
                 const uint32_t sbits = *reinterpret_cast<const uint16_t*>(raw + PKV_PAGE_TOKENS * 64 + r * 2);
                 const uint32_t s2 = sbits | (sbits << 16);
                 const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2);
-#ifndef PKV_VQ_SKIP_CONVERT                                           // (development switch: barrier traffic only)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 64 + ((c ^ sw) << 4));
@@ -482,10 +493,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                             make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
+            }
 #else
-                (void)dst; (void)scale2; (void)sw; (void)raw;
+            (void)stage; (void)raw; (void)prmt; (void)LO_A; (void)LO_B; (void)HI_A; (void)HI_B;
 #endif
-                fence_proxy_async_smem();                            // generic-proxy writes -> visible to the tensor core
+            fence_proxy_async_smem();                                // generic-proxy writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
                 mbar_arrive(&X->v_full[bs]);
                 mbar_arrive(&X->vr_empty[rs]);
             }
