@@ -79,6 +79,15 @@ typedef struct pkv_layer {
     const void*    Bw_bf16x3_dev;    /* optional bf16 [3][Wp][D], Wp = 128 if 2R+R_s <= 128 else 256: Bw as the sum of
                                         three bf16 matrices (hi, mid, lo; rows past 2R+R_s zero).  Enables the
                                         tensor-core cache write for bf16 x; NULL selects the CUDA-core kernels */
+    const float*   second_blocks_dev;/* optional fp32 [(2R+R_s)/16]: the tensor scale of every 16-column block of the
+                                        latent, for tiers -- one static scale per 16-aligned span of the
+                                        energy-sorted latent, as the reference fixes them offline
+                                        (phasorkv/quant.py:119-124, phasorkv/kernels/latent_attn.py:149-152).  The
+                                        quantising calls use it in place of `second`; pkv_absorb / the prologue
+                                        multiply the query's columns by second_blocks[j] / second, so that the decode
+                                        kernels, which know one scale per layer, stay as they are (the fp32 absorbed
+                                        rows they write are then in the cache's units, not the reference's).  NULL:
+                                        `second` for every block */
 } pkv_layer_t;
 
 /* The paged cache of one layer.  A page holds PKV_PAGE_TOKENS tokens.
@@ -152,6 +161,10 @@ int pkv_set_scale_round_up(int32_t on);
  * rounding rules of phasorkv/quant.py:70-89).  rows_dev [n, W]; slots_dev [n]. */
 int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev,
                       int32_t n_tokens, float second, void* stream);
+/* The same with one tensor scale per 16-column block (second_blocks_dev fp32 [W/16]): quantize_nv_block applied
+ * tier by tier (phasorkv/kernels/latent_attn.py:255-262).  pkv_cache_read_tiered is the matching read-back. */
+int pkv_quantize_rows_tiered(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev,
+                             int32_t n_tokens, const float* second_blocks_dev, void* stream);
 
 /* Fused cache write: c = x B^T (complex), rotation by e^{i theta t} * attn_scale, slow block
  * unrotated, NVFP4 quantisation, paged store.  Replaces PhasorKey.write (phasorkv/latent.py:61-70)
@@ -198,6 +211,9 @@ int pkv_vq_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_to
  * codes_out [n, W/2] packed nibbles; scales_out [n, W/16] E4M3 bytes. */
 int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, float second,
                    float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream);
+int pkv_cache_read_tiered(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens,
+                          const float* second_blocks_dev, float* rows_out_dev, uint8_t* codes_out_dev,
+                          uint8_t* scales_out_dev, void* stream);
 
 /* The same entry points under the names of the reference's vocabulary: pkv_quantize_nvfp4 is
  * pkv_quantize_rows (quantize_nv_block, phasorkv/kernels/nvfp4.py:43-55); pkv_dequant is pkv_cache_read

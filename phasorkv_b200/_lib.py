@@ -29,7 +29,8 @@ class Layer(ctypes.Structure):
                 ("R", c_int32), ("R_s", c_int32), ("n_slow", c_int32),
                 ("attn_scale", c_float), ("second", c_float),
                 ("Bw_dev", c_void_p), ("A_re_dev", c_void_p), ("A_im_dev", c_void_p), ("A_s_dev", c_void_p),
-                ("freq_dev", c_void_p), ("slow_dev", c_void_p), ("inv_freq_dev", c_void_p), ("Bw_bf16x3_dev", c_void_p)]
+                ("freq_dev", c_void_p), ("slow_dev", c_void_p), ("inv_freq_dev", c_void_p), ("Bw_bf16x3_dev", c_void_p),
+                ("second_blocks_dev", c_void_p)]
 
 
 class Exchange(ctypes.Structure):
@@ -60,6 +61,8 @@ SIGNATURES = {
     "pkv_v_page_bytes": (c_int64, [c_int32, c_int32]),
     "pkv_query_operand_bytes": (c_int64, [c_int32]),
     "pkv_quantize_rows": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_float, c_void_p]),
+    "pkv_quantize_rows_tiered": (c_int32, [POINTER(Cache), c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
+    "pkv_cache_read_tiered": (c_int32, [POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_cache_write": (c_int32, [POINTER(Layer), POINTER(Cache), c_void_p, c_int32, c_void_p, c_void_p, c_void_p,
                                   c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "pkv_write_scratch_floats": (c_int64, [c_int32, c_int32]),

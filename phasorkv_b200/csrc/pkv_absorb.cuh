@@ -48,6 +48,8 @@ struct Args {
     float* qabs_out;                // [batch][n_q][W] or null
     uint8_t* qop_out;               // operand blobs or null
     long qop_bytes;
+    const float* second_blocks;     // tiers: tensor scale of each 16-column block of the cache, or null
+    float inv_second;               // 1 / the layer's tensor scale
     int32_t* qsync;                 // [2 * batch] or null: qsync[b] counts the head groups of sequence b whose operand rows are in place
 };
 
@@ -61,6 +63,8 @@ inline Args make_args(const pkv_layer_t* L, const float* q, const int32_t* posit
     P.attn_scale = L->attn_scale;
     P.qabs_out = qabs_out; P.qop_out = qop_out;
     P.qop_bytes = pkv_page_bytes(2 * L->R + L->R_s) + 512;
+    P.second_blocks = L->second_blocks_dev;
+    P.inv_second = L->second > 0.0f ? 1.0f / L->second : 1.0f;
     P.qsync = nullptr;
     return P;
 }
@@ -86,6 +90,10 @@ __device__ __forceinline__ void body(const Args& P, int b, int hg, float* sm) {
     const int32_t* __restrict__ slow = P.slow;
     const double* __restrict__ inv_freq = P.inv_freq;
     const float attn_scale = P.attn_scale;
+    // tiers: the cache's block j is in units of second_blocks[j] while the decode kernels apply the layer's one scale,
+    // so the query's columns of block j carry the ratio
+    const float* __restrict__ tiers = P.second_blocks;
+    const float inv_second = P.inv_second;
     float* __restrict__ qabs_out = P.qabs_out;
     uint8_t* __restrict__ qop_out = P.qop_out;
     const long qop_bytes = P.qop_bytes;
@@ -154,8 +162,9 @@ __device__ __forceinline__ void body(const Args& P, int b, int hg, float* sm) {
                 const float ar = a_re[h], ai = a_im[h];
                 const float2 z = zq[h * h2 + f];
                 // conj(A) * z = (ar*zr + ai*zi) + i (ar*zi - ai*zr)
-                const float v = c < R ? __fadd_rn(__fmul_rn(ar, z.x), __fmul_rn(ai, z.y))
-                                      : __fsub_rn(__fmul_rn(ar, z.y), __fmul_rn(ai, z.x));
+                float v = c < R ? __fadd_rn(__fmul_rn(ar, z.x), __fmul_rn(ai, z.y))
+                                : __fsub_rn(__fmul_rn(ar, z.y), __fmul_rn(ai, z.x));
+                if (tiers) v *= tiers[c >> 4] * inv_second;
                 row[h * Wp + c] = v;
                 if (qabs_out) qabs_out[((size_t)b * n_q + h0 + h) * W + c] = v;
             }
@@ -168,6 +177,7 @@ __device__ __forceinline__ void body(const Args& P, int b, int hg, float* sm) {
                         int col = s < n_slow ? slow[s] : slow[s - n_slow] + h2;
                         v = fmaf(qb[h * head_dim + col], A_s[((size_t)g * 2 * n_slow + s) * R_s + r], v);
                     }
+                    if (tiers) v *= tiers[c >> 4] * inv_second;
                     if (qabs_out) qabs_out[((size_t)b * n_q + h0 + h) * W + c] = v;
                 }
                 row[h * Wp + c] = v;
@@ -302,6 +312,7 @@ __device__ __forceinline__ void body_tile(const Args& P, int b, uint8_t* blob, f
                     v = fmaf(qh[col], P.A_s[((size_t)g * 2 * n_slow + s) * R_s + r], v);
                 }
             }
+            if (P.second_blocks && c < W) v *= P.second_blocks[c >> 4] * P.inv_second;
             res[blk][i] = v;
             am = fmaxf(am, fabsf(v));
         }

@@ -145,6 +145,14 @@ __device__ __forceinline__ uint32_t pkv_e2m1_code(float x, float scale) {
     return idx | ((idx != 0u && y < 0.0f) ? 8u : 0u);
 }
 
+// The fp32 tensor scale of block j of a latent row: one per layer, or one per 16-column block (tiers)
+struct pkv_second {
+    float s;
+    const float* blocks;
+    __device__ __forceinline__ float of(int j) const { return blocks ? blocks[j] : s; }
+};
+inline pkv_second pkv_second_of(const pkv_layer_t* L) { return pkv_second{L->second, L->second_blocks_dev}; }
+
 // quantise 16 consecutive values; returns the 8 packed code bytes (low nibble = even column)
 __device__ __forceinline__ uint2 pkv_quantize_block16(const float (&v)[16], float second, uint8_t& scale_byte,
                                                       bool round_up = false) {

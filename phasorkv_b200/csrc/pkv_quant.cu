@@ -65,7 +65,7 @@ int pkv_check_cache(const pkv_cache_t* c) {
 // are written as zero codes with a zero scale
 __global__ void pkv_quantize_rows_kernel(uint8_t* __restrict__ latent, const float* __restrict__ rows,
                                          const int32_t* __restrict__ slots, int n_tokens, int W, int n_pages,
-                                         float second, int scale_up) {
+                                         const pkv_second second, int scale_up) {
     const int Wp = pkv_padded_width(W), RB = Wp / 2, nb = Wp / 16;
     const int page_bytes = pkv_page_bytes(W), codes_bytes = pkv_codes_bytes(W);
     long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -85,22 +85,38 @@ __global__ void pkv_quantize_rows_kernel(uint8_t* __restrict__ latent, const flo
             float4 f = src[i];
             v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
         }
-        packed = pkv_quantize_block16(v, second, sb, scale_up != 0);
+        packed = pkv_quantize_block16(v, second.of(j), sb, scale_up != 0);
     }
     *reinterpret_cast<uint2*>(page + pkv_code_offset(row, j * 8, RB)) = packed;
     page[codes_bytes + pkv_scale_offset(row, j)] = sb;
 }
 
+static int quantize_rows_impl(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev, int32_t n_tokens,
+                              float second, const float* second_blocks_dev, void* stream);
+
 extern "C" int pkv_quantize_rows(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev,
                                  int32_t n_tokens, float second, void* stream) {
+    if (!(second > 0.0f)) return PKV_ERR_INVALID;
+    return quantize_rows_impl(cache, rows_dev, slots_dev, n_tokens, second, nullptr, stream);
+}
+
+extern "C" int pkv_quantize_rows_tiered(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev,
+                                        int32_t n_tokens, const float* second_blocks_dev, void* stream) {
+    if (!second_blocks_dev) return PKV_ERR_INVALID;
+    return quantize_rows_impl(cache, rows_dev, slots_dev, n_tokens, 1.0f, second_blocks_dev, stream);
+}
+
+static int quantize_rows_impl(const pkv_cache_t* cache, const float* rows_dev, const int32_t* slots_dev, int32_t n_tokens,
+                              float second, const float* second_blocks_dev, void* stream) {
     int st = pkv_check_cache(cache);
     if (st) return st;
-    if (n_tokens < 0 || !(second > 0.0f)) return PKV_ERR_INVALID;
+    if (n_tokens < 0) return PKV_ERR_INVALID;
     if (n_tokens == 0) return PKV_OK;                      // nothing to do: buffers may be empty (NULL)
     if (!rows_dev || !slots_dev || (((uintptr_t)rows_dev) & 15u)) return PKV_ERR_INVALID;
     long n = (long)n_tokens * (pkv_padded_width(cache->W) / 16);
     pkv_quantize_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        cache->latent_dev, rows_dev, slots_dev, n_tokens, cache->W, cache->n_pages, second, pkv_scale_round_up_mode());
+        cache->latent_dev, rows_dev, slots_dev, n_tokens, cache->W, cache->n_pages, pkv_second{second, second_blocks_dev},
+        pkv_scale_round_up_mode());
     PKV_LAUNCH_CHECK();
     return PKV_OK;
 }
@@ -134,7 +150,7 @@ extern "C" int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const in
 
 // one thread per (token, 16-column block) of the true width W
 __global__ void pkv_cache_read_kernel(const uint8_t* __restrict__ latent, const int32_t* __restrict__ slots,
-                                      int n_tokens, int W, int n_pages, float second, float* __restrict__ rows_out,
+                                      int n_tokens, int W, int n_pages, const pkv_second second, float* __restrict__ rows_out,
                                       uint8_t* __restrict__ codes_out, uint8_t* __restrict__ scales_out) {
     const int RB = pkv_row_bytes(W), nb = W / 16;
     const int page_bytes = pkv_page_bytes(W), codes_bytes = pkv_codes_bytes(W);
@@ -150,7 +166,7 @@ __global__ void pkv_cache_read_kernel(const uint8_t* __restrict__ latent, const 
     if (codes_out) *reinterpret_cast<uint2*>(codes_out + (size_t)tok * (W / 2) + j * 8) = packed;
     if (scales_out) scales_out[(size_t)tok * nb + j] = sb;
     if (rows_out) {
-        float scale = __fmul_rn(pkv_e4m3_to_float(sb), second);
+        float scale = __fmul_rn(pkv_e4m3_to_float(sb), second.of(j));
         float* dst = rows_out + (size_t)tok * W + j * 16;
 #pragma unroll
         for (int i = 0; i < 8; ++i) dst[i] = __fmul_rn(pkv_e2m1_value((packed.x >> (4 * i)) & 15u), scale);
@@ -159,8 +175,24 @@ __global__ void pkv_cache_read_kernel(const uint8_t* __restrict__ latent, const 
     }
 }
 
+static int cache_read_impl(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, pkv_second second,
+                           float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream);
+
 extern "C" int pkv_cache_read(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, float second,
                               float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream) {
+    return cache_read_impl(cache, slots_dev, n_tokens, pkv_second{second, nullptr}, rows_out_dev, codes_out_dev, scales_out_dev, stream);
+}
+
+extern "C" int pkv_cache_read_tiered(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens,
+                                     const float* second_blocks_dev, float* rows_out_dev, uint8_t* codes_out_dev,
+                                     uint8_t* scales_out_dev, void* stream) {
+    if (!second_blocks_dev) return PKV_ERR_INVALID;
+    return cache_read_impl(cache, slots_dev, n_tokens, pkv_second{1.0f, second_blocks_dev}, rows_out_dev, codes_out_dev, scales_out_dev,
+                           stream);
+}
+
+static int cache_read_impl(const pkv_cache_t* cache, const int32_t* slots_dev, int32_t n_tokens, pkv_second second,
+                           float* rows_out_dev, uint8_t* codes_out_dev, uint8_t* scales_out_dev, void* stream) {
     int st = pkv_check_cache(cache);
     if (st) return st;
     if (n_tokens < 0) return PKV_ERR_INVALID;

@@ -44,7 +44,8 @@ struct WriteArgs {
     const int32_t* slots;         // [n_tokens]
     const int32_t* freq;          // [R]
     const double* inv_freq;
-    float attn_scale, second;
+    float attn_scale;
+    pkv_second second;            // tensor scale: per layer, or per 16-column block (tiers)
     int scale_up;                 // block scales rounded up (pkv_set_scale_round_up)
     uint8_t* latent;
     int n_pages;
@@ -259,8 +260,8 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = sums[(tl * 2 + half) * PC + i];
                     uint8_t sb;
-                    const uint2 packed = pkv_quantize_block16(v, A.second, sb, A.scale_up != 0);
                     const int j = (half ? colB : colA) / 16, RB = A.WP / 2;
+                    const uint2 packed = pkv_quantize_block16(v, A.second.of(j), sb, A.scale_up != 0);
                     uint8_t* page = A.latent + (size_t)(slot / PKV_PAGE_TOKENS) * pkv_page_bytes(W);
                     const uint32_t r = slot % PKV_PAGE_TOKENS;
                     *reinterpret_cast<uint2*>(page + pkv_code_offset(r, j * 8, RB)) = packed;
@@ -355,7 +356,7 @@ extern "C" int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cach
     WriteArgs Wa;
     Wa.Bw = layer->Bw_dev; Wa.x = x_dev; Wa.n_tokens = batch; Wa.D = D; Wa.W = W; Wa.WP = WP; Wa.R = layer->R;
     Wa.positions = write_positions_dev; Wa.slots = slots_dev; Wa.freq = layer->freq_dev; Wa.inv_freq = layer->inv_freq_dev;
-    Wa.attn_scale = layer->attn_scale; Wa.second = layer->second; Wa.scale_up = pkv_scale_round_up_mode();
+    Wa.attn_scale = layer->attn_scale; Wa.second = pkv_second_of(layer); Wa.scale_up = pkv_scale_round_up_mode();
     Wa.latent = cache->latent_dev; Wa.n_pages = cache->n_pages; Wa.latent_out = latent_out_dev;
     const bool with_v = cache->v_dev && v_rows_dev;
     Wa.v_rows = with_v ? reinterpret_cast<const uint4*>(v_rows_dev) : nullptr;

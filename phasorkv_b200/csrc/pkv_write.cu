@@ -26,7 +26,7 @@ template <int WP, typename XT>
 __global__ void __launch_bounds__(NT) pkv_cache_write_kernel(
     const float* __restrict__ Bw, const XT* __restrict__ x, const int32_t* __restrict__ positions,
     const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots, int n_tokens, int D, int W, int R, const int32_t* __restrict__ freq,
-    const double* __restrict__ inv_freq, float attn_scale, float second, int scale_up, uint8_t* __restrict__ latent, int n_pages,
+    const double* __restrict__ inv_freq, float attn_scale, const pkv_second second, int scale_up, uint8_t* __restrict__ latent, int n_pages,
     float* __restrict__ latent_out) {
     extern __shared__ __align__(16) float smem[];
     float* Xs = smem;                   // [KC][TM]
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(NT) pkv_cache_write_kernel(
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = Ls[t * LP + j * 16 + i];
         uint8_t sb;
-        uint2 packed = pkv_quantize_block16(v, second, sb, scale_up != 0);
+        uint2 packed = pkv_quantize_block16(v, second.of(j), sb, scale_up != 0);
         uint8_t* page = latent + (size_t)(slot / PKV_PAGE_TOKENS) * page_bytes;
         uint32_t row = slot % PKV_PAGE_TOKENS;
         *reinterpret_cast<uint2*>(page + pkv_code_offset(row, j * 8, RB)) = packed;
@@ -165,7 +165,7 @@ int launch_write(const pkv_layer_t* L, const pkv_cache_t* C, const void* x, cons
     PKV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     kern<<<(n + TM - 1) / TM, NT, smem, st>>>(L->Bw_dev, (const XT*)x, pos, (const float2*)ph, L->head_dim / 2, slots, n,
                                                  L->d_model, 2 * L->R + L->R_s, L->R, L->freq_dev, L->inv_freq_dev,
-                                                 L->attn_scale, L->second, pkv_scale_round_up_mode(), C ? C->latent_dev : nullptr,
+                                                 L->attn_scale, pkv_second_of(L), pkv_scale_round_up_mode(), C ? C->latent_dev : nullptr,
                                                  C ? C->n_pages : 0, latent_out);
     PKV_LAUNCH_CHECK();
     return PKV_OK;
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(256) pkv_project_small_kernel(const float* __r
 __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
     const float* __restrict__ raw, int n_slices, int n_tokens, const int32_t* __restrict__ positions,
     const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots, int W, int WP, int R,
-    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, float second, int scale_up,
+    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, const pkv_second second, int scale_up,
     uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, const uint4* __restrict__ v_rows,
     uint4* __restrict__ v_pool, int v_vecs, int n_kv) {
     __shared__ float row[PKV_MAX_WIDTH];
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(256) pkv_rotate_store_kernel(
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = row[tid * 16 + i];
         uint8_t sb;
-        uint2 packed = pkv_quantize_block16(v, second, sb, scale_up != 0);
+        uint2 packed = pkv_quantize_block16(v, second.of(tid), sb, scale_up != 0);
         uint8_t* page = latent + (size_t)(slot / PKV_PAGE_TOKENS) * pkv_page_bytes(W);
         uint32_t r = slot % PKV_PAGE_TOKENS;
         *reinterpret_cast<uint2*>(page + pkv_code_offset(r, tid * 8, RB)) = packed;
@@ -332,7 +332,7 @@ int launch_write_small(const pkv_layer_t* L, const pkv_cache_t* C, const void* x
     const bool with_v = C && C->v_dev && v_rows;
     PKV_CUDA_TRY(pkv_launch_chained(pkv_rotate_store_kernel, dim3(n), dim3(256), 0, st, scratch, n_slices, n, pos,
                                     (const float2*)ph, L->head_dim / 2, slots, W, WP, L->R, L->freq_dev, L->inv_freq_dev,
-                                    L->attn_scale, L->second, pkv_scale_round_up_mode(), C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out,
+                                    L->attn_scale, pkv_second_of(L), pkv_scale_round_up_mode(), C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out,
                                     with_v ? (const uint4*)v_rows : nullptr, with_v ? (uint4*)C->v_dev : nullptr,
                                     with_v ? C->n_kv * C->head_dim * 2 / 16 : 0, with_v ? C->n_kv : 1));
     return PKV_OK;

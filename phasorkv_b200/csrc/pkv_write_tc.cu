@@ -56,7 +56,7 @@ template <int WP>
 __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
     const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap bmap, int n_tokens, int D, int W, int R,
     const int32_t* __restrict__ positions, const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots,
-    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, float second, int scale_up,
+    const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, const pkv_second second, int scale_up,
     uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, int32_t* __restrict__ status) {
     using C = WCfg<WP>;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = row[j * 16 + i];
                         uint8_t sb;
-                        const uint2 packed = pkv_quantize_block16(v, second, sb, scale_up != 0);
+                        const uint2 packed = pkv_quantize_block16(v, second.of(j), sb, scale_up != 0);
                         *reinterpret_cast<uint2*>(page + pkv_code_offset(pr_row, j * 8, RB)) = packed;
                         page[codes_bytes + pkv_scale_offset(pr_row, j)] = sb;
                     }
@@ -214,7 +214,7 @@ int launch_write_tc(const CUtensorMap& xmap, const CUtensorMap& bmap, const pkv_
     PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
     PKV_CUDA_TRY(pkv_launch_chained(kern, dim3((n + TM_TOK - 1) / TM_TOK), dim3(NTHREADS), smem, st, xmap, bmap, n, L->d_model,
                                     2 * L->R + L->R_s, L->R, pos, (const float2*)ph, L->head_dim / 2, slots, L->freq_dev,
-                                    L->inv_freq_dev, L->attn_scale, L->second, pkv_scale_round_up_mode(),
+                                    L->inv_freq_dev, L->attn_scale, pkv_second_of(L), pkv_scale_round_up_mode(),
                                     C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out, status));
     return PKV_OK;
 }

@@ -110,18 +110,31 @@ class PagedLatentCache:
                                            _lib.ptr(scales), _lib.current_stream()), "pkv_vq_read")
         return rows, codes, scales
 
-    def quantize_rows(self, rows: torch.Tensor, slots: torch.Tensor, second: float) -> None:
-        """Given fp32 latent rows [n, W] -> NVFP4 codes + scales in the pages (bit-exact quantiser)."""
+    def quantize_rows(self, rows: torch.Tensor, slots: torch.Tensor, second) -> None:
+        """Given fp32 latent rows [n, W] -> NVFP4 codes + scales in the pages (bit-exact quantiser). `second`: the
+        fp32 tensor scale, or a float32 tensor [W/16] with one scale per 16-column block (tiers)."""
         rows = rows.to(torch.float32).contiguous()
+        if torch.is_tensor(second):
+            sb = second.to(device=self.device, dtype=torch.float32).contiguous()
+            _lib.check(_lib.load().pkv_quantize_rows_tiered(ctypes.byref(self.c), _lib.ptr(rows), _lib.ptr(slots), rows.shape[0],
+                                                            _lib.ptr(sb), _lib.current_stream()), "pkv_quantize_rows_tiered")
+            return
         _lib.check(_lib.load().pkv_quantize_rows(ctypes.byref(self.c), _lib.ptr(rows), _lib.ptr(slots), rows.shape[0],
                                                  ctypes.c_float(second), _lib.current_stream()), "pkv_quantize_rows")
 
-    def read(self, slots: torch.Tensor, second: float, rows: bool = True, codes: bool = True):
-        """-> (rows fp32 [n, W] | None, packed codes uint8 [n, W/2] | None, scale bytes uint8 [n, W/16] | None)."""
+    def read(self, slots: torch.Tensor, second, rows: bool = True, codes: bool = True):
+        """-> (rows fp32 [n, W] | None, packed codes uint8 [n, W/2] | None, scale bytes uint8 [n, W/16] | None).
+        `second` as for `quantize_rows`."""
         n = slots.numel()
         r = torch.empty((n, self.W), dtype=torch.float32, device=self.device) if rows else None
         c = torch.empty((n, self.W // 2), dtype=torch.uint8, device=self.device) if codes else None
         s = torch.empty((n, self.W // 16), dtype=torch.uint8, device=self.device) if codes else None
+        if torch.is_tensor(second):
+            sb = second.to(device=self.device, dtype=torch.float32).contiguous()
+            _lib.check(_lib.load().pkv_cache_read_tiered(ctypes.byref(self.c), _lib.ptr(slots), n, _lib.ptr(sb),
+                                                         _lib.ptr(r), _lib.ptr(c), _lib.ptr(s), _lib.current_stream()),
+                       "pkv_cache_read_tiered")
+            return r, c, s
         _lib.check(_lib.load().pkv_cache_read(ctypes.byref(self.c), _lib.ptr(slots), n, ctypes.c_float(second),
                                               _lib.ptr(r), _lib.ptr(c), _lib.ptr(s), _lib.current_stream()),
                    "pkv_cache_read")
@@ -237,6 +250,7 @@ class PhasorKey:
         self.inv_freq = None if inv_freq is None else inv_freq.to(torch.float64).cpu()
         self.attn_scale = float(attn_scale)
         self.second = 1.0
+        self.second_blocks = None                          # tiers: one tensor scale per 16-column block (set_second_tiers)
         self.device = torch.device(device)
         self._dev = None
 
@@ -280,7 +294,9 @@ class PhasorKey:
                                                        _lib.ptr(qd), _lib.ptr(phd), qd.shape[0], _lib.ptr(out),
                                                        _lib.current_stream()), "pkv_absorb_rows_f64")
             return out.transpose(0, 1)
-        L = self._layer()
+        self._layer()
+        L = self._dev["layer_plain"]
+        L.second = self.second
         qd = q.to(device=self.device, dtype=torch.float32).transpose(0, 1).contiguous()     # [Tq, H, d]
         phd = self._ph(ph)
         out = torch.empty((qd.shape[0], self.n_q, self.cache_width), dtype=torch.float32, device=self.device)
@@ -346,11 +362,40 @@ class PhasorKey:
         if self._dev is not None:
             self._dev["layer"].second = self.second
 
-    def calibrate_second(self, rows: torch.Tensor) -> float:
-        """Static rule of the reference: 32 sigma of the widest latent channel over 448 * 6."""
+    def calibrate_second(self, rows: torch.Tensor, span: int = 0):
+        """Static rule of the reference: 32 sigma of the widest latent channel over 448 * 6 (phasorkv/quant.py:119-124).
+        `span` (a multiple of 16): one such scale per span of that many columns of the energy-sorted latent -- the
+        reference's tiers (phasorkv/kernels/latent_attn.py:149-152, 255-262) -- instead of one for the whole row."""
         var = rows.float().var(dim=0)
-        self.set_second(float(32.0 * var.max().clamp_min(1e-30).sqrt() / (448.0 * 6.0)))
+        rule = lambda v: 32.0 * v.max().clamp_min(1e-30).sqrt() / (448.0 * 6.0)
+        self.set_second(float(rule(var)))
+        if span:
+            if span % 16:
+                raise ValueError("a tier span is a multiple of 16 columns")
+            W = self.cache_width
+            self.set_second_tiers([(lo, min(lo + span, W), float(rule(var[lo:min(lo + span, W)]))) for lo in range(0, W, span)])
         return self.second
+
+    def set_second_tiers(self, tiers) -> None:
+        """tiers: [(lo, hi, second)] covering the row in 16-aligned spans (None: back to one scale). Quantising
+        calls then use each block's own tensor scale; absorb_step / prologue_step fold `second_tier / second` into the
+        query's columns (their fp32 rows ws.qabs are then in the cache's units), the decode kernels are unchanged."""
+        self.second_blocks = None
+        if tiers is not None:
+            nb = (self.cache_width + 15) // 16
+            sb = torch.full((nb,), self.second, dtype=torch.float32)
+            for lo, hi, sec in tiers:
+                if lo % 16 or (hi % 16 and hi != self.cache_width) or not sec > 0:
+                    raise ValueError("tiers are 16-aligned spans with positive scales")
+                sb[lo // 16:(hi + 15) // 16] = float(sec)
+            self.second_blocks = sb
+        if self._dev is not None:
+            self._dev["second_blocks"] = None if self.second_blocks is None else self.second_blocks.to(self.device)
+            self._dev["layer"].second_blocks_dev = 0 if self.second_blocks is None else self._dev["second_blocks"].data_ptr()
+
+    def second_arg(self):
+        """What `PagedLatentCache.quantize_rows` / `read` take as `second` for this layer: the scalar, or the tiers."""
+        return self.second if getattr(self, "second_blocks", None) is None else self.second_blocks
 
     def new_cache(self, batch: int, max_tokens: int, with_v: bool = True, v_bits: int = 0) -> PagedLatentCache:
         return PagedLatentCache(self.cache_width, self.n_kv, self.head_dim, batch, max_tokens, self.device, with_v,
@@ -554,8 +599,14 @@ class PhasorKey:
                            t["Bw"].data_ptr(), t["A_re"].data_ptr(), t["A_im"].data_ptr(),
                            0 if t["A_s"] is None else t["A_s"].data_ptr(), t["freq"].data_ptr(),
                            0 if t["slow"] is None else t["slow"].data_ptr(), t["inv_freq"].data_ptr(),
-                           t["Bw3"].data_ptr() if Bw.shape[0] <= 256 else 0)
+                           t["Bw3"].data_ptr() if Bw.shape[0] <= 256 else 0, 0)
             t["layer"] = L
+            # the reference's absorb (no tiers folded in) goes through a copy of the struct without them
+            t["layer_plain"] = _lib.Layer.from_buffer_copy(L)
+            sb = getattr(self, "second_blocks", None)
+            if sb is not None:
+                t["second_blocks"] = sb.to(dev)
+                L.second_blocks_dev = t["second_blocks"].data_ptr()
             self._dev = t
         return self._dev["layer"]
 

@@ -308,6 +308,31 @@ def phasorkey_llama_heads():
     print("phasorkey_llama_heads")
 
 
+def nvfp4_tiers():
+    """NVFP4 with one static tensor scale per tier: the reference's cache write quantises every span of the latent
+    row on its own (kernels/latent_attn.write: quantize_nv_block per k_tier with quant.nv_static_second of the span's
+    variances). Spans of a falling spectrum, so that the scales differ by orders of magnitude."""
+    g = torch.Generator().manual_seed(4407)
+    W, n = 256, 96
+    sigma = torch.exp(-torch.arange(W) / 40.0)
+    x = torch.randn(n, W, generator=g) * sigma[None, :]
+    spans = [(0, 32), (32, 96), (96, 240), (240, 256)]
+    var = x.var(0)
+    codes = torch.zeros(n, W, dtype=torch.uint8)
+    scales = torch.zeros(n, W // 16, dtype=torch.float8_e4m3fn)
+    xhat = torch.zeros(n, W)
+    seconds = []
+    for lo, hi in spans:
+        sec = quant.nv_static_second(var[lo:hi], "nvfp4")
+        c, s, h = nvfp4.quantize_nv_block(x[:, lo:hi], "nvfp4", sec)
+        codes[:, lo:hi], scales[:, lo // 16:hi // 16], xhat[:, lo:hi] = c, s, h
+        seconds.append(float(sec))
+    np.savez_compressed(os.path.join(HERE, "nvfp4_tiers.npz"), x=x.numpy(), spans=np.array(spans), seconds=np.array(seconds, dtype=np.float32),
+                        codes=codes.numpy(), scales=scales.view(torch.uint8).numpy(), xhat=xhat.numpy(),
+                        packed=nvfp4.pack_nibbles(codes).numpy())
+    print("nvfp4_tiers", seconds)
+
+
 def v_tiers():
     """Per-token low-bit tiers of the reference (kernels/nvfp4.quantize_per_token) on rows of 128 values, the
     shape of one (token, kv head) value row: 3-bit and 2-bit, with ties, an all-zero row, a row below the
@@ -350,5 +375,7 @@ if __name__ == "__main__":
             attend_merge()
         if want("v_tiers"):
             v_tiers()
+        if want("nvfp4_tiers"):
+            nvfp4_tiers()
         if want("phasorkey_llama_heads"):
             phasorkey_llama_heads()

@@ -131,6 +131,79 @@ def test_quantiser_bit_exact_over_wide_magnitudes(second):
     assert np.array_equal(c_codes, ref_codes.numpy()) and np.array_equal(c_scales, ref_scales.numpy())
 
 
+def test_quantiser_with_one_scale_per_tier_matches_reference():
+    """Tiers: every 16-aligned span of the row has its own static tensor scale (phasorkv/quant.py:119-124 applied per
+    span, as phasorkv/kernels/latent_attn.py:255-262 writes its cache). Bit-exact against the reference's
+    span-by-span quantisation, and the tiered read-back returns its x_hat."""
+    g = _golden("nvfp4_tiers.npz")
+    x = torch.from_numpy(g["x"])
+    n, W = x.shape
+    sb = torch.zeros(W // 16)
+    for (lo, hi), sec in zip(g["spans"].tolist(), g["seconds"].tolist()):
+        sb[lo // 16:hi // 16] = sec
+    cache = PagedLatentCache(W, 8, 128, 1, n, "cuda", with_v=False)
+    lp = torch.arange(n, dtype=torch.int32, device="cuda")
+    slots = cache.slots(torch.zeros_like(lp), lp)
+    cache.quantize_rows(x.cuda(), slots, sb)
+    xhat, codes, scales = cache.read(slots, sb)
+    assert np.array_equal(codes.cpu().numpy(), g["packed"]) and np.array_equal(scales.cpu().numpy(), g["scales"])
+    assert np.array_equal(xhat.cpu().numpy(), g["xhat"])
+
+
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+def test_tiered_tensor_scales_through_write_and_decode(x_dtype):
+    """A layer whose energy-sorted latent falls by orders of magnitude along the row, with one static scale per
+    64-column span: every write kernel stores the reference quantiser's bits of its own rows under the span's
+    scale, and the decode (the query carries second_tier / second per block) meets fp32 scoring on the
+    dequantised cache. With the single scale of the widest channel the last span's blocks underflow to zero."""
+    spec = synth.make_layer("cfg2", 2)
+    decay = torch.exp(-torch.arange(spec.R, dtype=torch.float32) / 10.0)           # complex dim k shrinks like e^{-k/10}
+    pk = PhasorKey.from_factors(spec.A, spec.B * decay[:, None], spec.freq, spec.n_q, spec.n_kv, spec.head_dim, spec.inv_freq)
+    opk = po.PhasorKeyOracle(spec.A, spec.B * decay[:, None], spec.freq, spec.n_q, spec.n_kv, spec.head_dim)
+    g = torch.Generator().manual_seed(12)
+    T, pos0 = 333, 2000
+    x = synth.make_hidden(g, T, 4096).to(x_dtype)
+    v = synth.make_values(g, T, spec.n_kv, spec.head_dim)
+    q = synth.make_query(g, 1, spec.n_q, spec.head_dim)
+    pos = torch.arange(T) + pos0
+    rows_ref = opk.write(x.float(), po.rope_phasors(spec.inv_freq, pos))
+    pk.calibrate_second(rows_ref, span=64)
+    sb = pk.second_arg()
+    assert torch.is_tensor(sb) and float(sb.max() / sb.min()) > 100.0
+    cache = pk.new_cache(1, T)
+    lp = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = cache.slots(torch.zeros_like(lp), lp)
+    out = torch.empty((T, 256), device="cuda")
+    pk.write_paged(cache, x.cuda(), pos.to(torch.int32).cuda(), slots, v=v.cuda(), latent_out=out)       # chunk write kernels
+    assert rel(out.cpu(), rows_ref) < (5e-6 if x_dtype == torch.float32 else 3e-5)
+    hat, codes, scales = cache.read(slots, sb)
+    o_codes, o_scales, o_hat = po.nvfp4_quantize(out.cpu(), sb)
+    assert torch.equal(codes.cpu(), po.pack_nibbles(o_codes)) and torch.equal(scales.cpu(), o_scales) and torch.equal(hat.cpu(), o_hat)
+    assert float(hat[:, 112:128].abs().max()) > 0                                   # the weakest span survives with its own scale
+    _, _, flat = po.nvfp4_quantize(out.cpu(), torch.tensor([pk.second]))
+    assert float(flat[:, 112:128].abs().max()) == 0.0                               # ... and would not with the row's one scale
+    # newest token through the prologue (small-batch and general path use the same per-block scales)
+    cache.seqlens.fill_(T)
+    ws = pk.workspace(1, 2)
+    qpos = torch.tensor([T + pos0], dtype=torch.int32, device="cuda")
+    x_new = synth.make_hidden(g, 1, 4096).to(x_dtype).cuda()
+    row_new = torch.empty((1, 256), device="cuda")
+    pk.prologue_step(cache, x_new, qpos - 1, slots[-1:], q.cuda(), qpos, ws, v=v[-1:].cuda(), latent_out=row_new)
+    hat1, c1, s1 = cache.read(slots[-1:], sb)
+    n_codes, n_scales, _ = po.nvfp4_quantize(row_new.cpu(), sb)
+    assert torch.equal(c1.cpu(), po.pack_nibbles(n_codes)) and torch.equal(s1.cpu(), n_scales)
+    Sd = torch.zeros((1, spec.n_q, T), device="cuda")
+    pk.attend_step(cache, ws, scores_out=Sd, out=ws.out, after_prologue=True)
+    torch.cuda.synchronize()
+    hat, _, _ = cache.read(slots, sb)
+    qa = opk.absorb(q[0][:, None, :], po.rope_phasors(spec.inv_freq, torch.tensor([T + pos0])))[:, 0]
+    S_ref = opk.scores(qa, hat.cpu())
+    assert rel(Sd[0].cpu(), S_ref) < LOGIT_TOL
+    assert rel(ws.out[0].cpu(), po.attend(S_ref, v, spec.n_kv, spec.head_dim)) < OUT_TOL
+    # the reference-surface absorb stays the reference's (no tier ratio inside)
+    assert rel(pk.absorb(q[0][:, None, :], po.rope_phasors(spec.inv_freq, torch.tensor([T + pos0])))[:, 0].cpu(), qa) < 2e-6
+
+
 def test_quantiser_empty_and_bad_slots():
     cache = PagedLatentCache(256, 8, 128, 1, 128, "cuda", with_v=False)
     cache.quantize_rows(torch.zeros(0, 256), torch.zeros(0, dtype=torch.int32, device="cuda"), 1.0)

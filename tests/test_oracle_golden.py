@@ -169,3 +169,17 @@ def test_per_token_v_tiers_bit_exact():
         assert np.array_equal(scale.view(torch.int16).numpy(), g[f"scale{nbits}"])
         assert np.array_equal(xhat.numpy(), g[f"xhat{nbits}"])
         assert torch.equal(po.e2m1_decode(codes) * scale.float()[:, None], xhat)
+
+
+def test_nvfp4_with_one_scale_per_tier_bit_exact():
+    """One static tensor scale per span of the row (the reference's tiers): the oracle with a per-block scale vector
+    against the reference's span-by-span quantisation."""
+    g = _load("nvfp4_tiers.npz")
+    x = torch.from_numpy(g["x"])
+    sb = torch.zeros(x.shape[1] // 16)
+    for (lo, hi), sec in zip(g["spans"].tolist(), g["seconds"].tolist()):
+        sb[lo // 16:hi // 16] = sec
+    codes, scales, xhat = po.nvfp4_quantize(x, sb)
+    assert np.array_equal(codes.numpy(), g["codes"]) and np.array_equal(scales.numpy(), g["scales"])
+    assert np.array_equal(xhat.numpy(), g["xhat"])
+    assert np.array_equal(po.nvfp4_dequantize(codes, scales, sb).numpy(), g["xhat"])
