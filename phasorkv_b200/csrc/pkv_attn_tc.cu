@@ -45,7 +45,7 @@ constexpr int NTHREADS_SCORES = 11 * 32;      // scores only: two softmax groups
 constexpr int NTHREADS_VQ = 12 * 32;          // quantised V: warps 0-2 as always (3 idle), 4-7 softmax, 8-11 converters
 template <bool WV, bool VQ> constexpr int n_threads() { return VQ ? NTHREADS_VQ : (WV ? NTHREADS : NTHREADS_SCORES); }
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 19;     // probes of a bounded wait (a probe may itself block for microseconds): a second or two, then give up
 
 // tensor memory columns
 // Score buffers (pages in flight between MMA and softmax): two. In scores-only mode buffer = page parity, so
@@ -81,6 +81,11 @@ struct Extra {                       // lives at X_OFF
     uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_STAGES], v_empty[NV_STAGES];
     uint64_t s_full[NSB_S], s_empty[NSB_S], p_full[2], pv_done[2];
     uint64_t vr_full[NVR], vr_empty[NVR];                        // raw tiles of quantised V pages
+    // Quantised V: the bf16 stages are filled by four converter warps and drained by two MMA issuers (tiles of even /
+    // odd kv heads). A parity wait only tells neighbouring phases apart, so a barrier must be waited for by ONE
+    // thread, phase after phase: each stage therefore has a barrier pair per issuer (tile j: stage j % 3, issuer
+    // j & 1, phase j / 6), and each raw stage belongs to one converter warp (j % 4).
+    uint64_t vq_full[NVB_Q][2], vq_empty[NVB_Q][2];
     uint64_t sm_bar;                 // rendezvous of the 128 softmax threads (bounded, unlike bar.sync)
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -158,6 +163,8 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
         for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
         for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 1); }
+        for (int s = 0; s < NVB_Q; ++s)
+            for (int u = 0; u < 2; ++u) { mbar_init(&X->vq_full[s][u], 1); mbar_init(&X->vq_empty[s][u], 1); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }   // quantised V: two P.V issuers
         mbar_init(&X->sm_bar, WV ? 128 : 256);
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                             // the counter instead of waiting for that whole grid
                             const int need = (NQ + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
                             bool there = false;
-                            for (uint32_t it = 0; it < (WAIT_LIMIT >> 4) && !there; ++it) {    // a fraction of a second, then give up
+                            for (uint32_t it = 0; it < WAIT_LIMIT && !there; ++it) {    // about half a second, then give up
                                 int v;
                                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(qa.qsync + b) : "memory");
                                 there = v >= need;
@@ -371,7 +378,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_fence_after_sync();
                 for (int g = pv_only ? 1 : 0; g < NKV; g += PV_STEP) {
                     const int j = i * NKV + g, s = j % C::NVS;
-                    if (!wait_or_abort(&X->v_full[s], (j / C::NVS) & 1, X, status, 32)) return false;
+                    uint64_t* const full_bar = VQ ? &X->vq_full[VQ ? s : 0][j & 1] : &X->v_full[s];
+                    uint64_t* const empty_bar = VQ ? &X->vq_empty[VQ ? s : 0][j & 1] : &X->v_empty[s];
+                    if (!wait_or_abort(full_bar, (VQ ? j / (2 * NVB_Q) : j / C::NVS) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
                     const uint32_t va = sbase + C::V_OFF + s * V_STAGE_BYTES;
                     // B operand: 16 rows = the hi weights of the 8-head group holding this kv head's heads, then their lo parts
@@ -386,7 +395,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #else
                     (void)v_desc; (void)p_desc;
 #endif
-                    tc_commit(&X->v_empty[s]);
+                    tc_commit(empty_bar);
                 }
                 tc_commit(&X->pv_done[pb]);
                 return true;
@@ -450,7 +459,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int j = cw; j < n_tiles && ok; j += 4) {
             const int rs = j % NVR, bs = j % C::NVS;
             ok = __all_sync(0xffffffffu, wait_or_abort(&X->vr_full[rs], (j / NVR) & 1, X, status, 50));
-            if (ok && j >= C::NVS) ok = __all_sync(0xffffffffu, wait_or_abort(&X->v_empty[bs], ((j / C::NVS) - 1) & 1, X, status, 51));
+            // the stage was last used by tile j - 3 (the other issuer's): wait for that issuer's commit on its barrier
+            if (ok && j >= NVB_Q)
+                ok = __all_sync(0xffffffffu, wait_or_abort(&X->vq_empty[bs][(j - NVB_Q) & 1], ((j - NVB_Q) / (2 * NVB_Q)) & 1, X, status, 51));
             if (!ok) break;
             const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
             uint8_t* stage = smem + C::V_OFF + bs * V_STAGE_BYTES;
@@ -500,7 +511,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             fence_proxy_async_smem();                                // generic-proxy writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&X->v_full[bs]);
+                mbar_arrive(&X->vq_full[bs][j & 1]);
                 mbar_arrive(&X->vr_empty[rs]);
             }
         }
