@@ -35,7 +35,7 @@ extern "C" {
 #endif
 #define PKV_NOALLOC_MAX_PARTS 320     /* pkv_decode_attn_noalloc: upper bound on batch * n_split */
 #define PKV_SMALL_WRITE_TOKENS 64    /* pkv_cache_write spreads the projection over the GPU up to this n */
-#define PKV_VQ_TILE_BYTES 8448       /* quantised V: codes (128 tokens x 64 bytes) + 128 bf16 scales of one (page, kv head) */
+#define PKV_VQ_TILE_BYTES 8448       /* quantised V: bytes per (page, kv head): 128 tokens x 64 bytes of codes + 128 bf16 scales */
 
 enum pkv_status {
     PKV_OK = 0,
@@ -101,11 +101,11 @@ typedef struct pkv_layer {
  *   V page: [n_kv][128][head_dim] bf16 (head-major: the 128 x head_dim tile of one kv head is one
  *           contiguous block); the value of (slot, kv head g, dim) sits at element
  *           ((page * n_kv + g) * 128 + row) * head_dim + dim.  pkv_v_write / pkv_cache_write place rows there.
- *   Quantised V page (v_bits = 3 or 2; head_dim 128): per kv head one tile of PKV_VQ_TILE_BYTES bytes -- the
- *           per-token low-bit tier of the reference (phasorkv/kernels/nvfp4.py:58-67) applied to each
- *           (token, kv head) value row: 128 E2M1 codes, two per byte with the even dim in the low nibble, 64
- *           bytes per token whose 16-byte chunk c is stored at chunk position c ^ ((row >> 1) & 3), followed
- *           by the tile's 128 bf16 scales; tile index = page * n_kv + head.  pkv_vq_write fills it.
+ *   Quantised V page (v_bits = 3 or 2; head_dim 128): n_kv * 66 rows of 128 bytes -- the per-token low-bit tier of
+ *           the reference (phasorkv/kernels/nvfp4.py:58-67) applied to each (token, kv head) value row.  Rows
+ *           g*64 .. g*64+63 hold the codes of kv head g: 128 E2M1 codes per token, two per byte with the even dim in
+ *           the low nibble, 64 bytes per token whose 16-byte chunk c is stored at chunk position c ^ ((row >> 1) & 3);
+ *           the rows from n_kv*64 on hold the bf16 scales, 128 per kv head.  pkv_vq_write fills it.
  * A token's place is its *slot*: page_index * 128 + row. */
 typedef struct pkv_cache {
     uint8_t* latent_dev;
@@ -197,8 +197,9 @@ int pkv_v_write(const pkv_cache_t* cache, const void* v_dev, const int32_t* slot
  * quantised per (token, kv head) exactly as quantize_per_token does (phasorkv/kernels/nvfp4.py:58-67: one bf16
  * scale = bf16(max(amax, 1e-5) / 3) and integers -4 .. 3 rounded half to even for 3 bits; bf16(max(amax, 1e-5)
  * / 1.5) and levels +-0.5, +-1.5 for 2 bits; E2M1 codes, four bits of storage each) and stored at slots_dev [n].
- * pkv_decode_attn reads such pages when cache->v_bits != 0 (tensor-core kernel only; the codes are expanded to
- * bf16 times scale inside the kernel, so V costs 528 instead of 2048 bytes per token at 8 kv heads).
+ * pkv_decode_attn reads such pages when cache->v_bits != 0 (tensor-core kernel only): the codes become E4M3
+ * operands (the same numbers), the scales go into the softmax weights, P.V runs on the 8-bit tensor-core path; V
+ * costs 528 instead of 2048 bytes per token at 8 kv heads.
  * pkv_vq_read returns, per (token, kv head): rows_out [n, n_kv, 128] fp32 = value(code) * scale,
  * codes_out [n, n_kv, 128] one code per byte, scales_out [n, n_kv] bf16 bit patterns; any may be NULL. */
 int64_t pkv_vq_page_bytes(int32_t n_kv, int32_t head_dim);

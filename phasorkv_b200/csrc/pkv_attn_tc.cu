@@ -33,10 +33,17 @@ using namespace pkv;
 
 constexpr int NQ = 32, DH = 128;
 constexpr int NK_STAGES = 2, NV_STAGES = 4;
-// quantised V pages: raw tiles (codes + scales of one page and kv head) land in a ring of NVR stages; four
-// converter warps turn each into the bf16 operand tile, of which NVB_Q stages are kept
-constexpr int NVR = 4, NVB_Q = 3;
-constexpr int RAW_BYTES = PKV_VQ_TILE_BYTES;
+// Quantised V pages: the codes of a (page, kv head) tile land in a ring of NVR raw stages; four converter warps turn
+// each into an E4M3 operand tile (every E2M1 level is an exact E4M3 number), of which NVS_Q stages are kept. The
+// per-token scales of a page (one 2 KB block for the CTA's 8 kv heads) have a ring of their own: the softmax folds
+// them into the weights (E5M2, whose exponent range takes any scale), so that P.V runs as kind::f8f6f4 MMAs
+// (K = 32) on exact V operands.
+constexpr int NVR = 4, NVS_Q = 6;
+constexpr int RAW_BYTES = PKV_PAGE_TOKENS * 64;                // codes of one tile
+constexpr int VQ_STAGE_BYTES = PKV_PAGE_TOKENS * DH;           // the tile as E4M3: one 128-byte row per token
+constexpr int VQ_SCALE_BYTES = 8 * PKV_PAGE_TOKENS * 2;        // bf16 scales of 8 kv heads x 128 tokens
+constexpr int VQ_TERMS = 4;                                    // weights: p * scale as E5M2 residual terms (2^-12 of the value,
+                                                               // any magnitude of scale from 2^-14 to 5e4)
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
@@ -60,7 +67,8 @@ constexpr uint32_t TM_COLS = 512;
 
 template <int WP, bool VQ = false>
 struct Cfg {
-    static constexpr int NVS = VQ ? NVB_Q : NV_STAGES;           // bf16 V stages
+    static constexpr int NVS = VQ ? NVS_Q : NV_STAGES;           // V operand stages
+    static constexpr int VSB = VQ ? VQ_STAGE_BYTES : V_STAGE_BYTES;
     static constexpr int RB = WP / 2;                          // code bytes per row
     static constexpr int KB = WP / 64;                         // K = 64 MMA steps
     static constexpr int CODES = PKV_PAGE_TOKENS * RB;
@@ -69,8 +77,9 @@ struct Cfg {
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = ((QBLOB + 1023) / 1024) * 1024;
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
-    static constexpr int R_OFF = V_OFF + NVS * V_STAGE_BYTES;    // raw tiles of quantised V pages
-    static constexpr int P_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);
+    static constexpr int R_OFF = V_OFF + NVS * VSB;              // raw tiles of quantised V pages
+    static constexpr int SC_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);      // their scale blocks, two pages
+    static constexpr int P_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
     static constexpr int SMEM = X_OFF + 4096;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
@@ -78,14 +87,17 @@ struct Cfg {
 };
 
 struct Extra {                       // lives at X_OFF
-    uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_STAGES], v_empty[NV_STAGES];
+    uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NVS_Q], v_empty[NVS_Q];
     uint64_t s_full[NSB_S], s_empty[NSB_S], p_full[2], pv_done[2];
     uint64_t vr_full[NVR], vr_empty[NVR];                        // raw tiles of quantised V pages
-    // Quantised V: the bf16 stages are filled by four converter warps and drained by two MMA issuers (tiles of even /
-    // odd kv heads). A parity wait only tells neighbouring phases apart, so a barrier must be waited for by ONE
-    // thread, phase after phase: each stage therefore has a barrier pair per issuer (tile j: stage j % 3, issuer
-    // j & 1, phase j / 6), and each raw stage belongs to one converter warp (j % 4).
-    uint64_t vq_full[NVB_Q][2], vq_empty[NVB_Q][2];
+    // Quantised V: the operand stages are filled by four converter warps and drained by two MMA issuers (tiles of
+    // even / odd kv heads). A parity wait only tells neighbouring phases apart, so a barrier must be waited for by
+    // one thread, phase after phase: tile j uses stage j % 6 (an even number of stages: a stage always serves the
+    // same issuer) and raw stage j % 4 (always the same converter warp).
+    uint64_t sc_full[2], sc_empty[2];                            // scale blocks of quantised V pages
+#ifdef PKV_WAITPROF
+    unsigned long long waited[64];
+#endif
     uint64_t sm_bar;                 // rendezvous of the 128 softmax threads (bounded, unlike bar.sync)
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -96,13 +108,25 @@ struct Extra {                       // lives at X_OFF
 };
 
 static_assert(sizeof(Extra) <= 4096, "barriers and exchange arrays must fit behind the stages");
+static_assert(Cfg<256, true>::SMEM <= 232448 && Cfg<256, false>::SMEM <= 232448, "shared memory of one CTA");
+static_assert(Cfg<256, true>::V_OFF % 1024 == 0 && VQ_STAGE_BYTES % 1024 == 0, "swizzled operand stages start on 1024 bytes");
 
 // order-preserving map float -> uint so that an integer warp reduction gives the float maximum
 __device__ __forceinline__ uint32_t f2ord(float f) { uint32_t b = __float_as_uint(f); return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u); }
 __device__ __forceinline__ float ord2f(uint32_t u) { return __uint_as_float(u ^ ((u >> 31) ? 0x80000000u : 0xFFFFFFFFu)); }
 
 // bounded wait that also gives up when another role has already given up
+// Build with -DPKV_WAITPROF to turn `scores_out` into a table of 64 counters per CTA: the cycles lane 0 of each
+// warp spent in the wait with code `where` (entry 0: the CTA's cycles from entry to exit). The role that waits
+// least is the one that bounds the kernel. A development aid; the library is never shipped with it.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Extra* X, int32_t* status, int where) {
+#ifdef PKV_WAITPROF
+    const long long t0 = clock64();
+    struct Tally {
+        Extra* X; int where; long long t0;
+        __device__ ~Tally() { if ((threadIdx.x & 31) == 0) atomicAdd(&X->waited[where & 63], (unsigned long long)(clock64() - t0)); }
+    } tally{X, where, t0};
+#endif
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && X->abort_flag) return false;
@@ -128,7 +152,8 @@ __device__ __forceinline__ long long pkv_globaltimer() { long long t; asm volati
 template <int WP, int REP, bool WV, bool INLQ, bool VQ>
 __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap kmap,
-    const __grid_constant__ CUtensorMap qmap, const int32_t* __restrict__ page_table, int max_pages,
+    const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap smap,
+    const int32_t* __restrict__ page_table, int max_pages,
     const int32_t* __restrict__ seqlens, int n_split, int n_pages_pool, float col_scale, float inv_logit_scale,
     uint32_t flags, float* __restrict__ partials, float* __restrict__ scores_out, long scores_stride,
     int32_t* __restrict__ status, const pkv_absorb_impl::Args qa) {
@@ -144,6 +169,12 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     constexpr int NKV = NQ / REP > 8 ? 8 : NQ / REP;      // kv heads per CTA
     constexpr int HPC = NKV * REP;                         // query heads per CTA
     constexpr int PGS = (HPC / 8) * 256;                   // bytes of P per 8-token group: per 8 heads [hi 128 | lo 128]
+    // quantised V: the weights of kv head g are NPV operand rows (row = term * REP + head of the group; VQ_TERMS E5M2
+    // residual terms of p * scale, further rows zero), K-major in 16-token core matrices
+    constexpr int NPV = REP == 8 ? 32 : 16;
+    static_assert(!VQ || VQ_TERMS * REP <= NPV, "weight rows of a kv head");
+    constexpr int PG8 = (PKV_PAGE_TOKENS / 16) * NPV * 16; // bytes of one kv head's weights of a page
+    constexpr int VQ_TILE_ROWS = RAW_BYTES / 128, VQ_PAGE_ROWS = (NQ / REP) * (PKV_VQ_TILE_BYTES / 128);
     const int h_base = (WV ? (int)blockIdx.z : 0) * HPC, g_base = (WV ? (int)blockIdx.z : 0) * NKV;
     static_assert(WV || HPC == NQ, "scores-only launches use a grouped-query instantiation");
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -155,16 +186,23 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     scores_out = nullptr;
     if (tid == 0) { PKV_TL(0); tl_buf[1] = pkv_globaltimer(); uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); tl_buf[15] = sm; }
 #endif
+#ifdef PKV_WAITPROF
+    unsigned long long* wp_buf = reinterpret_cast<unsigned long long*>(scores_out) + ((size_t)(blockIdx.z * gridDim.y + b) * gridDim.x + split) * 64;
+    scores_out = nullptr;
+    const long long wp_t0 = clock64();
+#endif
     pkv_grid_launch_dependents();
 
     // ---- prologue that touches no global memory: barriers, tensor memory
     if (tid == 0) {
+#ifdef PKV_WAITPROF
+        for (int k = 0; k < 64; ++k) X->waited[k] = 0;
+#endif
         mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
-        for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
+        for (int s = 0; s < NVS_Q; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
         for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 1); }
-        for (int s = 0; s < NVB_Q; ++s)
-            for (int u = 0; u < 2; ++u) { mbar_init(&X->vq_full[s][u], 1); mbar_init(&X->vq_empty[s][u], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 128); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }   // quantised V: two P.V issuers
         mbar_init(&X->sm_bar, WV ? 128 : 256);
@@ -302,8 +340,8 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     } else if (warp == 1 && WV) {
         // ================================================================== V producer
         {
-            if (lane == 0) tma_prefetch_desc(&vmap);
-            int issued = 0;
+            if (lane == 0) { tma_prefetch_desc(&vmap); if (VQ) tma_prefetch_desc(&smap); }
+            int issued = 0, sc_issued = 0;
             bool stop = false, waited = !(early && tail_written);
             for (int base = 0; base < P && !stop; base += 32) {
                 const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
@@ -316,11 +354,19 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         } else {
                             if (!waited && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                             for (int g = 0; g < NKV; ++g) {
-                                if constexpr (VQ) {                  // the tile as stored: codes and scales of (page, kv head)
-                                    const int j = i * NKV + g, s = j % NVR;
+                                if constexpr (VQ) {
+                                    if (g == 0) {                    // the page's scale block first: 8 kv heads x 128 bf16
+                                        const int ss = i & 1;
+                                        if (i >= 2 && !wait_or_abort(&X->sc_empty[ss], ((i >> 1) - 1) & 1, X, status, 22)) { stop = true; break; }
+                                        mbar_arrive_expect_tx(&X->sc_full[ss], VQ_SCALE_BYTES);
+                                        tma_load_2d(smem + C::SC_OFF + ss * VQ_SCALE_BYTES, &smap, 0,
+                                                    pidx * VQ_PAGE_ROWS + (NQ / REP) * VQ_TILE_ROWS + g_base * 2, &X->sc_full[ss]);
+                                        sc_issued = i + 1;
+                                    }
+                                    const int j = i * NKV + g, s = j % NVR;        // the codes of (page, kv head) as stored
                                     if (j >= NVR && !wait_or_abort(&X->vr_empty[s], ((j / NVR) - 1) & 1, X, status, 21)) { stop = true; break; }
                                     mbar_arrive_expect_tx(&X->vr_full[s], RAW_BYTES);
-                                    tma_load_2d(smem + C::R_OFF + s * RAW_BYTES, &vmap, 0, (pidx * (NQ / REP) + g_base + g) * (RAW_BYTES / 128),
+                                    tma_load_2d(smem + C::R_OFF + s * RAW_BYTES, &vmap, 0, pidx * VQ_PAGE_ROWS + (g_base + g) * VQ_TILE_ROWS,
                                                 &X->vr_full[s]);
                                     issued = j + 1;
                                     continue;
@@ -341,6 +387,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             if (lane == 0 && X->abort_flag) {
                 if constexpr (VQ) {
                     for (int j = max(0, issued - NVR); j < issued; ++j) mbar_wait(&X->vr_full[j % NVR], (j / NVR) & 1, 1u << 16);
+                    for (int j = max(0, sc_issued - 2); j < sc_issued; ++j) mbar_wait(&X->sc_full[j & 1], (j >> 1) & 1, 1u << 16);
                 } else {
                     for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
                         mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
@@ -362,7 +409,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             constexpr int STEP = WV ? 1 : 2;
             const uint32_t sfb_tm = tb + TM_SFB + (first ? 16u : 0u);
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
-            constexpr uint32_t idesc_o = idesc_bf16(128, 16, true, false);
+            constexpr uint32_t idesc_o = VQ ? idesc_f8(128, NPV, true, false, 0u, 1u) : idesc_bf16(128, 16, true, false);   // V: E4M3, weights: E5M2
             const bool pv_only = VQ && warp == 3;
             bool ok = pv_only || wait_or_abort(&X->q_full, 0, X, status, 30);
             if (warp == 2) PKV_TL(7);
@@ -378,11 +425,24 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_fence_after_sync();
                 for (int g = pv_only ? 1 : 0; g < NKV; g += PV_STEP) {
                     const int j = i * NKV + g, s = j % C::NVS;
-                    uint64_t* const full_bar = VQ ? &X->vq_full[VQ ? s : 0][j & 1] : &X->v_full[s];
-                    uint64_t* const empty_bar = VQ ? &X->vq_empty[VQ ? s : 0][j & 1] : &X->v_empty[s];
-                    if (!wait_or_abort(full_bar, (VQ ? j / (2 * NVB_Q) : j / C::NVS) & 1, X, status, 32)) return false;
+                    uint64_t* const empty_bar = &X->v_empty[s];
+                    if (!wait_or_abort(&X->v_full[s], (j / C::NVS) & 1, X, status, 32)) return false;
                     tc_fence_after_sync();
-                    const uint32_t va = sbase + C::V_OFF + s * V_STAGE_BYTES;
+                    const uint32_t va = sbase + C::V_OFF + s * C::VSB;
+                    if constexpr (VQ) {
+                        // A: the tile as E4M3, 128 tokens x 128 bytes (dims contiguous: MN-major, one 128-byte swizzle atom
+                        // wide); B: this kv head's weight rows; K = 32 tokens per instruction
+                        const uint64_t v8_desc = smem_desc(va, 0, 1024, SWZ_128B);
+                        const uint64_t p8_desc = smem_desc(sbase + C::P_OFF + pb * P_BYTES + g * PG8, NPV * 16, 128, SWZ_NONE);
+#ifndef PKV_VQ_SKIP_PV
+#pragma unroll
+                        for (int k = 0; k < PKV_PAGE_TOKENS / 32; ++k)
+                            mma_f8(tb + TM_O + NPV * g, v8_desc + (uint64_t)(k * 32 * 128 / 16), p8_desc + (uint64_t)(k * 2 * NPV * 16 / 16), idesc_o,
+                                   !(i == 0 && k == 0));
+#endif
+                        tc_commit(empty_bar);
+                        continue;
+                    }
                     // B operand: 16 rows = the hi weights of the 8-head group holding this kv head's heads, then their lo parts
                     const uint32_t pa = sbase + C::P_OFF + pb * P_BYTES + ((g * REP) >> 3) * 256;
                     const uint64_t v_desc = smem_desc(va, V_STAGE_BYTES / 2, 1024, SWZ_128B);
@@ -440,15 +500,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         }
     } else if (VQ && warp >= 8) {
         // ================================================================== V converter (quantised V pages)
-        // Thread = token row of the tile. A row is 64 bytes of E2M1 codes and one bf16 scale; it becomes 128
-        // bf16 values (code value times scale, rounded to bf16: exact unless the code is +-1.5, +-3 or +-6,
-        // then one rounding of at most 2^-9) in the 128-byte-swizzled layout a tensor tile load of a bf16
-        // V page would have produced, which is what the P.V descriptors expect.
+        // A token's 64 bytes of E2M1 codes become 128 E4M3 bytes (exactly the same numbers) in the 128-byte-swizzled
+        // MN-major layout the P.V descriptors expect; the token's scale is not applied here but folded into the weights.
         // Each converter warp owns every fourth tile (a lane takes four token rows of it), so that four tiles are in
         // work at once and the waits of one hide behind the arithmetic of the others.
         const int cw = warp - 8;
-        // bf16 bit patterns of the eight E2M1 magnitudes (0 .5 1 1.5 2 3 4 6) as byte tables for prmt
-        constexpr uint32_t LO_A = 0xC0800000u, LO_B = 0xC0804000u, HI_A = 0x3F3F3F00u, HI_B = 0x40404040u;
+        // E4M3 bytes of the eight E2M1 magnitudes 0 .5 1 1.5 2 3 4 6 (00 30 38 3C 40 44 48 4C) as byte tables for prmt
+        constexpr uint32_t LUT_A = 0x3C383000u, LUT_B = 0x4C484440u;
         auto prmt = [](uint32_t a, uint32_t b, uint32_t c) -> uint32_t {
             uint32_t d;
             asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -459,59 +517,39 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int j = cw; j < n_tiles && ok; j += 4) {
             const int rs = j % NVR, bs = j % C::NVS;
             ok = __all_sync(0xffffffffu, wait_or_abort(&X->vr_full[rs], (j / NVR) & 1, X, status, 50));
-            // the stage was last used by tile j - 3 (the other issuer's): wait for that issuer's commit on its barrier
-            if (ok && j >= NVB_Q)
-                ok = __all_sync(0xffffffffu, wait_or_abort(&X->vq_empty[bs][(j - NVB_Q) & 1], ((j - NVB_Q) / (2 * NVB_Q)) & 1, X, status, 51));
+            if (ok && j >= C::NVS) ok = __all_sync(0xffffffffu, wait_or_abort(&X->v_empty[bs], ((j / C::NVS) - 1) & 1, X, status, 51));
             if (!ok) break;
             const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
-            uint8_t* stage = smem + C::V_OFF + bs * V_STAGE_BYTES;
+            uint8_t* stage = smem + C::V_OFF + bs * C::VSB;
 #ifndef PKV_VQ_SKIP_CONVERT                                           // (development switch: barrier traffic only)
 #pragma unroll 1
             for (int rg = 0; rg < 4; ++rg) {
                 const int r = rg * 32 + lane;
                 const uint32_t sw = ((uint32_t)r >> 1) & 3u;
                 uint8_t* dst = stage + r * 128;
-                const uint32_t sbits = *reinterpret_cast<const uint16_t*>(raw + PKV_PAGE_TOKENS * 64 + r * 2);
-                const uint32_t s2 = sbits | (sbits << 16);
-                const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 64 + ((c ^ sw) << 4));
                     const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                    uint32_t o[8];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const uint32_t w = wv[u], m = w & 0x77777777u, m2 = m >> 16, up = w << 4;
-                        uint32_t o[4];
-                        {
-                            const uint32_t lo = prmt(LO_A, LO_B, m);
-                            const uint32_t hi = prmt(HI_A, HI_B, m) | (prmt(up, w, 0xD9C8u) & 0x80808080u);
-                            o[0] = prmt(lo, hi, 0x5140u);
-                            o[1] = prmt(lo, hi, 0x7362u);
-                        }
-                        {
-                            const uint32_t lo = prmt(LO_A, LO_B, m2);
-                            const uint32_t hi = prmt(HI_A, HI_B, m2) | (prmt(up, w, 0xFBEAu) & 0x80808080u);
-                            o[2] = prmt(lo, hi, 0x5140u);
-                            o[3] = prmt(lo, hi, 0x7362u);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[k]), scale2);
-                            o[k] = *reinterpret_cast<const uint32_t*>(&pr);
-                        }
-                        const int chunk = 4 * c + u;                 // 8 dims = one 16-byte chunk of the row
-                        *reinterpret_cast<uint4*>(dst + (chunk >> 3) * (V_STAGE_BYTES / 2) + (((chunk & 7) ^ (r & 7)) << 4)) =
-                            make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int u = 0; u < 4; ++u) {                    // 8 codes -> 8 bytes: magnitude by table, sign on top
+                        const uint32_t w = wv[u], m = w & 0x77777777u, up = w << 4;
+                        o[2 * u] = prmt(LUT_A, LUT_B, m) | (prmt(up, w, 0xD9C8u) & 0x80808080u);
+                        o[2 * u + 1] = prmt(LUT_A, LUT_B, m >> 16) | (prmt(up, w, 0xFBEAu) & 0x80808080u);
                     }
+                    // 32 dims = two 16-byte chunks of the token's 128-byte row (128-byte swizzle: chunk ^ (row & 7))
+                    *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
                 }
             }
 #else
-            (void)stage; (void)raw; (void)prmt; (void)LO_A; (void)LO_B; (void)HI_A; (void)HI_B;
+            (void)stage; (void)raw; (void)prmt; (void)LUT_A; (void)LUT_B;
 #endif
             fence_proxy_async_smem();                                // generic-proxy writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&X->vq_full[bs][j & 1]);
+                mbar_arrive(&X->v_full[bs]);
                 mbar_arrive(&X->vr_empty[rs]);
             }
         }
@@ -551,6 +589,11 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             pkv_absorb_impl::body_tile<WP>(qa, b, smem + C::Q_OFF, reinterpret_cast<float*>(smem + C::P_OFF), tid - 3 * 32);
             fence_proxy_async_smem();                       // generic-proxy writes -> visible to tcgen05.mma / tcgen05.cp
             mbar_arrive(&X->q_full);
+        }
+        if constexpr (VQ) {                                  // the pad rows of the weight operands stay zero for good
+            uint4* pz = reinterpret_cast<uint4*>(smem + C::P_OFF);
+            for (int k = tid - W_SM * 32; k < 2 * P_BYTES / 16; k += 128) pz[k] = make_uint4(0u, 0u, 0u, 0u);
+            softmax_sync();                                 // ... before any thread writes a weight byte
         }
         bool ok = wait_all(&X->q_full, 0, 40);
 #pragma unroll
@@ -646,6 +689,20 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 }
                 (void)corr;
                 if (with_v && i > 0) {
+                    if constexpr (VQ) {
+#pragma unroll
+                        for (int g = 0; g < NKV; ++g)
+#pragma unroll
+                            for (int c0 = 0; c0 < NPV; c0 += 16) {   // column n = term * REP + head of the group
+                                uint32_t r[16];
+                                tmem_ld16(tl + TM_O + NPV * g + c0, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int c = 0; c < 16; ++c)
+                                    r[c] = __float_as_uint(__uint_as_float(r[c]) * corr_of(g * REP + ((c0 + c) % REP)));
+                                tmem_st16(tl + TM_O + NPV * g + c0, r);
+                            }
+                    } else
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
                         // the 16 columns of kv head g are the hi and lo weights of the 8-head group that holds its
@@ -667,6 +724,16 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 ok = wait_all(&X->pv_done[buf], ((i >> 1) - 1) & 1, 43);      // P buffer free again
                 if (!ok) break;
             }
+            float vs[VQ ? NKV : 1];                             // quantised V: this token's scale of every kv head
+            if constexpr (VQ) {
+                ok = wait_all(&X->sc_full[buf], (i >> 1) & 1, 46);
+                if (!ok) break;
+                const uint16_t* sc = reinterpret_cast<const uint16_t*>(smem + C::SC_OFF + buf * VQ_SCALE_BYTES) + row;
+#pragma unroll
+                for (int g = 0; g < NKV; ++g) vs[g] = pkv_bf16_bits_to_float(sc[g * PKV_PAGE_TOKENS]);
+                mbar_arrive(&X->sc_empty[buf]);
+            }
+            (void)vs;
             // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 8-head group
             // [hi | lo] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
             uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * PGS + (row & 7) * 2;
@@ -674,7 +741,20 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             for (int h = 0; h < HPC; ++h) {
                 const float mh = m_of(h);
                 float p = exp2f(s[h] - (mh > -INFINITY ? mh : 0.0f));                 // exp2(-inf) = 0 for masked rows
-                if (with_v) {
+                if constexpr (VQ) {
+                    // p * scale as E5M2 residual terms (each takes the error down by 2^-3; E5M2 is the top byte of the
+                    // half-precision number, so the way back is a shift), rows term * REP + head of the kv head's operand
+                    const int g = h / REP, hh = h % REP;
+                    float res = p > 0.0f ? p * vs[VQ ? g : 0] : 0.0f;      // a masked row's scale may be anything
+                    uint8_t* dst = smem + C::P_OFF + buf * P_BYTES + g * PG8 + (row >> 4) * (NPV * 16) + (row & 15);
+#pragma unroll
+                    for (int t = 0; t < VQ_TERMS; ++t) {
+                        const uint8_t b8 = (uint8_t)__nv_cvt_float_to_fp8(res, __NV_SATFINITE, __NV_E5M2);
+                        res -= __half2float(__ushort_as_half((unsigned short)((unsigned)b8 << 8)));
+                        const int n = t * REP + hh;
+                        dst[(n >> 3) * 128 + (n & 7) * 16] = b8;
+                    }
+                } else if (with_v) {
                     // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
                     // that value, so numerator and denominator of softmax . V carry the same rounding
                     const __nv_bfloat16 hi = __float2bfloat16(p);
@@ -700,7 +780,25 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         if (early) pkv_grid_wait();
         if (ok) {
             tc_fence_after_sync();
-            if (with_v) {
+            if constexpr (VQ) {
+#pragma unroll
+                for (int g = 0; g < NKV; ++g) {                 // columns term * REP + head: the three terms of a head add up
+                    float acc[REP];
+#pragma unroll
+                    for (int c = 0; c < REP; ++c) acc[c] = 0.0f;
+#pragma unroll
+                    for (int c0 = 0; c0 < VQ_TERMS * REP; c0 += 8) {
+                        uint32_t r[8];
+                        tmem_ld8(tl + TM_O + NPV * g + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            if (c0 + c < VQ_TERMS * REP) acc[(c0 + c) % REP] += __uint_as_float(r[c]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < REP; ++c) part[(h_base + g * REP + c) * (DH + 2) + row] = acc[c];
+                }
+            } else if (with_v) {
 #pragma unroll
                 for (int g = 0; g < NKV; ++g) {
                     uint32_t r[16];
@@ -748,6 +846,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     __syncthreads();
 #ifdef PKV_TIMELINE
     if (tid == 0) { PKV_TL(13); tl_buf[14] = pkv_globaltimer(); }
+#endif
+#ifdef PKV_WAITPROF
+    if (tid < 64) wp_buf[tid] = tid == 0 ? (unsigned long long)(clock64() - wp_t0) : X->waited[tid];
 #endif
     operand_released();
     if (X->abort_flag) {
@@ -801,8 +902,10 @@ int encode_rows128_map(CUtensorMap* map, const void* base, uint64_t rows, uint32
     return PKV_OK;
 }
 
+struct VMaps { CUtensorMap v, s; };
+
 template <int WP, int REP, bool WV, bool INLQ, bool VQ = false>
-int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
+int launch_tc_impl(const VMaps& vm, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
               long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
     auto kern = pkv_attn_tc_kernel<WP, REP, WV, INLQ, VQ>;
@@ -817,24 +920,24 @@ int launch_tc_impl(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cach
     rc = qa.q ? encode_rows128_map(&qmap, C->latent_dev, (uint64_t)C->n_pages * (Cfg<WP>::PAGE / 128), Cfg<WP>::QBLOB / 128)
               : encode_rows128_map(&qmap, qop, (uint64_t)batch * (Cfg<WP>::QBLOB / 128), Cfg<WP>::QBLOB / 128);
     if (rc) return rc;
-    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(n_threads<WV, VQ>()), smem, st, vmap, kmap, qmap,
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(n_split, batch, WV && REP == 1 ? NQ / 8 : 1), dim3(n_threads<WV, VQ>()), smem, st, vm.v, kmap, qmap, vm.s,
                                     pt, max_pages, seqlens, n_split, C->n_pages, L->second * logit_scale,
                                     1.0f / logit_scale, flags, partials, scores, scores_stride, status, qa));
     return PKV_OK;
 }
 
 template <int WP, int REP, bool WV, bool VQ = false>
-int launch_tc(const CUtensorMap& vmap, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
+int launch_tc(const VMaps& vm, const pkv_layer_t* L, const pkv_cache_t* C, const uint8_t* qop, const int32_t* pt,
               int max_pages, const int32_t* seqlens, int batch, int n_split, uint32_t flags, float* partials, float* scores,
               long scores_stride, int32_t* status, const pkv_absorb_impl::Args& qa, cudaStream_t st) {
     if constexpr (VQ) {                              // quantised V pages: the operand comes from pkv_absorb
         if (qa.q) return PKV_ERR_UNSUPPORTED;
-        return launch_tc_impl<WP, REP, WV, false, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
+        return launch_tc_impl<WP, REP, WV, false, true>(vm, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
                                                         scores, scores_stride, status, qa, st);
     } else {
-        return qa.q ? launch_tc_impl<WP, REP, WV, true>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials, scores,
+        return qa.q ? launch_tc_impl<WP, REP, WV, true>(vm, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials, scores,
                                                         scores_stride, status, qa, st)
-                    : launch_tc_impl<WP, REP, WV, false>(vmap, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
+                    : launch_tc_impl<WP, REP, WV, false>(vm, L, C, qop, pt, max_pages, seqlens, batch, n_split, flags, partials,
                                                          scores, scores_stride, status, qa, st);
     }
 }
@@ -863,8 +966,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     if (rep != 1 && rep != 4 && rep != 8) return PKV_ERR_UNSUPPORTED;
     if (q_dev && (((uintptr_t)q_dev) & 15u)) return PKV_ERR_INVALID;
     const bool with_v = !(flags & PKV_ATTN_SCORES_ONLY);
-    CUtensorMap vmap;
-    memset(&vmap, 0, sizeof(vmap));
+    VMaps vm;                                       // V tiles (bf16 pages, or the code tiles of quantised pages) and their scale blocks
+    memset(&vm, 0, sizeof(vm));
+    CUtensorMap& vmap = vm.v;
+    CUtensorMap& smap = vm.s;
     {
         int st = init_encoder();
         if (st) return st;
@@ -872,7 +977,10 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     const bool vq = with_v && cache->v_bits != 0;    // V pages hold per-token low-bit codes (pkv_vq_write)
     if (vq) {
         if (!cache->vq_dev || (((uintptr_t)cache->vq_dev) & 127u) || cache->head_dim != DH) return PKV_ERR_INVALID;
-        int st = encode_rows128_map(&vmap, cache->vq_dev, (uint64_t)cache->n_pages * cache->n_kv * (RAW_BYTES / 128), RAW_BYTES / 128);
+        const uint64_t rows = (uint64_t)cache->n_pages * cache->n_kv * (PKV_VQ_TILE_BYTES / 128);
+        int st = encode_rows128_map(&vmap, cache->vq_dev, rows, RAW_BYTES / 128);           // the codes of a (page, kv head) tile
+        if (st) return st;
+        st = encode_rows128_map(&smap, cache->vq_dev, rows, VQ_SCALE_BYTES / 128);          // the scales of 8 kv heads of a page
         if (st) return st;
     } else if (with_v) {
         if (!cache->v_dev || (((uintptr_t)cache->v_dev) & 15u)) return PKV_ERR_INVALID;
@@ -883,21 +991,21 @@ int pkv_attn_tc_launch(const pkv_layer_t* layer, const pkv_cache_t* cache, const
     const uint8_t* qop = (const uint8_t*)q_dev;
     int rc;
 #define PKV_TC_CASE(WP_, R_)                                                                                         \
-    rc = with_v ? launch_tc<WP_, R_, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
+    rc = with_v ? launch_tc<WP_, R_, true>(vm, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
                                            flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)       \
-                : launch_tc<WP_, R_, false>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
+                : launch_tc<WP_, R_, false>(vm, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, \
                                             flags, partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
 #define PKV_TC_VQ(WP_, R_)                                                                                                \
-    rc = launch_tc<WP_, R_, true, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
+    rc = launch_tc<WP_, R_, true, true>(vm, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags, \
                                         partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
     if (vq) {
         if (rep == 1) { if (wide) PKV_TC_VQ(256, 1); else PKV_TC_VQ(128, 1); }
         else if (rep == 8) { if (wide) PKV_TC_VQ(256, 8); else PKV_TC_VQ(128, 8); }
         else { if (wide) PKV_TC_VQ(256, 4); else PKV_TC_VQ(128, 4); }
     } else if (rep == 1 && with_v) {                // one query head per kv head: 4 CTAs of 8 heads per (sequence, split)
-        rc = wide ? launch_tc<256, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
+        rc = wide ? launch_tc<256, 1, true>(vm, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
                                             partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream)
-                  : launch_tc<128, 1, true>(vmap, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
+                  : launch_tc<128, 1, true>(vm, layer, cache, qop, page_table_dev, max_pages, seqlens_dev, batch, n_split, flags,
                                             partials_dev, scores_out_dev, scores_stride, status_dev, qa, stream);
     } else if (rep == 8) { if (wide) PKV_TC_CASE(256, 8); else PKV_TC_CASE(128, 8); }
     else { if (wide) PKV_TC_CASE(256, 4); else PKV_TC_CASE(128, 4); }      // scores only never touches V: any grouping

@@ -4,12 +4,14 @@
 // +-1.5, scale = bf16(max(amax, 1e-5) / 1.5)), four bits of storage per code as in its "nib" cache layout
 // (phasorkv/kernels/latent_attn.py:207-212).
 //
-// Pool layout (pkv_cache_t::vq_dev): per page and kv head one tile of 66 rows of 128 bytes,
-//   bytes 0 .. 8191   : codes, 64 bytes per token (two per byte, even dim in the low nibble); the 16-byte
-//                       chunk c of token r sits at chunk position c ^ ((r >> 1) & 3) of the token's 64 bytes,
-//                       so that 8 consecutive tokens read the same chunk without a shared-memory bank conflict
-//   bytes 8192 .. 8447: the 128 bf16 scales of the tile's tokens
-// tile index = page * n_kv + head.  The attention kernel copies a tile to shared memory as it is.
+// Pool layout (pkv_cache_t::vq_dev): a page is n_kv * 66 rows of 128 bytes,
+//   rows g * 64 .. g * 64 + 63 : the codes of kv head g, 64 bytes per token (two per byte, even dim in the low
+//                                nibble); the 16-byte chunk c of token r sits at chunk position c ^ ((r >> 1) & 3)
+//                                of the token's 64 bytes, so that 8 consecutive tokens read the same chunk without
+//                                a shared-memory bank conflict
+//   rows n_kv * 64 ..          : the bf16 scales, 128 per kv head (256 bytes), heads in order
+// The attention kernel copies a code tile (64 rows) and the scale block of its 8 kv heads (16 rows) to shared
+// memory as they are.
 #include "pkv_common.cuh"
 
 int pkv_check_cache(const pkv_cache_t* c);
@@ -50,11 +52,12 @@ __global__ void __launch_bounds__(256) pkv_vq_write_kernel(const uint2* __restri
         }
         packed |= code << (4 * i);
     }
-    uint8_t* tile = pool + ((size_t)(slot / PKV_PAGE_TOKENS) * n_kv + g) * PKV_VQ_TILE_BYTES;
+    uint8_t* page = pool + (size_t)(slot / PKV_PAGE_TOKENS) * n_kv * PKV_VQ_TILE_BYTES;
+    uint8_t* tile = page + (size_t)g * 8192;
     const uint32_t r = slot % PKV_PAGE_TOKENS;
     const uint32_t chunk = (lane >> 3) ^ ((r >> 1) & 3u);
     *reinterpret_cast<uint16_t*>(tile + r * 64 + chunk * 16 + (lane & 7) * 2) = (uint16_t)packed;
-    if (lane == 0) *reinterpret_cast<__nv_bfloat16*>(tile + 8192 + r * 2) = sb;
+    if (lane == 0) *reinterpret_cast<__nv_bfloat16*>(page + (size_t)n_kv * 8192 + g * 256 + r * 2) = sb;
 }
 
 // read-back in the reference's form: dequantised rows, unpacked codes, scale bit patterns
@@ -67,11 +70,12 @@ __global__ void __launch_bounds__(256) pkv_vq_read_kernel(const uint8_t* __restr
     const int tok = (int)(row / n_kv), g = (int)(row % n_kv);
     const int slot = slots[tok];
     if (slot < 0 || slot >= n_pages * PKV_PAGE_TOKENS) return;
-    const uint8_t* tile = pool + ((size_t)(slot / PKV_PAGE_TOKENS) * n_kv + g) * PKV_VQ_TILE_BYTES;
+    const uint8_t* page = pool + (size_t)(slot / PKV_PAGE_TOKENS) * n_kv * PKV_VQ_TILE_BYTES;
+    const uint8_t* tile = page + (size_t)g * 8192;
     const uint32_t r = slot % PKV_PAGE_TOKENS;
     const uint32_t chunk = (lane >> 3) ^ ((r >> 1) & 3u);
     const uint32_t packed = *reinterpret_cast<const uint16_t*>(tile + r * 64 + chunk * 16 + (lane & 7) * 2);
-    const uint16_t sbits = *reinterpret_cast<const uint16_t*>(tile + 8192 + r * 2);
+    const uint16_t sbits = *reinterpret_cast<const uint16_t*>(page + (size_t)n_kv * 8192 + g * 256 + r * 2);
     const float s = pkv_bf16_bits_to_float(sbits);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
