@@ -4,12 +4,16 @@
 // x is bf16 and therefore exact; the fp32 factor matrix enters as the sum of three bf16 matrices
 // (hi + mid + lo, exact to 2^-24 relative), i.e. three passes over the same x tile that accumulate in
 // the same 128 x W accumulator. One CTA owns 128 tokens and the whole latent row of each:
-//   warp 0     producer: TMA tensor loads of the x tile [128 tokens x 64] and of the three factor
-//              tiles [W x 64] per 64-wide slice of d_model, through a ring of shared-memory stages
+//   warp 0     producer: TMA tensor loads of the x tile [128 tokens x KT] and of the three factor
+//              tiles [W x KT] per KT-wide slice of d_model, through a ring of shared-memory stages
 //   warp 1     MMA issuer
-//   warps 2-5  epilogue, one token (TMEM lane) per thread: accumulator row -> shared memory, rotation
-//              of the pairs (k, R + k) by the token's phasors, NVFP4 quantisation with the reference's
-//              rounding, store into the token's cache page
+//   all 16 warps, once the accumulator is complete: the epilogue. A warp reads the tensor-memory lanes of
+//              its quarter (warp % 4: 32 tokens, one per lane) and takes every fourth *unit* (warp / 4): a
+//              unit is the 16 real columns 16u .. 16u+15 with their 16 imaginary partners R + 16u .., i.e.
+//              two whole NVFP4 blocks, or one block of the unrotated rest. Rotation by the token's phasors,
+//              NVFP4 quantisation with the reference's rounding and the store into the token's cache page
+//              all happen in registers, straight from tensor memory. (R not a multiple of 16: a real block
+//              and its partners do not line up; then four warps take a token row each through shared memory.)
 // Every wait is bounded; a give-up is recorded in `status` and the roles unwind.
 #include "pkv_common.cuh"
 #include "pkv_tcgen05.cuh"
@@ -21,26 +25,45 @@ namespace {
 using namespace pkv;
 
 constexpr int TM_TOK = 128;                  // tokens per CTA
-constexpr int KT = 64;                       // d_model slice per stage: 128-byte rows, 128-byte swizzle
-constexpr int X_TILE = TM_TOK * KT * 2;      // 16 KB
-constexpr int NTHREADS = 6 * 32;
+constexpr int NTHREADS = 16 * 32;
+constexpr int NST_MAX = 4;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
+// d_model slice per stage. What bounds the main loop is how long a slice takes to arrive, so a CTA keeps all of its
+// shared memory in flight; at W = 256 four slices of 32 (64-byte rows, 64-byte swizzle) do that better than two of
+// 64 (measured 77 against 86 us for 16384 tokens), at W = 128 three slices of 64 (128-byte rows and swizzle) beat
+// seven of 32 (46 against 53 us: a slice of 32 is only 0.2 us of MMA work).
 template <int WP>
 struct WCfg {
+    static constexpr int KT = WP == 256 ? 32 : 64;
+    static constexpr uint64_t SWZ = KT == 64 ? SWZ_128B : SWZ_64B;
+    static constexpr int SBO = 8 * KT * 2;                         // 8 rows of a swizzle atom
+    static constexpr int X_TILE = TM_TOK * KT * 2;
     static constexpr int B_TILE = WP * KT * 2;                     // one bf16 term of the factor slice
     static constexpr int STAGE = X_TILE + 3 * B_TILE;
-    static constexpr int NST = WP == 256 ? 2 : 3;
-    static constexpr int ROWS = TM_TOK * (WP + 1) * 4;              // epilogue rows, reusing the stages
+    static constexpr int FIT = (232448 - 1024) / STAGE;
+    static constexpr int NST = FIT > NST_MAX ? NST_MAX : FIT;
+    static constexpr int ROWS = TM_TOK * (WP + 1) * 4;              // epilogue rows (R % 16 != 0), reusing the stages
     static constexpr int BODY = NST * STAGE > ROWS ? NST * STAGE : ROWS;
     static constexpr int SMEM = BODY + 256;
+    static_assert(STAGE % 1024 == 0 && NST >= 2 && SMEM <= 232448, "stages");
 };
 
 struct WExtra {
-    uint64_t full[3], empty[3], done;
+    uint64_t full[NST_MAX], empty[NST_MAX], done;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
+
+// store one quantised block of a token row
+template <int WP>
+__device__ __forceinline__ void store_block(uint8_t* page, uint32_t pr_row, int j, int codes_bytes, const float (&v)[16], float second,
+                                            bool round_up) {
+    uint8_t sb;
+    const uint2 packed = pkv_quantize_block16(v, second, sb, round_up);
+    *reinterpret_cast<uint2*>(page + pkv_code_offset(pr_row, j * 8, WP / 2)) = packed;
+    page[codes_bytes + pkv_scale_offset(pr_row, j)] = sb;
+}
 
 __device__ __forceinline__ bool wwait(uint64_t* bar, uint32_t parity, WExtra* X, int32_t* status, int where) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -62,11 +85,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
     extern __shared__ __align__(1024) uint8_t smem[];
     WExtra* X = reinterpret_cast<WExtra*>(smem + C::BODY);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int KT = C::KT, X_TILE = C::X_TILE;
     const int tok0 = blockIdx.x * TM_TOK;
     const int n_kt = D / KT;
     pkv_grid_launch_dependents();
     if (tid == 0) {
-        for (int s = 0; s < 3; ++s) { mbar_init(&X->full[s], 1); mbar_init(&X->empty[s], 1); }
+        for (int s = 0; s < NST_MAX; ++s) { mbar_init(&X->full[s], 1); mbar_init(&X->empty[s], 1); }
         mbar_init(&X->done, 1);
         X->abort_flag = 0;
         fence_barrier_init();
@@ -110,22 +134,97 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
                 for (int t = 0; t < 3; ++t)
 #pragma unroll
                     for (int k = 0; k < KT / 16; ++k)
-                        mma_bf16(tb, smem_desc(xa + k * 32, 0, 1024, SWZ_128B),
-                                 smem_desc(xa + X_TILE + t * C::B_TILE + k * 32, 0, 1024, SWZ_128B), idesc, (kt | t | k) != 0);
+                        mma_bf16(tb, smem_desc(xa + k * 32, 0, C::SBO, C::SWZ),
+                                 smem_desc(xa + X_TILE + t * C::B_TILE + k * 32, 0, C::SBO, C::SWZ), idesc, (kt | t | k) != 0);
                 tc_commit(&X->empty[s]);
             }
             if (ok) tc_commit(&X->done);
         }
-    } else {
-        // ================================================================== epilogue: one token per thread
-        const int quad = warp & 3;
+    }
+    __syncwarp();
+
+    // ================================================================== epilogue: every warp
+    {
+        const int quad = warp & 3, grp = warp >> 2;
         const int rowi = quad * 32 + lane;
         const int tok = tok0 + rowi;
-        bool ok = __all_sync(0xffffffffu, wwait(&X->done, 0, X, status, 62));
-        if (ok) {
-            tc_fence_after_sync();
+        const bool ok = __all_sync(0xffffffffu, wwait(&X->done, 0, X, status, 62));
+        const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
+        const bool live = ok && tok < n_tokens;
+        const int slot = live && latent ? slots[tok] : -1;
+        const bool paged = slot >= 0 && slot < n_pages * PKV_PAGE_TOKENS;
+        uint8_t* page = paged ? latent + (size_t)(slot / PKV_PAGE_TOKENS) * pkv_page_bytes(W) : nullptr;
+        const uint32_t pr_row = paged ? slot % PKV_PAGE_TOKENS : 0;
+        const int codes_bytes = pkv_codes_bytes(W);
+        constexpr int NB = WP / 16;
+        if (ok) tc_fence_after_sync();
+        if (ok && (R & 15) == 0) {
+            // units: R / 16 rotated pairs of blocks (u, R / 16 + u), then the blocks behind 2R one by one
+            const int n_pair = R >> 4, n_unit = n_pair + (NB - 2 * n_pair);
+            const double pos = live && !phasors ? (double)positions[tok] : 0.0;
+            for (int u = grp; u < n_unit; u += 4) {
+                if (u < n_pair) {
+                    uint32_t ra[16], rb[16];
+                    tmem_ld16(tl + 16 * u, ra);                         // whole warp: tensor-memory loads are warp-wide
+                    tmem_ld16(tl + R + 16 * u, rb);
+                    tmem_ld_wait();
+                    if (live) {
+                        float re[16], im[16];
+                        int f_prev = -1;
+                        float pr = 1.0f, pi = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int f = freq[16 * u + i];
+                            if (f != f_prev) {                         // attn_scale * e^{i * position * inv_freq[f]}
+                                if (phasors) {
+                                    const float2 p = phasors[(size_t)tok * h2 + f];
+                                    pr = p.x; pi = p.y;
+                                } else {
+                                    double sn, cs;
+                                    sincos(pos * inv_freq[f], &sn, &cs);
+                                    pr = (float)((double)attn_scale * cs); pi = (float)((double)attn_scale * sn);
+                                }
+                                f_prev = f;
+                            }
+                            const float a = __uint_as_float(ra[i]), b = __uint_as_float(rb[i]);
+                            re[i] = __fsub_rn(__fmul_rn(a, pr), __fmul_rn(b, pi));
+                            im[i] = __fadd_rn(__fmul_rn(a, pi), __fmul_rn(b, pr));
+                        }
+                        if (latent_out) {
+                            float4* o = reinterpret_cast<float4*>(latent_out + (size_t)tok * W + 16 * u);
+                            float4* o2 = reinterpret_cast<float4*>(latent_out + (size_t)tok * W + R + 16 * u);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                o[i] = make_float4(re[4 * i], re[4 * i + 1], re[4 * i + 2], re[4 * i + 3]);
+                                o2[i] = make_float4(im[4 * i], im[4 * i + 1], im[4 * i + 2], im[4 * i + 3]);
+                            }
+                        }
+                        if (paged) {
+                            store_block<WP>(page, pr_row, u, codes_bytes, re, second.of(u), scale_up != 0);
+                            store_block<WP>(page, pr_row, n_pair + u, codes_bytes, im, second.of(n_pair + u), scale_up != 0);
+                        }
+                    }
+                } else {
+                    const int j = 2 * n_pair + (u - n_pair);
+                    uint32_t ra[16];
+                    tmem_ld16(tl + 16 * j, ra);
+                    tmem_ld_wait();
+                    if (live) {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(ra[i]);
+                        if (latent_out && 16 * j < W) {                // W is a multiple of 16: a block is all row or all padding
+                            float4* o = reinterpret_cast<float4*>(latent_out + (size_t)tok * W + 16 * j);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        }
+                        if (paged) store_block<WP>(page, pr_row, j, codes_bytes, v, second.of(j), scale_up != 0);
+                    }
+                }
+            }
+        } else if (ok && grp == 0) {
+            // real blocks and their imaginary partners do not line up: a thread takes a whole token row through shared memory
             float* row = reinterpret_cast<float*>(smem) + (size_t)rowi * (WP + 1);     // the stages are idle now
-            const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < WP; c0 += 16) {
                 uint32_t r[16];
@@ -134,8 +233,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
 #pragma unroll
                 for (int i = 0; i < 16; ++i) row[c0 + i] = __uint_as_float(r[i]);
             }
-            if (tok < n_tokens) {
-                // rotation of (column k, column R + k) by attn_scale * e^{i * position * inv_freq[freq[k]]}
+            if (live) {
                 const double pos = phasors ? 0.0 : (double)positions[tok];
                 int f_prev = -1;
                 float pr = 1.0f, pi = 0.0f;
@@ -158,21 +256,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
                 }
                 if (latent_out)
                     for (int c = 0; c < W; ++c) latent_out[(size_t)tok * W + c] = row[c];
-                const int slot = latent ? slots[tok] : -1;
-                if (slot >= 0 && slot < n_pages * PKV_PAGE_TOKENS) {
-                    constexpr int RB = WP / 2, NB = WP / 16;
-                    uint8_t* page = latent + (size_t)(slot / PKV_PAGE_TOKENS) * pkv_page_bytes(W);
-                    const uint32_t pr_row = slot % PKV_PAGE_TOKENS;
-                    const int codes_bytes = pkv_codes_bytes(W);
+                if (paged) {
 #pragma unroll 1
                     for (int j = 0; j < NB; ++j) {
                         float v[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = row[j * 16 + i];
-                        uint8_t sb;
-                        const uint2 packed = pkv_quantize_block16(v, second.of(j), sb, scale_up != 0);
-                        *reinterpret_cast<uint2*>(page + pkv_code_offset(pr_row, j * 8, RB)) = packed;
-                        page[codes_bytes + pkv_scale_offset(pr_row, j)] = sb;
+                        store_block<WP>(page, pr_row, j, codes_bytes, v, second.of(j), scale_up != 0);
                     }
                 }
             }
@@ -185,7 +275,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
 
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_w = nullptr;
 
-int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
     if (!g_encode_w) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -195,10 +285,11 @@ int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
     }
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {KT, box_rows};
+    cuuint32_t box[2] = {box_cols, box_rows};                  // a box row is one swizzle row: 64 or 128 bytes
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode_w(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { g_pkv_last_cuda_error = (int)r; return PKV_ERR_CUDA; }
     return PKV_OK;
@@ -223,7 +314,7 @@ int launch_write_tc(const CUtensorMap& xmap, const CUtensorMap& bmap, const pkv_
 
 // bf16 x, three-term bf16 factors present, d_model a multiple of 64: the tensor-core write can run
 bool pkv_write_tc_usable(const pkv_layer_t* L, int32_t x_dtype, const void* x_dev) {
-    return x_dtype == PKV_BF16 && L->Bw_bf16x3_dev && (L->d_model % KT) == 0 && !(((uintptr_t)x_dev) & 15u) &&
+    return x_dtype == PKV_BF16 && L->Bw_bf16x3_dev && (L->d_model % 64) == 0 && !(((uintptr_t)x_dev) & 15u) &&
            !(((uintptr_t)L->Bw_bf16x3_dev) & 15u);
 }
 
@@ -231,9 +322,10 @@ int pkv_write_tc_launch(const pkv_layer_t* L, const pkv_cache_t* C, const void* 
                         const int32_t* slots, int n, float* latent_out, int32_t* status, cudaStream_t st) {
     const int W = 2 * L->R + L->R_s, WP = pkv_padded_width(W);
     CUtensorMap xmap, bmap;
-    int rc = encode_2d_bf16(&xmap, x_dev, (uint64_t)n, (uint64_t)L->d_model, TM_TOK);
+    const uint32_t kt = WP == 128 ? WCfg<128>::KT : WCfg<256>::KT;
+    int rc = encode_2d_bf16(&xmap, x_dev, (uint64_t)n, (uint64_t)L->d_model, TM_TOK, kt);
     if (rc) return rc;
-    rc = encode_2d_bf16(&bmap, L->Bw_bf16x3_dev, (uint64_t)3 * WP, (uint64_t)L->d_model, (uint32_t)WP);
+    rc = encode_2d_bf16(&bmap, L->Bw_bf16x3_dev, (uint64_t)3 * WP, (uint64_t)L->d_model, (uint32_t)WP, kt);
     if (rc) return rc;
     return WP == 128 ? launch_write_tc<128>(xmap, bmap, L, C, pos, ph, slots, n, latent_out, status, st)
                      : launch_write_tc<256>(xmap, bmap, L, C, pos, ph, slots, n, latent_out, status, st);
