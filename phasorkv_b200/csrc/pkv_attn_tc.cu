@@ -38,12 +38,12 @@ constexpr int NK_STAGES = 2, NV_STAGES = 4;
 // per-token scales of a page (one 2 KB block for the CTA's 8 kv heads) have a ring of their own: the softmax folds
 // them into the weights (E5M2, whose exponent range takes any scale), so that P.V runs as kind::f8f6f4 MMAs
 // (K = 32) on exact V operands.
-constexpr int NVR = 4, NVS_Q = 6;
+constexpr int NVR = 4, NVS_Q = 4;
 constexpr int RAW_BYTES = PKV_PAGE_TOKENS * 64;                // codes of one tile
 constexpr int VQ_STAGE_BYTES = PKV_PAGE_TOKENS * DH;           // the tile as E4M3: one 128-byte row per token
 constexpr int VQ_SCALE_BYTES = 8 * PKV_PAGE_TOKENS * 2;        // bf16 scales of 8 kv heads x 128 tokens
-constexpr int VQ_TERMS = 4;                                    // weights: p * scale as E5M2 residual terms (2^-12 of the value,
-                                                               // any magnitude of scale from 2^-14 to 5e4)
+constexpr int VQ_TERMS = 4;                                    // weights: p * scale as E5M2 terms (2^-11 of the value, any scale
+                                                               // whose product with p stays inside half precision)
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
@@ -79,7 +79,8 @@ struct Cfg {
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
     static constexpr int R_OFF = V_OFF + NVS * VSB;              // raw tiles of quantised V pages
     static constexpr int SC_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);      // their scale blocks, two pages
-    static constexpr int P_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);
+    static constexpr int L_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);   // row sums of the softmax: [head][token row] fp32
+    static constexpr int P_OFF = L_OFF + (VQ ? NQ * PKV_PAGE_TOKENS * 4 : 0);
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
     static constexpr int SMEM = X_OFF + 4096;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
@@ -92,8 +93,8 @@ struct Extra {                       // lives at X_OFF
     uint64_t vr_full[NVR], vr_empty[NVR];                        // raw tiles of quantised V pages
     // Quantised V: the operand stages are filled by four converter warps and drained by two MMA issuers (tiles of
     // even / odd kv heads). A parity wait only tells neighbouring phases apart, so a barrier must be waited for by
-    // one thread, phase after phase: tile j uses stage j % 6 (an even number of stages: a stage always serves the
-    // same issuer) and raw stage j % 4 (always the same converter warp).
+    // one thread, phase after phase: tile j uses operand stage and raw stage j % 4 (an even number of stages: a stage
+    // always serves the same issuer, and always the same converter warp).
     uint64_t sc_full[2], sc_empty[2];                            // scale blocks of quantised V pages
 #ifdef PKV_WAITPROF
     unsigned long long waited[64];
@@ -142,6 +143,11 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ex
 // 6 last page asked for, 7 query there, 8 first page there, 9 last scores committed, 10 first scores seen,
 // 11 last page reduced, 12 partial written, 13 all roles done, 14 exit (globaltimer ns), 15 SM id.
 // A development aid for the fixed cost of a launch; the library is never shipped with it.
+#ifdef PKV_WAITPROF
+#define PKV_WPM(slot) do { const long long n_ = clock64(); if ((threadIdx.x & 31) == 0) atomicAdd(&X->waited[slot], (unsigned long long)(n_ - wp_t)); wp_t = n_; } while (0)
+#else
+#define PKV_WPM(slot) do { } while (0)
+#endif
 #ifdef PKV_TIMELINE
 #define PKV_TL(slot) do { tl_buf[slot] = clock64(); } while (0)
 __device__ __forceinline__ long long pkv_globaltimer() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
@@ -170,10 +176,11 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     constexpr int HPC = NKV * REP;                         // query heads per CTA
     constexpr int PGS = (HPC / 8) * 256;                   // bytes of P per 8-token group: per 8 heads [hi 128 | lo 128]
     // quantised V: the weights of kv head g are NPV operand rows (row = term * REP + head of the group; VQ_TERMS E5M2
-    // residual terms of p * scale, further rows zero), K-major in 16-token core matrices
+    // residual terms of p * scale, further rows zero), MN-major: a token's 16 rows of an MN group are 16 contiguous
+    // bytes, tokens 16 bytes apart, the second MN group (REP = 8) 2 KB on
     constexpr int NPV = REP == 8 ? 32 : 16;
-    static_assert(!VQ || VQ_TERMS * REP <= NPV, "weight rows of a kv head");
-    constexpr int PG8 = (PKV_PAGE_TOKENS / 16) * NPV * 16; // bytes of one kv head's weights of a page
+    static_assert(!VQ || (VQ_TERMS == 4 && VQ_TERMS * REP <= NPV), "weight rows of a kv head");
+    constexpr int PG8 = PKV_PAGE_TOKENS * NPV;             // bytes of one kv head's weights of a page
     constexpr int VQ_TILE_ROWS = RAW_BYTES / 128, VQ_PAGE_ROWS = (NQ / REP) * (PKV_VQ_TILE_BYTES / 128);
     const int h_base = (WV ? (int)blockIdx.z : 0) * HPC, g_base = (WV ? (int)blockIdx.z : 0) * NKV;
     static_assert(WV || HPC == NQ, "scores-only launches use a grouped-query instantiation");
@@ -409,7 +416,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             constexpr int STEP = WV ? 1 : 2;
             const uint32_t sfb_tm = tb + TM_SFB + (first ? 16u : 0u);
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
-            constexpr uint32_t idesc_o = VQ ? idesc_f8(128, NPV, true, false, 0u, 1u) : idesc_bf16(128, 16, true, false);   // V: E4M3, weights: E5M2
+            constexpr uint32_t idesc_o = VQ ? idesc_f8(128, NPV, true, true, 0u, 1u) : idesc_bf16(128, 16, true, false);   // V: E4M3, weights: E5M2
             const bool pv_only = VQ && warp == 3;
             bool ok = pv_only || wait_or_abort(&X->q_full, 0, X, status, 30);
             if (warp == 2) PKV_TL(7);
@@ -431,13 +438,14 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                     const uint32_t va = sbase + C::V_OFF + s * C::VSB;
                     if constexpr (VQ) {
                         // A: the tile as E4M3, 128 tokens x 128 bytes (dims contiguous: MN-major, one 128-byte swizzle atom
-                        // wide); B: this kv head's weight rows; K = 32 tokens per instruction
+                        // wide); B: this kv head's weight rows, MN-major without swizzle (groups of 8 tokens 128 bytes
+                        // apart, MN groups of 16 rows 2 KB apart); K = 32 tokens per instruction
                         const uint64_t v8_desc = smem_desc(va, 0, 1024, SWZ_128B);
-                        const uint64_t p8_desc = smem_desc(sbase + C::P_OFF + pb * P_BYTES + g * PG8, NPV * 16, 128, SWZ_NONE);
+                        const uint64_t p8_desc = smem_desc(sbase + C::P_OFF + pb * P_BYTES + g * PG8, 128, NPV == 16 ? 128 : PKV_PAGE_TOKENS * 16, SWZ_NONE);
 #ifndef PKV_VQ_SKIP_PV
 #pragma unroll
                         for (int k = 0; k < PKV_PAGE_TOKENS / 32; ++k)
-                            mma_f8(tb + TM_O + NPV * g, v8_desc + (uint64_t)(k * 32 * 128 / 16), p8_desc + (uint64_t)(k * 2 * NPV * 16 / 16), idesc_o,
+                            mma_f8(tb + TM_O + NPV * g, v8_desc + (uint64_t)(k * 32 * 128 / 16), p8_desc + (uint64_t)(k * 32 * 16 / 16), idesc_o,
                                    !(i == 0 && k == 0));
 #endif
                         tc_commit(empty_bar);
@@ -521,7 +529,12 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             if (!ok) break;
             const uint8_t* raw = smem + C::R_OFF + rs * RAW_BYTES;
             uint8_t* stage = smem + C::V_OFF + bs * C::VSB;
+#ifdef PKV_WAITPROF
+            long long wp_t = clock64();
+#endif
 #ifndef PKV_VQ_SKIP_CONVERT                                           // (development switch: barrier traffic only)
+            // (a compact loop on purpose: unrolled, this code and the softmax loop no longer fit the instruction cache
+            // together, and both then run at the speed of instruction fetch)
 #pragma unroll 1
             for (int rg = 0; rg < 4; ++rg) {
                 const int r = rg * 32 + lane;
@@ -552,6 +565,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 mbar_arrive(&X->v_full[bs]);
                 mbar_arrive(&X->vr_empty[rs]);
             }
+            PKV_WPM(58);                                    // one tile converted
         }
     } else {
         // ================================================================== softmax (128 threads, one token row each)
@@ -573,16 +587,15 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // Per head (all kept in registers, identical in every thread that shares statistics): the
         // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
         // this thread's share of the sum of 2^(s - m).
-        // (With quantised V the CTA has 12 warps and 168 registers per thread. The column scales then stay in
-        // shared memory, where the query operand's tail holds them, and are read as broadcasts; the reference
-        // maxima, identical in every lane, are kept one per lane -- lane h holds head h's -- and fetched by
-        // shuffle; so are the rescale factors.)
-        float cs[VQ ? 1 : HPC], m[VQ ? 1 : HPC], l[HPC];
+        // (With quantised V the loops over the heads are not unrolled, so nothing per head can live in a register
+        // array: the column scales stay in shared memory, where the query operand's tail holds them, and are read
+        // as broadcasts; the reference maxima, identical in every lane, are kept one per lane -- lane h holds head
+        // h's -- and fetched by shuffle, so are the rescale factors; the row sums have a shared-memory array.)
+        float cs[VQ ? 1 : HPC], m[VQ ? 1 : HPC], l[VQ ? 1 : HPC];
         float m_lane = -INFINITY;
-        auto m_of = [&](int h) -> float {
-            if constexpr (VQ) return __shfl_sync(0xffffffffu, m_lane, h);
-            else return m[VQ ? 0 : h];
-        };
+        float* const lsm = reinterpret_cast<float*>(smem + C::L_OFF) + row;       // [head][token row]
+        auto m_of = [&](int h) -> float { return __shfl_sync(0xffffffffu, m_lane, h); };
+        (void)lsm; (void)m_of; (void)m_lane;
         if constexpr (INLQ) if (sg == 0) {
             // the query may come from the launch before this one unless the caller says it was ready earlier
             if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
@@ -590,18 +603,15 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             fence_proxy_async_smem();                       // generic-proxy writes -> visible to tcgen05.mma / tcgen05.cp
             mbar_arrive(&X->q_full);
         }
-        if constexpr (VQ) {                                  // the pad rows of the weight operands stay zero for good
-            uint4* pz = reinterpret_cast<uint4*>(smem + C::P_OFF);
-            for (int k = tid - W_SM * 32; k < 2 * P_BYTES / 16; k += 128) pz[k] = make_uint4(0u, 0u, 0u, 0u);
-            softmax_sync();                                 // ... before any thread writes a weight byte
-        }
         bool ok = wait_all(&X->q_full, 0, 40);
+        if constexpr (VQ) {
+#pragma unroll 1
+            for (int h = 0; h < HPC; ++h) lsm[h * PKV_PAGE_TOKENS] = 0.0f;
+        } else {
 #pragma unroll
-        for (int h = 0; h < HPC; ++h) {
-            if constexpr (!VQ) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; }
-            l[h] = 0.0f;
+            for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
         }
-        (void)cs; (void)m;
+        (void)cs; (void)m; (void)l;
         for (int i = sg; i < P && ok; i += SG) {
             const int sb = i % NSB;                         // score buffer
             const int buf = i & 1;                          // P buffer and exchange slots
@@ -609,6 +619,157 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             if (!ok) break;
             if (i == 0 && warp == W_SM && lane == 0) PKV_TL(10);
             tc_fence_after_sync();
+#ifdef PKV_WAITPROF
+            long long wp_t = clock64();
+#endif
+            if constexpr (VQ) {
+                // ---------------- quantised V pages. Compact loops over the kv heads: unrolled over all 32 heads, this
+                // code and the converter's no longer fit the instruction cache together, and both roles then run at the
+                // speed of instruction fetch. The scores are read from tensor memory twice (vote, then weights) instead
+                // of kept in 32 registers, the row sums live in shared memory.
+                const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
+                const bool valid = token < T;
+                const float* hs = rs + h_base;
+                const uint32_t s_tm = tl + TM_S + 128 * sb + h_base;
+                auto load_scores = [&](int g, float (&sv)[REP]) {
+                    uint32_t r[PKV_QUERY_TERMS][REP];
+#pragma unroll
+                    for (int t = 0; t < PKV_QUERY_TERMS; ++t) tmem_ldn<REP>(s_tm + 32 * t + g * REP, r[t]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) {
+                        float a = __uint_as_float(r[0][hh]);
+#pragma unroll
+                        for (int t = 1; t < PKV_QUERY_TERMS; ++t) a += __uint_as_float(r[t][hh]);   // the terms share the head's tensor scale
+                        a *= hs[g * REP + hh] * col_scale;
+                        sv[hh] = valid ? a : -INFINITY;
+                    }
+                };
+                // ---- does any head of any row outgrow its reference maximum by more than the threshold?
+                float exc = -INFINITY;
+#pragma unroll 1
+                for (int g = 0; g < NKV; ++g) {
+                    float sv[REP];
+                    load_scores(g, sv);
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) exc = fmaxf(exc, sv[hh] - m_of(g * REP + hh));   // +inf while the head has no reference yet
+                }
+                PKV_WPM(52);
+                bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
+                if (lane == 0) X->wflag[buf][quad] = grow ? 1 : 0;
+                ok = softmax_sync();
+                if (!ok) break;
+                grow = (X->wflag[buf][0] | X->wflag[buf][1] | X->wflag[buf][2] | X->wflag[buf][3]) != 0;
+                PKV_WPM(53);
+                if (grow) {
+                    float wm = -INFINITY;                   // lane h: the tile maximum of head h
+#pragma unroll 1
+                    for (int g = 0; g < NKV; ++g) {
+                        float sv[REP];
+                        load_scores(g, sv);
+#pragma unroll
+                        for (int hh = 0; hh < REP; ++hh) {
+                            const uint32_t red = __reduce_max_sync(0xffffffffu, f2ord(sv[hh]));
+                            if (lane == g * REP + hh) wm = ord2f(red);
+                        }
+                    }
+                    X->wmax[buf][quad][lane] = wm;
+                    ok = softmax_sync();
+                    if (!ok) break;
+                    const float tm = fmaxf(fmaxf(X->wmax[buf][0][lane], X->wmax[buf][1][lane]),
+                                           fmaxf(X->wmax[buf][2][lane], X->wmax[buf][3][lane]));
+                    if (i > 0) {                            // the accumulators must be at rest before they are rescaled
+                        ok = wait_all(&X->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, 42);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+                    const float m_new = fmaxf(m_lane, tm);
+                    const float corr_lane = m_lane > -INFINITY ? exp2f(m_lane - m_new) : 1.0f;     // nothing accumulated yet: leave as is
+                    m_lane = m_new;
+#pragma unroll 1
+                    for (int h = 0; h < HPC; ++h) lsm[h * PKV_PAGE_TOKENS] *= __shfl_sync(0xffffffffu, corr_lane, h);
+                    if (i > 0) {
+#pragma unroll 1
+                        for (int g = 0; g < NKV; ++g)
+#pragma unroll 1
+                            for (int c0 = 0; c0 < NPV; c0 += 16) {   // column n = term * REP + head of the group
+                                uint32_t r[16];
+                                tmem_ld16(tl + TM_O + NPV * g + c0, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int c = 0; c < 16; ++c)
+                                    r[c] = __float_as_uint(__uint_as_float(r[c]) * __shfl_sync(0xffffffffu, corr_lane, g * REP + ((c0 + c) % REP)));
+                                tmem_st16(tl + TM_O + NPV * g + c0, r);
+                            }
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                    }
+                }
+                PKV_WPM(54);
+                if (i >= 2) {
+                    ok = wait_all(&X->pv_done[buf], ((i >> 1) - 1) & 1, 43);      // P buffer free again
+                    if (!ok) break;
+                }
+                ok = wait_all(&X->sc_full[buf], (i >> 1) & 1, 46);               // this page's scales
+                if (!ok) break;
+                PKV_WPM(55);
+                // ---- weights relative to the reference maximum, times the token's scale of the kv head, as E5M2 terms:
+                // in half precision (two heads per register) a term is the number's top byte (E5M2 = a half cut after two
+                // mantissa bits) and the remainder is an exact subtraction; four terms leave less than 2^-11 of the value.
+                // The kv head's operand row of this token is 16 contiguous bytes per MN group, byte n = term * REP + head.
+                const uint16_t* sc = reinterpret_cast<const uint16_t*>(smem + C::SC_OFF + buf * VQ_SCALE_BYTES) + row;
+                uint8_t* pdst = smem + C::P_OFF + buf * P_BYTES + row * 16;
+#pragma unroll 1
+                for (int g = 0; g < NKV; ++g) {
+                    float sv[REP], pw[REP];
+                    load_scores(g, sv);
+                    const float vsg = pkv_bf16_bits_to_float(sc[g * PKV_PAGE_TOKENS]);
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) {
+                        const int h = g * REP + hh;
+                        if (scores_out && valid) scores_out[((size_t)b * NQ + h_base + h) * scores_stride + token] = sv[hh] * inv_logit_scale;
+                        const float mh = m_of(h);
+                        const float p = exp2f(sv[hh] - (mh > -INFINITY ? mh : 0.0f));     // exp2(-inf) = 0 for masked rows
+                        pw[hh] = p > 0.0f ? fminf(p * vsg, 57344.0f) : 0.0f;            // a masked row's scale may be anything
+                        lsm[h * PKV_PAGE_TOKENS] += p;
+                    }
+                    constexpr int NP = (REP + 1) / 2, NW = (REP + 3) / 4;
+                    uint32_t x[NP], wd[VQ_TERMS][NW];
+#pragma unroll
+                    for (int k = 0; k < NP; ++k) {
+                        const __half2 h2 = __floats2half2_rn(pw[2 * k], 2 * k + 1 < REP ? pw[2 * k + 1 < REP ? 2 * k + 1 : 0] : 0.0f);
+                        x[k] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+#pragma unroll
+                    for (int t = 0; t < VQ_TERMS; ++t) {
+#pragma unroll
+                        for (int w = 0; w < NW; ++w)              // top bytes of four heads, in head order
+                            asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(wd[t][w]) : "r"(x[2 * w]), "r"(2 * w + 1 < NP ? x[2 * w + 1 < NP ? 2 * w + 1 : 0] : 0u));
+                        if (t + 1 < VQ_TERMS) {
+#pragma unroll
+                            for (int k = 0; k < NP; ++k) {
+                                const uint32_t top = x[k] & 0xFF00FF00u;
+                                const __half2 r2 = __hsub2(*reinterpret_cast<const __half2*>(&x[k]), *reinterpret_cast<const __half2*>(&top));
+                                x[k] = *reinterpret_cast<const uint32_t*>(&r2);
+                            }
+                        }
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(pdst + g * PG8);
+                    if constexpr (REP == 8) {                     // 32 rows: terms 0, 1 in the first MN group, 2, 3 in the second
+                        dst[0] = make_uint4(wd[0][0], wd[0][1], wd[1][0], wd[1][1]);
+                        dst[PKV_PAGE_TOKENS] = make_uint4(wd[2][0], wd[2][1], wd[3][0], wd[3][1]);
+                    } else if constexpr (REP == 4) {
+                        dst[0] = make_uint4(wd[0][0], wd[1][0], wd[2][0], wd[3][0]);
+                    } else {                                      // one head: rows 0 .. 3 are its terms, the rest stay zero
+                        dst[0] = make_uint4((wd[0][0] & 0xFFu) | ((wd[1][0] & 0xFFu) << 8) | ((wd[2][0] & 0xFFu) << 16) | (wd[3][0] << 24), 0u, 0u, 0u);
+                    }
+                }
+                mbar_arrive(&X->sc_empty[buf]);
+                tc_fence_before_sync();
+                mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
+                fence_proxy_async_smem();                   // generic-proxy writes -> visible to the tensor core
+                mbar_arrive(&X->p_full[buf]);
+            } else {
             float s[HPC];
             {
 #pragma unroll
@@ -623,8 +784,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < HPC; ++h) s[h] *= VQ ? rs[h_base + h] * col_scale : cs[VQ ? 0 : h];
+                for (int h = 0; h < HPC; ++h) s[h] *= cs[h];
             }
+            PKV_WPM(52);                                    // scores out of tensor memory
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
             const bool valid = token < T;
             if (scores_out && valid) {
@@ -636,7 +798,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
                 if (!valid) s[h] = -INFINITY;
-                exc = fmaxf(exc, s[h] - m_of(h));           // +inf while the head has no reference yet
+                exc = fmaxf(exc, s[h] - m[h]);              // +inf while the head has no reference yet
             }
             bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
             if (with_v) {                                   // P.V needs one reference per head for all 128 rows
@@ -645,6 +807,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 if (!ok) break;
                 grow = (X->wflag[buf][0] | X->wflag[buf][1] | X->wflag[buf][2] | X->wflag[buf][3]) != 0;
             }                                               // scores only: every warp keeps its own statistics
+            PKV_WPM(53);                                    // vote (with its rendezvous)
             if (grow) {
                 // exact tile maximum per head: warp reduction, then (with V) across the four warps
                 float wm = -INFINITY;
@@ -666,43 +829,15 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         tc_fence_after_sync();
                     }
                 }
-                float corr[VQ ? 1 : HPC];
-                float corr_lane = 1.0f;
-                auto corr_of = [&](int h) -> float {
-                    if constexpr (VQ) return __shfl_sync(0xffffffffu, corr_lane, h);
-                    else return corr[VQ ? 0 : h];
-                };
-                if constexpr (VQ) {                         // lane h: head h
-                    const float m_new = fmaxf(m_lane, tm);
-                    corr_lane = m_lane > -INFINITY ? exp2f(m_lane - m_new) : 1.0f;
-                    m_lane = m_new;
+                float corr[HPC];
 #pragma unroll
-                    for (int h = 0; h < HPC; ++h) l[h] *= corr_of(h);
-                } else {
-#pragma unroll
-                    for (int h = 0; h < HPC; ++h) {
-                        const float m_new = fmaxf(m[VQ ? 0 : h], __shfl_sync(0xffffffffu, tm, h));
-                        corr[VQ ? 0 : h] = m[VQ ? 0 : h] > -INFINITY ? exp2f(m[VQ ? 0 : h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
-                        m[VQ ? 0 : h] = m_new;
-                        l[h] *= corr[VQ ? 0 : h];
-                    }
+                for (int h = 0; h < HPC; ++h) {
+                    const float m_new = fmaxf(m[h], __shfl_sync(0xffffffffu, tm, h));
+                    corr[h] = m[h] > -INFINITY ? exp2f(m[h] - m_new) : 1.0f;     // nothing accumulated yet: leave as is
+                    m[h] = m_new;
+                    l[h] *= corr[h];
                 }
-                (void)corr;
                 if (with_v && i > 0) {
-                    if constexpr (VQ) {
-#pragma unroll
-                        for (int g = 0; g < NKV; ++g)
-#pragma unroll
-                            for (int c0 = 0; c0 < NPV; c0 += 16) {   // column n = term * REP + head of the group
-                                uint32_t r[16];
-                                tmem_ld16(tl + TM_O + NPV * g + c0, r);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int c = 0; c < 16; ++c)
-                                    r[c] = __float_as_uint(__uint_as_float(r[c]) * corr_of(g * REP + ((c0 + c) % REP)));
-                                tmem_st16(tl + TM_O + NPV * g + c0, r);
-                            }
-                    } else
 #pragma unroll
                     for (int g = 0; g < NKV; ++g) {
                         // the 16 columns of kv head g are the hi and lo weights of the 8-head group that holds its
@@ -712,49 +847,28 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
-                            r[c] = __float_as_uint(__uint_as_float(r[c]) * corr_of(((g * REP) >> 3) * 8 + (c & 7)));
+                            r[c] = __float_as_uint(__uint_as_float(r[c]) * corr[((g * REP) >> 3) * 8 + (c & 7)]);
                         tmem_st16(tl + TM_O + 16 * g, r);
                     }
                     tmem_st_wait();
                     tc_fence_before_sync();
                 }
             }
+            PKV_WPM(54);                                    // new reference maxima, rescale
             // ---- probabilities relative to the reference maximum; row sums stay per thread
             if (with_v && i >= 2) {
                 ok = wait_all(&X->pv_done[buf], ((i >> 1) - 1) & 1, 43);      // P buffer free again
                 if (!ok) break;
             }
-            float vs[VQ ? NKV : 1];                             // quantised V: this token's scale of every kv head
-            if constexpr (VQ) {
-                ok = wait_all(&X->sc_full[buf], (i >> 1) & 1, 46);
-                if (!ok) break;
-                const uint16_t* sc = reinterpret_cast<const uint16_t*>(smem + C::SC_OFF + buf * VQ_SCALE_BYTES) + row;
-#pragma unroll
-                for (int g = 0; g < NKV; ++g) vs[g] = pkv_bf16_bits_to_float(sc[g * PKV_PAGE_TOKENS]);
-                mbar_arrive(&X->sc_empty[buf]);
-            }
-            (void)vs;
+            PKV_WPM(55);                                    // weight buffer free, scales there
             // weights of token `row`, head h: 8-token group (row / 8) of 1024 bytes = per 8-head group
             // [hi | lo] x (8 heads x 16 bytes), token (row % 8) inside the 16 bytes
             uint8_t* pbuf = smem + C::P_OFF + buf * P_BYTES + (row >> 3) * PGS + (row & 7) * 2;
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
-                const float mh = m_of(h);
+                const float mh = m[h];
                 float p = exp2f(s[h] - (mh > -INFINITY ? mh : 0.0f));                 // exp2(-inf) = 0 for masked rows
-                if constexpr (VQ) {
-                    // p * scale as E5M2 residual terms (each takes the error down by 2^-3; E5M2 is the top byte of the
-                    // half-precision number, so the way back is a shift), rows term * REP + head of the kv head's operand
-                    const int g = h / REP, hh = h % REP;
-                    float res = p > 0.0f ? p * vs[VQ ? g : 0] : 0.0f;      // a masked row's scale may be anything
-                    uint8_t* dst = smem + C::P_OFF + buf * P_BYTES + g * PG8 + (row >> 4) * (NPV * 16) + (row & 15);
-#pragma unroll
-                    for (int t = 0; t < VQ_TERMS; ++t) {
-                        const uint8_t b8 = (uint8_t)__nv_cvt_float_to_fp8(res, __NV_SATFINITE, __NV_E5M2);
-                        res -= __half2float(__ushort_as_half((unsigned short)((unsigned)b8 << 8)));
-                        const int n = t * REP + hh;
-                        dst[(n >> 3) * 128 + (n & 7) * 16] = b8;
-                    }
-                } else if (with_v) {
+                if (with_v) {
                     // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
                     // that value, so numerator and denominator of softmax . V carry the same rounding
                     const __nv_bfloat16 hi = __float2bfloat16(p);
@@ -770,6 +884,8 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 fence_proxy_async_smem();                   // generic-proxy writes -> visible to the tensor core
                 mbar_arrive(&X->p_full[buf]);
             }
+            }
+            PKV_WPM(56);                                    // weights written
         }
         if (warp == W_SM && lane == 0) PKV_TL(11);
         // ---- epilogue: O^T back from TMEM, row sums reduced over the 128 token rows
@@ -817,7 +933,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             float lw = 0.0f, mw = -INFINITY;
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
-                float v = l[h];
+                float v = VQ ? lsm[h * PKV_PAGE_TOKENS] : l[VQ ? 0 : h];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if (lane == h) { lw = v; mw = VQ ? m_lane : m[VQ ? 0 : h]; }
