@@ -38,18 +38,21 @@ constexpr int NK_STAGES = 2, NV_STAGES = 4;
 // per-token scales of a page (one 2 KB block for the CTA's 8 kv heads) have a ring of their own: the softmax folds
 // them into the weights (E5M2, whose exponent range takes any scale), so that P.V runs as kind::f8f6f4 MMAs
 // (K = 32) on exact V operands.
-constexpr int NVR = 4, NVS_Q = 4;
+constexpr int NVR = 8, NVS_Q = 4;                              // a whole page of codes in flight: the raw ring is what hides HBM latency
 constexpr int RAW_BYTES = PKV_PAGE_TOKENS * 64;                // codes of one tile
 constexpr int VQ_STAGE_BYTES = PKV_PAGE_TOKENS * DH;           // the tile as E4M3: one 128-byte row per token
 constexpr int VQ_SCALE_BYTES = 8 * PKV_PAGE_TOKENS * 2;        // bf16 scales of 8 kv heads x 128 tokens
 constexpr int VQ_TERMS = 4;                                    // weights: p * scale as E5M2 terms (2^-11 of the value, any scale
                                                                // whose product with p stays inside half precision)
 constexpr int NK_MAX = 8;              // K stages in scores-only mode (they take over the idle V stages)
+constexpr int NV_BARS = NVS_Q > NV_STAGES ? NVS_Q : NV_STAGES;    // barrier pairs of the V operand stages, whichever instantiation has more
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
 constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
 constexpr int NTHREADS_SCORES = 11 * 32;      // scores only: two softmax groups that take alternate pages
-constexpr int NTHREADS_VQ = 12 * 32;          // quantised V: warps 0-2 as always (3 idle), 4-7 softmax, 8-11 converters
+constexpr int NTHREADS_VQ = 20 * 32;          // quantised V: warps 0-2 as always, 3 second P.V issuer, 4-11 softmax (two groups that split
+                                              // the kv heads), 12-19 converters (two per tile). Each role's chain of dependent instructions
+                                              // is what bounds a page, so the roles are spread over as many warps as the layout allows
 template <bool WV, bool VQ> constexpr int n_threads() { return VQ ? NTHREADS_VQ : (WV ? NTHREADS : NTHREADS_SCORES); }
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
 constexpr uint32_t WAIT_LIMIT = 1u << 19;     // probes of a bounded wait (a probe may itself block for microseconds): a second or two, then give up
@@ -63,11 +66,13 @@ constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residua
 constexpr uint32_t TM_O = 256;        // with V only (then NSB = 2): n_kv x 16 O^T accumulators, 8 hi + 8 lo weight columns
 constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set per score buffer
 constexpr uint32_t TM_SFB = 432;      // 16 per MMA issuer (two in scores-only mode): query scale factors, a 4-column group per K step
+constexpr uint32_t TM_L = 464;        // quantised V: 32 columns of row sums (lane = token row, column = head), the softmax threads' own scratch
 constexpr uint32_t TM_COLS = 512;
 
 template <int WP, bool VQ = false>
 struct Cfg {
     static constexpr int NVS = VQ ? NVS_Q : NV_STAGES;           // V operand stages
+    static_assert(NVS <= NV_BARS, "every operand stage has its barrier pair");
     static constexpr int VSB = VQ ? VQ_STAGE_BYTES : V_STAGE_BYTES;
     static constexpr int RB = WP / 2;                          // code bytes per row
     static constexpr int KB = WP / 64;                         // K = 64 MMA steps
@@ -79,8 +84,7 @@ struct Cfg {
     static constexpr int V_OFF = K_OFF + NK_STAGES * PAGE;
     static constexpr int R_OFF = V_OFF + NVS * VSB;              // raw tiles of quantised V pages
     static constexpr int SC_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);      // their scale blocks, two pages
-    static constexpr int L_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);   // row sums of the softmax: [head][token row] fp32
-    static constexpr int P_OFF = L_OFF + (VQ ? NQ * PKV_PAGE_TOKENS * 4 : 0);
+    static constexpr int P_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
     static constexpr int SMEM = X_OFF + 4096;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
@@ -88,13 +92,13 @@ struct Cfg {
 };
 
 struct Extra {                       // lives at X_OFF
-    uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NVS_Q], v_empty[NVS_Q];
+    uint64_t q_full, k_full[NK_MAX], k_empty[NK_MAX], v_full[NV_BARS], v_empty[NV_BARS];
     uint64_t s_full[NSB_S], s_empty[NSB_S], p_full[2], pv_done[2];
     uint64_t vr_full[NVR], vr_empty[NVR];                        // raw tiles of quantised V pages
     // Quantised V: the operand stages are filled by four converter warps and drained by two MMA issuers (tiles of
     // even / odd kv heads). A parity wait only tells neighbouring phases apart, so a barrier must be waited for by
-    // one thread, phase after phase: tile j uses operand stage and raw stage j % 4 (an even number of stages: a stage
-    // always serves the same issuer, and always the same converter warp).
+    // one thread (or warps in lockstep), phase after phase, never every other phase: tile j uses operand stage j % 4 (an
+    // even number: a stage always serves the same issuer) and raw stage j % 8, both always with the converter pair j % 4.
     uint64_t sc_full[2], sc_empty[2];                            // scale blocks of quantised V pages
 #ifdef PKV_WAITPROF
     unsigned long long waited[64];
@@ -103,7 +107,7 @@ struct Extra {                       // lives at X_OFF
     uint32_t tmem_base;
     volatile int abort_flag;
     float wmax[2][4][NQ];
-    int wflag[2][4];
+    int wflag[2][8];
     float lsum[2][4][NQ];            // [softmax group][warp][head]
     float mfin[2][4][NQ];
 };
@@ -207,12 +211,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #endif
         mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
         for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
-        for (int s = 0; s < NVS_Q; ++s) { mbar_init(&X->v_full[s], 1); mbar_init(&X->v_empty[s], 1); }
-        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 128); }
-        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], 128); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }   // quantised V: two P.V issuers
-        mbar_init(&X->sm_bar, WV ? 128 : 256);
+        // quantised V: two converter warps per tile, 256 softmax threads, two P.V issuers
+        for (int s = 0; s < NV_BARS; ++s) { mbar_init(&X->v_full[s], VQ ? 2 : 1); mbar_init(&X->v_empty[s], 1); }
+        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 2); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 256); }
+        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], VQ ? 256 : 128); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], VQ ? 256 : 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }
+        mbar_init(&X->sm_bar, WV && !VQ ? 128 : 256);
         X->abort_flag = 0;
         fence_barrier_init();
     }
@@ -348,36 +353,52 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // ================================================================== V producer
         {
             if (lane == 0) { tma_prefetch_desc(&vmap); if (VQ) tma_prefetch_desc(&smap); }
-            int issued = 0, sc_issued = 0;
+            int issued = 0;
             bool stop = false, waited = !(early && tail_written);
             for (int base = 0; base < P && !stop; base += 32) {
                 const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
                 for (int jj = 0; jj < 32 && base + jj < P && !stop; ++jj) {
                     const int i = base + jj;
                     const int pidx = __shfl_sync(0xffffffffu, mine, jj);
+                    if constexpr (VQ) {
+                        // Quantised pages: a lane's chain of wait, arm and copy takes ~0.4 us per tile, too long for eight tiles
+                        // of a page that lasts 2 us. Lanes 0 .. 7 therefore work side by side, lane s on the tiles of raw
+                        // stage s (tile j = page * NKV + kv head, stage j % 8), lane 8 on the page's scale block.
+                        static_assert(NVR == 8 && (NKV == 4 || NKV == 8), "a lane per raw stage");
+                        if (pidx < 0 || pidx >= n_pages_pool) {
+                            stop = true;                             // the K producer reports it
+                        } else {
+                            if (!waited && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
+                            if (lane == NVR) {                       // 8 kv heads x 128 bf16
+                                const int ss = i & 1;
+                                if (i >= 2 && !wait_or_abort(&X->sc_empty[ss], ((i >> 1) - 1) & 1, X, status, 22)) stop = true;
+                                if (!stop) {
+                                    mbar_arrive_expect_tx(&X->sc_full[ss], VQ_SCALE_BYTES);
+                                    tma_load_2d(smem + C::SC_OFF + ss * VQ_SCALE_BYTES, &smap, 0,
+                                                pidx * VQ_PAGE_ROWS + (NQ / REP) * VQ_TILE_ROWS + g_base * 2, &X->sc_full[ss]);
+                                    issued = i + 1;
+                                }
+                            } else if (lane < NVR) {
+                                for (int g = 0; g < NKV && !stop; ++g) {
+                                    const int j = i * NKV + g;                     // the codes of (page, kv head) as stored
+                                    if (j % NVR != lane) continue;
+                                    if (j >= NVR && !wait_or_abort(&X->vr_empty[lane], ((j / NVR) - 1) & 1, X, status, 21)) { stop = true; break; }
+                                    mbar_arrive_expect_tx(&X->vr_full[lane], RAW_BYTES);
+                                    tma_load_2d(smem + C::R_OFF + lane * RAW_BYTES, &vmap, 0, pidx * VQ_PAGE_ROWS + (g_base + g) * VQ_TILE_ROWS,
+                                                &X->vr_full[lane]);
+                                    issued = j + 1;
+                                }
+                            }
+                        }
+                        stop = __any_sync(0xffffffffu, stop);
+                        continue;
+                    }
                     if (lane == 0) {
                         if (pidx < 0 || pidx >= n_pages_pool) {
                             stop = true;                             // the K producer reports it
                         } else {
                             if (!waited && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
                             for (int g = 0; g < NKV; ++g) {
-                                if constexpr (VQ) {
-                                    if (g == 0) {                    // the page's scale block first: 8 kv heads x 128 bf16
-                                        const int ss = i & 1;
-                                        if (i >= 2 && !wait_or_abort(&X->sc_empty[ss], ((i >> 1) - 1) & 1, X, status, 22)) { stop = true; break; }
-                                        mbar_arrive_expect_tx(&X->sc_full[ss], VQ_SCALE_BYTES);
-                                        tma_load_2d(smem + C::SC_OFF + ss * VQ_SCALE_BYTES, &smap, 0,
-                                                    pidx * VQ_PAGE_ROWS + (NQ / REP) * VQ_TILE_ROWS + g_base * 2, &X->sc_full[ss]);
-                                        sc_issued = i + 1;
-                                    }
-                                    const int j = i * NKV + g, s = j % NVR;        // the codes of (page, kv head) as stored
-                                    if (j >= NVR && !wait_or_abort(&X->vr_empty[s], ((j / NVR) - 1) & 1, X, status, 21)) { stop = true; break; }
-                                    mbar_arrive_expect_tx(&X->vr_full[s], RAW_BYTES);
-                                    tma_load_2d(smem + C::R_OFF + s * RAW_BYTES, &vmap, 0, pidx * VQ_PAGE_ROWS + (g_base + g) * VQ_TILE_ROWS,
-                                                &X->vr_full[s]);
-                                    issued = j + 1;
-                                    continue;
-                                }
                                 const int j = i * NKV + g, s = j % NV_STAGES;
                                 if (j >= NV_STAGES && !wait_or_abort(&X->v_empty[s], ((j / NV_STAGES) - 1) & 1, X, status, 20)) { stop = true; break; }
                                 uint8_t* dst = smem + C::V_OFF + s * V_STAGE_BYTES;
@@ -391,11 +412,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                     stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
                 }
             }
-            if (lane == 0 && X->abort_flag) {
+            if (X->abort_flag) {                                     // let copies in flight land before leaving
                 if constexpr (VQ) {
-                    for (int j = max(0, issued - NVR); j < issued; ++j) mbar_wait(&X->vr_full[j % NVR], (j / NVR) & 1, 1u << 16);
-                    for (int j = max(0, sc_issued - 2); j < sc_issued; ++j) mbar_wait(&X->sc_full[j & 1], (j >> 1) & 1, 1u << 16);
-                } else {
+                    // `issued` is the lane's own: one past its last tile (lanes 0 .. 7), one past its last page (lane 8)
+                    if (lane < NVR && issued > 0) mbar_wait(&X->vr_full[lane], ((issued - 1) / NVR) & 1, 1u << 16);
+                    if (lane == NVR)
+                        for (int j = max(0, issued - 2); j < issued; ++j) mbar_wait(&X->sc_full[j & 1], (j >> 1) & 1, 1u << 16);
+                } else if (lane == 0) {
                     for (int j = max(0, issued - NV_STAGES); j < issued; ++j)
                         mbar_wait(&X->v_full[j % NV_STAGES], (j / NV_STAGES) & 1, 1u << 16);
                 }
@@ -506,13 +529,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             }
             if (ok && with_v && !pv_only) do_pv(P - 1);
         }
-    } else if (VQ && warp >= 8) {
+    } else if (VQ && warp >= 12) {
         // ================================================================== V converter (quantised V pages)
         // A token's 64 bytes of E2M1 codes become 128 E4M3 bytes (exactly the same numbers) in the 128-byte-swizzled
         // MN-major layout the P.V descriptors expect; the token's scale is not applied here but folded into the weights.
-        // Each converter warp owns every fourth tile (a lane takes four token rows of it), so that four tiles are in
+        // Two converter warps share every fourth tile (a lane takes two token rows of it), so that four tiles are in
         // work at once and the waits of one hide behind the arithmetic of the others.
-        const int cw = warp - 8;
+        const int cw = (warp - 12) & 3, half = (warp - 12) >> 2;
         // E4M3 bytes of the eight E2M1 magnitudes 0 .5 1 1.5 2 3 4 6 (00 30 38 3C 40 44 48 4C) as byte tables for prmt
         constexpr uint32_t LUT_A = 0x3C383000u, LUT_B = 0x4C484440u;
         auto prmt = [](uint32_t a, uint32_t b, uint32_t c) -> uint32_t {
@@ -536,7 +559,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             // (a compact loop on purpose: unrolled, this code and the softmax loop no longer fit the instruction cache
             // together, and both then run at the speed of instruction fetch)
 #pragma unroll 1
-            for (int rg = 0; rg < 4; ++rg) {
+            for (int rg = 2 * half; rg < 2 * half + 2; ++rg) {
                 const int r = rg * 32 + lane;
                 const uint32_t sw = ((uint32_t)r >> 1) & 3u;
                 uint8_t* dst = stage + r * 128;
@@ -571,6 +594,10 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // ================================================================== softmax (128 threads, one token row each)
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
         const int sg = VQ ? 0 : (warp - 3) >> 2;            // softmax group: pages sg, sg + SG, ...
+        const int hg = VQ ? (warp - 4) >> 2 : 0;            // quantised V: group hg takes kv heads hg * NKV / 2 .. of every page
+        constexpr int GPG = VQ ? NKV / 2 : NKV;             // kv heads per group
+        const int g_lo = hg * GPG, g_hi = g_lo + GPG;
+        (void)hg; (void)g_lo; (void)g_hi;
         (void)W_SM;
         const int row = quad * 32 + lane;
         const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
@@ -580,7 +607,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             return __all_sync(0xffffffffu, wait_or_abort(bar, parity, X, status, where));
         };
         int sync_phase = 0;
-        auto softmax_sync = [&]() -> bool {                 // all 128 softmax threads meet here
+        auto softmax_sync = [&]() -> bool {                 // all softmax threads meet here
             mbar_arrive(&X->sm_bar);
             return wait_all(&X->sm_bar, (sync_phase++) & 1, 45);
         };
@@ -590,12 +617,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // (With quantised V the loops over the heads are not unrolled, so nothing per head can live in a register
         // array: the column scales stay in shared memory, where the query operand's tail holds them, and are read
         // as broadcasts; the reference maxima, identical in every lane, are kept one per lane -- lane h holds head
-        // h's -- and fetched by shuffle, so are the rescale factors; the row sums have a shared-memory array.)
+        // h's -- and fetched by shuffle, so are the rescale factors; the row sums live in spare tensor-memory columns,
+        // which a thread can index at run time.)
         float cs[VQ ? 1 : HPC], m[VQ ? 1 : HPC], l[VQ ? 1 : HPC];
         float m_lane = -INFINITY;
-        float* const lsm = reinterpret_cast<float*>(smem + C::L_OFF) + row;       // [head][token row]
+        const uint32_t l_tm = tl + TM_L;                    // row sums: tensor-memory columns, one per head, this thread's lane
         auto m_of = [&](int h) -> float { return __shfl_sync(0xffffffffu, m_lane, h); };
-        (void)lsm; (void)m_of; (void)m_lane;
+        (void)l_tm; (void)m_of; (void)m_lane;
         if constexpr (INLQ) if (sg == 0) {
             // the query may come from the launch before this one unless the caller says it was ready earlier
             if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
@@ -605,8 +633,10 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         }
         bool ok = wait_all(&X->q_full, 0, 40);
         if constexpr (VQ) {
+            const uint32_t zero[REP] = {};
 #pragma unroll 1
-            for (int h = 0; h < HPC; ++h) lsm[h * PKV_PAGE_TOKENS] = 0.0f;
+            for (int g = g_lo; g < g_hi; ++g) tmem_stn<REP>(l_tm + g * REP, zero);
+            tmem_st_wait();
         } else {
 #pragma unroll
             for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
@@ -648,7 +678,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 // ---- does any head of any row outgrow its reference maximum by more than the threshold?
                 float exc = -INFINITY;
 #pragma unroll 1
-                for (int g = 0; g < NKV; ++g) {
+                for (int g = g_lo; g < g_hi; ++g) {
                     float sv[REP];
                     load_scores(g, sv);
 #pragma unroll
@@ -656,15 +686,16 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 }
                 PKV_WPM(52);
                 bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
-                if (lane == 0) X->wflag[buf][quad] = grow ? 1 : 0;
+                if (lane == 0) X->wflag[buf][hg * 4 + quad] = grow ? 1 : 0;
                 ok = softmax_sync();
                 if (!ok) break;
-                grow = (X->wflag[buf][0] | X->wflag[buf][1] | X->wflag[buf][2] | X->wflag[buf][3]) != 0;
+                grow = (X->wflag[buf][0] | X->wflag[buf][1] | X->wflag[buf][2] | X->wflag[buf][3] | X->wflag[buf][4] | X->wflag[buf][5] |
+                        X->wflag[buf][6] | X->wflag[buf][7]) != 0;
                 PKV_WPM(53);
                 if (grow) {
-                    float wm = -INFINITY;                   // lane h: the tile maximum of head h
+                    float wm = -INFINITY;                   // lane h: the tile maximum of head h (this group's heads)
 #pragma unroll 1
-                    for (int g = 0; g < NKV; ++g) {
+                    for (int g = g_lo; g < g_hi; ++g) {
                         float sv[REP];
                         load_scores(g, sv);
 #pragma unroll
@@ -673,7 +704,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                             if (lane == g * REP + hh) wm = ord2f(red);
                         }
                     }
-                    X->wmax[buf][quad][lane] = wm;
+                    if (lane >= g_lo * REP && lane < g_hi * REP) X->wmax[buf][quad][lane] = wm;
                     ok = softmax_sync();
                     if (!ok) break;
                     const float tm = fmaxf(fmaxf(X->wmax[buf][0][lane], X->wmax[buf][1][lane]),
@@ -687,10 +718,18 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                     const float corr_lane = m_lane > -INFINITY ? exp2f(m_lane - m_new) : 1.0f;     // nothing accumulated yet: leave as is
                     m_lane = m_new;
 #pragma unroll 1
-                    for (int h = 0; h < HPC; ++h) lsm[h * PKV_PAGE_TOKENS] *= __shfl_sync(0xffffffffu, corr_lane, h);
+                    for (int g = g_lo; g < g_hi; ++g) {
+                        uint32_t lr[REP];
+                        tmem_ldn<REP>(l_tm + g * REP, lr);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int hh = 0; hh < REP; ++hh) lr[hh] = __float_as_uint(__uint_as_float(lr[hh]) * __shfl_sync(0xffffffffu, corr_lane, g * REP + hh));
+                        tmem_stn<REP>(l_tm + g * REP, lr);
+                    }
+                    tmem_st_wait();
                     if (i > 0) {
 #pragma unroll 1
-                        for (int g = 0; g < NKV; ++g)
+                        for (int g = g_lo; g < g_hi; ++g)
 #pragma unroll 1
                             for (int c0 = 0; c0 < NPV; c0 += 16) {   // column n = term * REP + head of the group
                                 uint32_t r[16];
@@ -720,8 +759,10 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 const uint16_t* sc = reinterpret_cast<const uint16_t*>(smem + C::SC_OFF + buf * VQ_SCALE_BYTES) + row;
                 uint8_t* pdst = smem + C::P_OFF + buf * P_BYTES + row * 16;
 #pragma unroll 1
-                for (int g = 0; g < NKV; ++g) {
+                for (int g = g_lo; g < g_hi; ++g) {
                     float sv[REP], pw[REP];
+                    uint32_t lr[REP];
+                    tmem_ldn<REP>(l_tm + g * REP, lr);        // (waited for together with the scores)
                     load_scores(g, sv);
                     const float vsg = pkv_bf16_bits_to_float(sc[g * PKV_PAGE_TOKENS]);
 #pragma unroll
@@ -731,8 +772,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         const float mh = m_of(h);
                         const float p = exp2f(sv[hh] - (mh > -INFINITY ? mh : 0.0f));     // exp2(-inf) = 0 for masked rows
                         pw[hh] = p > 0.0f ? fminf(p * vsg, 57344.0f) : 0.0f;            // a masked row's scale may be anything
-                        lsm[h * PKV_PAGE_TOKENS] += p;
+                        lr[hh] = __float_as_uint(__uint_as_float(lr[hh]) + p);
                     }
+                    tmem_stn<REP>(l_tm + g * REP, lr);
                     constexpr int NP = (REP + 1) / 2, NW = (REP + 3) / 4;
                     uint32_t x[NP], wd[VQ_TERMS][NW];
 #pragma unroll
@@ -764,6 +806,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         dst[0] = make_uint4((wd[0][0] & 0xFFu) | ((wd[1][0] & 0xFFu) << 8) | ((wd[2][0] & 0xFFu) << 16) | (wd[3][0] << 24), 0u, 0u, 0u);
                     }
                 }
+                tmem_st_wait();                             // the row sums are read again with the next page
                 mbar_arrive(&X->sc_empty[buf]);
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
@@ -897,8 +940,8 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         if (ok) {
             tc_fence_after_sync();
             if constexpr (VQ) {
-#pragma unroll
-                for (int g = 0; g < NKV; ++g) {                 // columns term * REP + head: the three terms of a head add up
+#pragma unroll 1
+                for (int g = g_lo; g < g_hi; ++g) {             // columns term * REP + head: the terms of a head add up
                     float acc[REP];
 #pragma unroll
                     for (int c = 0; c < REP; ++c) acc[c] = 0.0f;
@@ -931,16 +974,36 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                     for (int h = 0; h < NQ; ++h) part[h * (DH + 2) + row] = 0.0f;
             }
             float lw = 0.0f, mw = -INFINITY;
+            if constexpr (VQ) {
+#pragma unroll 1
+                for (int g = g_lo; g < g_hi; ++g) {
+                    uint32_t lr[REP];
+                    tmem_ldn<REP>(l_tm + g * REP, lr);
+                    tmem_ld_wait();
 #pragma unroll
-            for (int h = 0; h < HPC; ++h) {
-                float v = VQ ? lsm[h * PKV_PAGE_TOKENS] : l[VQ ? 0 : h];
+                    for (int hh = 0; hh < REP; ++hh) {
+                        float v = __uint_as_float(lr[hh]);
 #pragma unroll
-                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == h) { lw = v; mw = VQ ? m_lane : m[VQ ? 0 : h]; }
+                        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                        if (lane == g * REP + hh) { lw = v; mw = m_lane; }
+                    }
+                }
+                if (lane >= g_lo * REP && lane < g_hi * REP) {  // a head's sums come from the group that owns it
+                    X->lsum[0][quad][lane] = lw;
+                    X->mfin[0][quad][lane] = mw;
+                }
+            } else {
+#pragma unroll
+                for (int h = 0; h < HPC; ++h) {
+                    float v = l[VQ ? 0 : h];
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == h) { lw = v; mw = m[VQ ? 0 : h]; }
+                }
+                X->lsum[sg][quad][lane] = lw;
+                X->mfin[sg][quad][lane] = mw;               // per warp in scores-only mode, identical otherwise
             }
-            X->lsum[sg][quad][lane] = lw;
-            X->mfin[sg][quad][lane] = mw;                   // per warp in scores-only mode, identical otherwise
-            if (softmax_sync() && quad == 0 && sg == 0 && lane < HPC) {
+            if (softmax_sync() && quad == 0 && sg == 0 && hg == 0 && lane < HPC) {
                 float M = -INFINITY, lt = 0.0f;
 #pragma unroll
                 for (int w = 0; w < 4 * SG; ++w) M = fmaxf(M, X->mfin[w >> 2][w & 3][lane]);
