@@ -283,71 +283,77 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // 32 pages) and handed to lane 0 by shuffle: a dependent global load per page would cap the producer
         // at one page per memory latency.
         if (lane == 0) { tma_prefetch_desc(&kmap); tma_prefetch_desc(&qmap); }
-        int issued = 0;
+        // A lane's chain of wait, arm and copy costs ~0.4 - 0.7 us per page: as much as a page lasts in scores-only mode.
+        // So lane s takes the pages of stage s (page i, stage i % nks) and the lanes work side by side, round after
+        // round; lane 0 also fetches the query operand -- at once, or in early mode after the first round, so that the
+        // stages fill while the launch before this one still runs.
+        static_assert(32 % nks == 0, "a round of pages lies inside one fetch of 32 page indices");
+        int issued = -1;                                             // the lane's own last page
         bool q_sent = inline_q, stop = false, waited = !early;
-        for (int base = 0; base <= P && !stop; base += 32) {
-            const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
-            for (int jj = 0; jj < 32 && base + jj <= P && !stop; ++jj) {
-                const int i = base + jj;
-                const int pidx = __shfl_sync(0xffffffffu, mine, jj);
-                if (lane == 0) {
-                    // early mode: first fill the latent stages (but never with a page that is still being written)
-                    if (!q_sent && (!early || i == min(P, nks) || (tail_written && p_lo + i == npages - 1))) {
-                        if (qa.qsync && early) {
-                            // the launch before signals each sequence's operand as soon as it is in place (it may
-                            // still be busy with other work, e.g. the cache write of the newest token): poll
-                            // the counter instead of waiting for that whole grid
-                            const int need = (NQ + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
-                            bool there = false;
-                            for (uint32_t it = 0; it < WAIT_LIMIT && !there; ++it) {    // about half a second, then give up
-                                int v;
-                                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(qa.qsync + b) : "memory");
-                                there = v >= need;
-                                if (!there) {
-                                    if ((it & 63u) == 63u && X->abort_flag) break;
-                                    __nanosleep(40);
-                                }
-                            }
-                            if (!there) {
-                                if (!X->abort_flag && status) { atomicExch(&status[0], 1); atomicExch(&status[1], 11); }
-                                X->abort_flag = 1;
-                                stop = true;
-                            }
-                            asm volatile("fence.proxy.async;" ::: "memory");    // the operand was written by ordinary stores, the tile load reads it
-                        } else if (!waited) { pkv_grid_wait(); waited = true; }
-                        if (!stop) {
-                        mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
-                        tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
-                        q_sent = true;
-                        PKV_TL(5);
-                        }
-                    }
-                    if (!waited && tail_written && i < P && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
-                    if (i < P && !stop) {
-                        const int s = i % nks;
-                        if (i >= nks && !wait_or_abort(&X->k_empty[s], ((i / nks) - 1) & 1, X, status, 10)) {
-                            stop = true;
-                        } else if (pidx < 0 || pidx >= n_pages_pool) {   // never dereference a bad page index
-                            X->abort_flag = 1;
-                            if (status) { atomicExch(&status[0], 2); atomicExch(&status[1], p_lo + i); }
-                            stop = true;
-                        } else {
-                            mbar_arrive_expect_tx(&X->k_full[s], C::PAGE);
-                            // one tensor tile of PAGE/128 rows x 128 bytes (plain bulk copies of this size were
-                            // measured at ~16 GB/s per SM, tiled loads are not limited that way)
-                            tma_load_2d(smem + C::K_OFF + s * C::PAGE, &kmap, 0, pidx * (C::PAGE / 128), &X->k_full[s]);
-                            issued = i + 1;
-                            if (i == 0) PKV_TL(4);
-                            if (i == P - 1) PKV_TL(6);
-                        }
+        auto send_query = [&]() {                                    // lane 0
+            if (qa.qsync && early) {
+                // the launch before signals each sequence's operand as soon as it is in place (it may
+                // still be busy with other work, e.g. the cache write of the newest token): poll
+                // the counter instead of waiting for that whole grid
+                const int need = (NQ + pkv_absorb_impl::HG - 1) / pkv_absorb_impl::HG;
+                bool there = false;
+                for (uint32_t it = 0; it < WAIT_LIMIT && !there; ++it) {    // about half a second, then give up
+                    int v;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(qa.qsync + b) : "memory");
+                    there = v >= need;
+                    if (!there) {
+                        if ((it & 63u) == 63u && X->abort_flag) break;
+                        __nanosleep(40);
                     }
                 }
-                stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
+                if (!there) {
+                    if (!X->abort_flag && status) { atomicExch(&status[0], 1); atomicExch(&status[1], 11); }
+                    X->abort_flag = 1;
+                    stop = true;
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");    // the operand was written by ordinary stores, the tile load reads it
+            } else if (!waited) { pkv_grid_wait(); waited = true; }
+            if (!stop) {
+                mbar_arrive_expect_tx(&X->q_full, C::QBLOB);
+                tma_load_2d(smem + C::Q_OFF, &qmap, 0, b * (C::QBLOB / 128), &X->q_full);
+                PKV_TL(5);
+            }
+            q_sent = true;
+        };
+        if (lane == 0 && !q_sent && !early) send_query();
+        stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
+        for (int base = 0; base < P && !stop; base += 32) {
+            const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
+            for (int r0 = 0; r0 < 32 && base + r0 < P && !stop; r0 += nks) {
+                const int i = base + r0 + lane;                      // this lane's page of the round
+                const int pidx = __shfl_sync(0xffffffffu, mine, (r0 + lane) & 31);
+                if (lane < nks && i < P) {
+                    // a page that the launch before this one still writes (the newest token's) waits for that launch
+                    if (!waited && tail_written && p_lo + i == npages - 1) { pkv_grid_wait(); waited = true; }
+                    if (i >= nks && !wait_or_abort(&X->k_empty[lane], ((i / nks) - 1) & 1, X, status, 10)) {
+                        stop = true;
+                    } else if (pidx < 0 || pidx >= n_pages_pool) {   // never dereference a bad page index
+                        X->abort_flag = 1;
+                        if (status) { atomicExch(&status[0], 2); atomicExch(&status[1], p_lo + i); }
+                        stop = true;
+                    } else {
+                        mbar_arrive_expect_tx(&X->k_full[lane], C::PAGE);
+                        // one tensor tile of PAGE/128 rows x 128 bytes (plain bulk copies of this size were
+                        // measured at ~16 GB/s per SM, tiled loads are not limited that way)
+                        tma_load_2d(smem + C::K_OFF + lane * C::PAGE, &kmap, 0, pidx * (C::PAGE / 128), &X->k_full[lane]);
+                        issued = i;
+                        if (i == 0) PKV_TL(4);
+                        if (i == P - 1) PKV_TL(6);
+                    }
+                }
+                if (lane == 0 && !q_sent && !stop) send_query();     // early mode: the first round of pages is on its way
+                stop = __any_sync(0xffffffffu, stop);
             }
         }
-        if (lane == 0 && X->abort_flag) {                            // let copies in flight land before leaving
-            if (q_sent) mbar_wait(&X->q_full, 0, 1u << 16);
-            for (int i = max(0, issued - nks); i < issued; ++i) mbar_wait(&X->k_full[i % nks], (i / nks) & 1, 1u << 16);
+        if (lane == 0 && !q_sent && !stop) send_query();             // (no page at all)
+        if (X->abort_flag) {                                         // let copies in flight land before leaving
+            if (lane == 0 && q_sent && !inline_q) mbar_wait(&X->q_full, 0, 1u << 16);
+            if (lane < nks && issued >= 0) mbar_wait(&X->k_full[lane], (issued / nks) & 1, 1u << 16);
         }
     } else if (warp == 1 && WV) {
         // ================================================================== V producer
