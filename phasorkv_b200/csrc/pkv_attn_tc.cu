@@ -49,7 +49,8 @@ constexpr int NV_BARS = NVS_Q > NV_STAGES ? NVS_Q : NV_STAGES;    // barrier pai
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
 constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
-constexpr int NTHREADS_SCORES = 11 * 32;      // scores only: two softmax groups that take alternate pages
+constexpr int NTHREADS_SCORES = 16 * 32;      // scores only: K producer, three MMA issuers, three softmax groups; page i belongs to
+                                              // issuer, score buffer and group i % 3
 constexpr int NTHREADS_VQ = 20 * 32;          // quantised V: warps 0-2 as always, 3 second P.V issuer, 4-11 softmax (two groups that split
                                               // the kv heads), 12-19 converters (two per tile). Each role's chain of dependent instructions
                                               // is what bounds a page, so the roles are spread over as many warps as the layout allows
@@ -61,11 +62,11 @@ constexpr uint32_t WAIT_LIMIT = 1u << 19;     // probes of a bounded wait (a pro
 // Score buffers (pages in flight between MMA and softmax): two. In scores-only mode buffer = page parity, so
 // each MMA issuer shares its buffer and barriers with exactly one softmax group (a barrier whose phases are
 // waited for by two threads in turn could be seen a whole phase early by the one that runs ahead).
-constexpr int NSB_V = 2, NSB_S = 2;
+constexpr int NSB_V = 2, NSB_S = 3;
 constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residual terms x 32 heads)
 constexpr uint32_t TM_O = 256;        // with V only (then NSB = 2): n_kv x 16 O^T accumulators, 8 hi + 8 lo weight columns
 constexpr uint32_t TM_SFA = 384;      // NSB x 16 : cache scale factors, one set per score buffer
-constexpr uint32_t TM_SFB = 432;      // 16 per MMA issuer (two in scores-only mode): query scale factors, a 4-column group per K step
+constexpr uint32_t TM_SFB = 432;      // 16 per MMA issuer (three in scores-only mode): query scale factors, a 4-column group per K step
 constexpr uint32_t TM_L = 464;        // quantised V: 32 columns of row sums (lane = token row, column = head), the softmax threads' own scratch
 constexpr uint32_t TM_COLS = 512;
 
@@ -86,7 +87,7 @@ struct Cfg {
     static constexpr int SC_OFF = R_OFF + (VQ ? NVR * RAW_BYTES : 0);      // their scale blocks, two pages
     static constexpr int P_OFF = SC_OFF + (VQ ? 2 * VQ_SCALE_BYTES : 0);
     static constexpr int X_OFF = P_OFF + 2 * P_BYTES;          // barriers and small arrays
-    static constexpr int SMEM = X_OFF + 4096;
+    static constexpr int SMEM = X_OFF + 6144;
     static constexpr uint64_t SWZ = RB == 128 ? SWZ_128B : SWZ_64B;
     static constexpr uint32_t SBO = 8 * RB;
 };
@@ -108,11 +109,12 @@ struct Extra {                       // lives at X_OFF
     volatile int abort_flag;
     float wmax[2][4][NQ];
     int wflag[2][8];
-    float lsum[2][4][NQ];            // [softmax group][warp][head]
-    float mfin[2][4][NQ];
+    float lsum[NSB_S][4][NQ];        // [softmax group][warp][head]
+    float mfin[NSB_S][4][NQ];
 };
 
-static_assert(sizeof(Extra) <= 4096, "barriers and exchange arrays must fit behind the stages");
+constexpr int X_BYTES = 6144;
+static_assert(sizeof(Extra) <= X_BYTES, "barriers and exchange arrays must fit behind the stages");
 static_assert(Cfg<256, true>::SMEM <= 232448 && Cfg<256, false>::SMEM <= 232448, "shared memory of one CTA");
 static_assert(Cfg<256, true>::V_OFF % 1024 == 0 && VQ_STAGE_BYTES % 1024 == 0, "swizzled operand stages start on 1024 bytes");
 
@@ -121,6 +123,14 @@ __device__ __forceinline__ uint32_t f2ord(float f) { uint32_t b = __float_as_uin
 __device__ __forceinline__ float ord2f(uint32_t u) { return __uint_as_float(u ^ ((u >> 31) ? 0x80000000u : 0xFFFFFFFFu)); }
 
 // bounded wait that also gives up when another role has already given up
+// 2^x by the special-function unit alone (2 ulp; results below 2^-126 become 0): the weights of a softmax need no more,
+// and exp2f() wraps the same instruction in a range reduction of its own
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Build with -DPKV_WAITPROF to turn `scores_out` into a table of 64 counters per CTA: the cycles lane 0 of each
 // warp spent in the wait with code `where` (entry 0: the CTA's cycles from entry to exit). The role that waits
 // least is the one that bounds the kernel. A development aid; the library is never shipped with it.
@@ -217,7 +227,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 256); }
         for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], VQ ? 256 : 128); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], VQ ? 256 : 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }
-        mbar_init(&X->sm_bar, WV && !VQ ? 128 : 256);
+        mbar_init(&X->sm_bar, WV ? (VQ ? 256 : 128) : 128 * NSB_S);
         X->abort_flag = 0;
         fence_barrier_init();
     }
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
     const int P = p_hi - p_lo;
     constexpr bool with_v = WV;                      // scores-only launches are a separate instantiation
-    constexpr int SG = WV ? 1 : 2;                   // softmax groups
+    constexpr int SG = WV ? 1 : NSB_S;               // softmax groups
     constexpr int NSB = WV ? NSB_V : NSB_S;
     constexpr int nks = WV ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
@@ -276,7 +286,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         return;
     }
 
-    constexpr int W_SM = VQ ? 4 : 3;                  // first softmax warp
+    constexpr int W_SM = (VQ || !WV) ? 4 : 3;         // first softmax warp
     if (warp == 0) {
         // ================================================================== K producer
         // The page indices are fetched 32 at a time by the whole warp (one coalesced load, one round trip per
@@ -430,20 +440,21 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 }
             }
         }
-    } else if (warp == 2 || warp == 1 || (VQ && warp == 3)) {
+    } else if (warp == 2 || warp == 1 || ((VQ || !WV) && warp == 3)) {
         // ================================================================== MMA issuer
         // One thread issues every tcgen05 instruction of its pages; what bounds it is the latency of its own
         // instruction chain (two satisfied barrier waits, 4 + 4 tcgen05 issues of ~75 cycles, two commits:
-        // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V it is the longest
-        // link, so the warp the V stream leaves idle becomes a second issuer: warp 2 takes the even pages,
-        // warp 1 the odd ones (each feeds the softmax group of its parity).
+        // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V the chains of issuer and
+        // softmax are what a page costs, so there are three of each: warp 2 takes the pages 0, 3, 6 .., warp 1 (which the
+        // V stream leaves idle) 1, 4, 7 .., warp 3 the rest; each feeds the softmax group of the same number through a
+        // score buffer of its own.
         // With quantised V a page's bytes last a third as long, and the P.V issue chain (8 MMAs, a wait and a commit per
         // kv head) becomes the longest link: warp 3 then issues the P.V of the odd kv heads, warp 2 scores + even heads.
         constexpr int PV_STEP = VQ ? 2 : 1;
         if (lane == 0) {
-            const int first = (!WV && warp == 1) ? 1 : 0;
-            constexpr int STEP = WV ? 1 : 2;
-            const uint32_t sfb_tm = tb + TM_SFB + (first ? 16u : 0u);
+            const int first = WV ? 0 : (warp == 2 ? 0 : (warp == 1 ? 1 : 2));
+            constexpr int STEP = WV ? 1 : NSB_S;
+            const uint32_t sfb_tm = tb + TM_SFB + 16u * (uint32_t)first;
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
             constexpr uint32_t idesc_o = VQ ? idesc_f8(128, NPV, true, true, 0u, 1u) : idesc_bf16(128, 16, true, false);   // V: E4M3, weights: E5M2
             const bool pv_only = VQ && warp == 3;
@@ -599,7 +610,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     } else {
         // ================================================================== softmax (128 threads, one token row each)
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
-        const int sg = VQ ? 0 : (warp - 3) >> 2;            // softmax group: pages sg, sg + SG, ...
+        const int sg = VQ ? 0 : (warp - W_SM) >> 2;         // softmax group: pages sg, sg + SG, ...
         const int hg = VQ ? (warp - 4) >> 2 : 0;            // quantised V: group hg takes kv heads hg * NKV / 2 .. of every page
         constexpr int GPG = VQ ? NKV / 2 : NKV;             // kv heads per group
         const int g_lo = hg * GPG, g_hi = g_lo + GPG;
@@ -625,7 +636,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // as broadcasts; the reference maxima, identical in every lane, are kept one per lane -- lane h holds head
         // h's -- and fetched by shuffle, so are the rescale factors; the row sums live in spare tensor-memory columns,
         // which a thread can index at run time.)
-        float cs[VQ ? 1 : HPC], m[VQ ? 1 : HPC], l[VQ ? 1 : HPC];
+        // (Scores only: 16 warps leave 128 registers per thread, so the column scales are read from shared memory there too.)
+        constexpr bool CS_REG = WV && !VQ;
+        float cs[CS_REG ? HPC : 1], m[VQ ? 1 : HPC], l[VQ ? 1 : HPC];
         float m_lane = -INFINITY;
         const uint32_t l_tm = tl + TM_L;                    // row sums: tensor-memory columns, one per head, this thread's lane
         auto m_of = [&](int h) -> float { return __shfl_sync(0xffffffffu, m_lane, h); };
@@ -633,7 +646,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         if constexpr (INLQ) if (sg == 0) {
             // the query may come from the launch before this one unless the caller says it was ready earlier
             if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
-            pkv_absorb_impl::body_tile<WP>(qa, b, smem + C::Q_OFF, reinterpret_cast<float*>(smem + C::P_OFF), tid - 3 * 32);
+            pkv_absorb_impl::body_tile<WP>(qa, b, smem + C::Q_OFF, reinterpret_cast<float*>(smem + C::P_OFF), tid - W_SM * 32);
             fence_proxy_async_smem();                       // generic-proxy writes -> visible to tcgen05.mma / tcgen05.cp
             mbar_arrive(&X->q_full);
         }
@@ -645,7 +658,11 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             tmem_st_wait();
         } else {
 #pragma unroll
-            for (int h = 0; h < HPC; ++h) { cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f; m[h] = -INFINITY; l[h] = 0.0f; }
+            for (int h = 0; h < HPC; ++h) {
+                if constexpr (CS_REG) cs[h] = ok ? rs[h_base + h] * col_scale : 0.0f;
+                m[h] = -INFINITY;
+                l[h] = 0.0f;
+            }
         }
         (void)cs; (void)m; (void)l;
         for (int i = sg; i < P && ok; i += SG) {
@@ -667,11 +684,18 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 const bool valid = token < T;
                 const float* hs = rs + h_base;
                 const uint32_t s_tm = tl + TM_S + 128 * sb + h_base;
-                auto load_scores = [&](int g, float (&sv)[REP]) {
-                    uint32_t r[PKV_QUERY_TERMS][REP];
+                // the loads of kv head g + 1 are on their way while g is worked on: ask, wait, copy, ask for the next, compute
+                auto ask_scores = [&](int g, uint32_t (&r)[PKV_QUERY_TERMS][REP]) {
 #pragma unroll
                     for (int t = 0; t < PKV_QUERY_TERMS; ++t) tmem_ldn<REP>(s_tm + 32 * t + g * REP, r[t]);
-                    tmem_ld_wait();
+                };
+                auto take_scores = [&](int g, uint32_t (&rn)[PKV_QUERY_TERMS][REP], float (&sv)[REP]) {
+                    uint32_t r[PKV_QUERY_TERMS][REP];
+#pragma unroll
+                    for (int t = 0; t < PKV_QUERY_TERMS; ++t)
+#pragma unroll
+                        for (int hh = 0; hh < REP; ++hh) r[t][hh] = rn[t][hh];
+                    if (g + 1 < g_hi) ask_scores(g + 1, rn);
 #pragma unroll
                     for (int hh = 0; hh < REP; ++hh) {
                         float a = __uint_as_float(r[0][hh]);
@@ -683,10 +707,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 };
                 // ---- does any head of any row outgrow its reference maximum by more than the threshold?
                 float exc = -INFINITY;
+                uint32_t rn[PKV_QUERY_TERMS][REP];
+                ask_scores(g_lo, rn);
 #pragma unroll 1
                 for (int g = g_lo; g < g_hi; ++g) {
                     float sv[REP];
-                    load_scores(g, sv);
+                    tmem_ld_wait();
+                    take_scores(g, rn, sv);
 #pragma unroll
                     for (int hh = 0; hh < REP; ++hh) exc = fmaxf(exc, sv[hh] - m_of(g * REP + hh));   // +inf while the head has no reference yet
                 }
@@ -700,10 +727,12 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 PKV_WPM(53);
                 if (grow) {
                     float wm = -INFINITY;                   // lane h: the tile maximum of head h (this group's heads)
+                    ask_scores(g_lo, rn);
 #pragma unroll 1
                     for (int g = g_lo; g < g_hi; ++g) {
                         float sv[REP];
-                        load_scores(g, sv);
+                        tmem_ld_wait();
+                        take_scores(g, rn, sv);
 #pragma unroll
                         for (int hh = 0; hh < REP; ++hh) {
                             const uint32_t red = __reduce_max_sync(0xffffffffu, f2ord(sv[hh]));
@@ -764,19 +793,25 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 // The kv head's operand row of this token is 16 contiguous bytes per MN group, byte n = term * REP + head.
                 const uint16_t* sc = reinterpret_cast<const uint16_t*>(smem + C::SC_OFF + buf * VQ_SCALE_BYTES) + row;
                 uint8_t* pdst = smem + C::P_OFF + buf * P_BYTES + row * 16;
+                uint32_t ln[REP];
+                ask_scores(g_lo, rn);
+                tmem_ldn<REP>(l_tm + g_lo * REP, ln);       // (the row sums travel with the scores)
 #pragma unroll 1
                 for (int g = g_lo; g < g_hi; ++g) {
                     float sv[REP], pw[REP];
                     uint32_t lr[REP];
-                    tmem_ldn<REP>(l_tm + g * REP, lr);        // (waited for together with the scores)
-                    load_scores(g, sv);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) lr[hh] = ln[hh];
+                    take_scores(g, rn, sv);
+                    if (g + 1 < g_hi) tmem_ldn<REP>(l_tm + (g + 1) * REP, ln);
                     const float vsg = pkv_bf16_bits_to_float(sc[g * PKV_PAGE_TOKENS]);
 #pragma unroll
                     for (int hh = 0; hh < REP; ++hh) {
                         const int h = g * REP + hh;
                         if (scores_out && valid) scores_out[((size_t)b * NQ + h_base + h) * scores_stride + token] = sv[hh] * inv_logit_scale;
                         const float mh = m_of(h);
-                        const float p = exp2f(sv[hh] - (mh > -INFINITY ? mh : 0.0f));     // exp2(-inf) = 0 for masked rows
+                        const float p = ex2_fast(sv[hh] - (mh > -INFINITY ? mh : 0.0f));  // exp2(-inf) = 0 for masked rows
                         pw[hh] = p > 0.0f ? fminf(p * vsg, 57344.0f) : 0.0f;            // a masked row's scale may be anything
                         lr[hh] = __float_as_uint(__uint_as_float(lr[hh]) + p);
                     }
@@ -833,7 +868,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_fence_before_sync();
                 mbar_arrive(&X->s_empty[sb]);               // the MMA warp may overwrite this S buffer
 #pragma unroll
-                for (int h = 0; h < HPC; ++h) s[h] *= cs[h];
+                for (int h = 0; h < HPC; ++h) s[h] *= CS_REG ? cs[CS_REG ? h : 0] : rs[h_base + h] * col_scale;
             }
             PKV_WPM(52);                                    // scores out of tensor memory
             const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
@@ -843,12 +878,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 for (int h = 0; h < HPC; ++h) scores_out[((size_t)b * NQ + h_base + h) * scores_stride + token] = s[h] * inv_logit_scale;
             }
             // ---- does any head of any row outgrow its reference maximum by more than the threshold?
-            float exc = -INFINITY;
+            float ex4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains instead of one of 32 dependent maxima
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
                 if (!valid) s[h] = -INFINITY;
-                exc = fmaxf(exc, s[h] - m[h]);              // +inf while the head has no reference yet
+                ex4[h & 3] = fmaxf(ex4[h & 3], s[h] - m[h]);                 // +inf while the head has no reference yet
             }
+            const float exc = fmaxf(fmaxf(ex4[0], ex4[1]), fmaxf(ex4[2], ex4[3]));
             bool grow = __any_sync(0xffffffffu, exc > RESCALE_THRESHOLD);
             if (with_v) {                                   // P.V needs one reference per head for all 128 rows
                 if (lane == 0) X->wflag[buf][quad] = grow ? 1 : 0;
@@ -916,7 +952,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
                 const float mh = m[h];
-                float p = exp2f(s[h] - (mh > -INFINITY ? mh : 0.0f));                 // exp2(-inf) = 0 for masked rows
+                float p = ex2_fast(s[h] - (mh > -INFINITY ? mh : 0.0f));              // exp2(-inf) = 0 for masked rows
                 if (with_v) {
                     // the weight goes to the tensor core as hi + lo bf16; the row sum is taken over exactly
                     // that value, so numerator and denominator of softmax . V carry the same rounding
