@@ -264,8 +264,10 @@ int pkv_absorb_rows_f64(const double* A_re_dev, const double* A_im_dev, const do
  * of the `batch` sequences (x_dev [batch, d_model], write_positions_dev / slots_dev / v_rows_dev
  * [batch]) and pkv_absorb of the step's queries (q_dev at query_positions_dev [batch]) -- as ONE
  * launch: the reference's per-layer patch makes them back to back (PhasorKey.write, then
- * PhasorKey.absorb: phasorkv/latent.py:57-83) and neither depends on the other. The bits written are
- * those of the two separate calls. The single launch needs batch <= PKV_SMALL_WRITE_TOKENS, R a
+ * PhasorKey.absorb: phasorkv/latent.py:57-83) and neither depends on the other. The absorbed queries are
+ * those of pkv_absorb bit for bit; the latent rows are those of pkv_cache_write up to the order in which a
+ * row's partial sums are added (the last bit of a value may differ; the stored codes and scales are the
+ * quantiser's bits of the rows this call forms). The single launch needs batch <= PKV_SMALL_WRITE_TOKENS, R a
  * multiple of 16 and d_model a multiple of 32 and at most 16384; otherwise the two separate launches
  * are made (scratch_dev, optional, is only used then). latent_out_dev, qabs_out_dev, qop_out_dev,
  * v_rows_dev are optional as in the separate calls. q_dev NULL: the write alone (the queries are then

@@ -9,8 +9,9 @@
 // together and that form two whole NVFP4 blocks -- and CTA r of the cluster owns the r-th eighth of
 // d_model. Each CTA leaves its partial dot products in its own shared memory; after one cluster
 // barrier CTA r adds the eight partials of tokens 2r and 2r+1 through distributed shared memory,
-// rotates, quantises and stores them. No scratch in global memory, no second launch. The additions are
-// made in the order of the two-launch path of pkv_write.cu, so both give the same bits.
+// rotates, quantises and stores them. No scratch in global memory, no second launch. (The partial sums of a
+// slice are added in another order than in the two-launch path of pkv_write.cu: the two may differ in the last
+// bit of a latent value.)
 //
 // Absorb role: the grid rows behind the column tiles run pkv_absorb_impl::body unchanged.
 #include "pkv_absorb.cuh"
@@ -67,14 +68,15 @@ __device__ __forceinline__ float4 load_x4(const XT* src) {
     }
 }
 
-// SMALL: at most PTS tokens (a token-sharded sequence set, a batch of a few sequences). The same tiles, but a
-// thread owns one pair column and one sixteenth of the chunk's k range for ALL tokens, so that a factor value
-// read from shared memory feeds PTS multiply-adds instead of one: the loop is no longer bound by shared-memory
-// bandwidth (6 reads of 16 bytes per 32 multiply-adds instead of 3 per 8). The k slices are added in ascending
-// order; the sum order differs from the general path, so the two paths may differ in the last bit of a sum.
+// The projection of a pass is register-tiled: a thread owns one pair column, PTS tokens and one slice of the
+// chunk's k range, so that a factor value read from shared memory feeds PTS multiply-adds (6 reads of 16 bytes per
+// 32 multiply-adds; one token per thread needs 3 per 8 and is bound by shared-memory bandwidth: 12.1 us per launch
+// at 16 tokens against 7.1 us at 4). TG = token groups of a pass: 1 (at most PTS tokens: a token-sharded sequence
+// set, a batch of a few sequences; 16 k slices) or 4 (16 tokens, 4 k slices). The k slices are added in ascending
+// order.
 constexpr int PTS = 4;
 
-template <typename XT, bool SMALL>
+template <typename XT, int TG>
 __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x;
@@ -92,7 +94,8 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     const XT* x = reinterpret_cast<const XT*>(A.x);
     const int t = tid >> 4, c = tid & 15;
     constexpr int NVB = 2 * PC * (KC / 4) / NT;     // 16-byte vectors per thread: factor tile (16)
-    constexpr int NVX = (SMALL ? PTS : PT) * (KC / 4) / NT;       // ... and token tile (8; 2 for the small path)
+    constexpr int PTT = TG * PTS;                   // tokens of a pass that are worked on
+    constexpr int NVX = PTT * (KC / 4) / NT;        // ... and token tile (8; 2 with one token group)
 
     for (int t0 = 0; t0 < n_tokens; t0 += PT) {
         const int my_tok = t0 + ks * TPR + (tid >> 4);              // for tid < TPR * PC: the token this thread rotates
@@ -150,10 +153,10 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                 *reinterpret_cast<float4*>(xs + (i / (KC / 4)) * KC + (i % (KC / 4)) * 4) = xv[n];
             }
             __syncthreads();
-            if constexpr (SMALL) {
-                // thread = (pair column c2, k slice kq of KC / 16 values); all PTS tokens
-                const int c2 = tid & 15, kq = tid >> 4;
-                constexpr int KS = KC / 16;
+            {
+                // thread = (pair column c2, token group tgi, k slice kq of KC / KQ values)
+                constexpr int KQ = 16 / TG, KS = KC / KQ;
+                const int c2 = tid & 15, tgi = (tid >> 4) % TG, kq = (tid >> 4) / TG;
                 float re[PTS][4], im[PTS][4];
 #pragma unroll
                 for (int tt = 0; tt < PTS; ++tt)
@@ -161,8 +164,8 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                     for (int e = 0; e < 4; ++e) re[tt][e] = im[tt][e] = 0.0f;
                 const float* ar = bs + c2 * BP + kq * KS;
                 const float* br = bs + (PC + c2) * BP + kq * KS;
-                const float* xr = xs + kq * KS;
-#pragma unroll
+                const float* xr = xs + tgi * PTS * KC + kq * KS;
+#pragma unroll 4
                 for (int k = 0; k < KS; k += 4) {
                     const float4 av = *reinterpret_cast<const float4*>(ar + k);
                     const float4 bq = pair ? *reinterpret_cast<const float4*>(br + k) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -176,45 +179,21 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
                     }
                 }
                 __syncthreads();                                    // every thread is done with the token tile: it becomes the exchange area
-                float* red = xs;                                    // [16 k slices][PTS][2][PC]
+                float* red = xs;                                    // [KQ k slices][PTT tokens][2][PC]
 #pragma unroll
                 for (int tt = 0; tt < PTS; ++tt) {
-                    red[((kq * PTS + tt) * 2 + 0) * PC + c2] = (re[tt][0] + re[tt][1]) + (re[tt][2] + re[tt][3]);
-                    red[((kq * PTS + tt) * 2 + 1) * PC + c2] = (im[tt][0] + im[tt][1]) + (im[tt][2] + im[tt][3]);
+                    red[((kq * PTT + tgi * PTS + tt) * 2 + 0) * PC + c2] = (re[tt][0] + re[tt][1]) + (re[tt][2] + re[tt][3]);
+                    red[((kq * PTT + tgi * PTS + tt) * 2 + 1) * PC + c2] = (im[tt][0] + im[tt][1]) + (im[tt][2] + im[tt][3]);
                 }
                 __syncthreads();
-                if (tid < PTS * 2 * PC) {
-                    const int tt = tid >> 5, half = (tid >> 4) & 1, cc = tid & 15;
+                for (int idx = tid; idx < PTT * 2 * PC; idx += NT) {
+                    const int tt = idx >> 5, half = (idx >> 4) & 1, cc = idx & 15;
                     float v = 0.0f;
 #pragma unroll
-                    for (int q = 0; q < 16; ++q) v += red[((q * PTS + tt) * 2 + half) * PC + cc];
+                    for (int q = 0; q < KQ; ++q) v += red[((q * PTT + tt) * 2 + half) * PC + cc];
                     part[((ch * 2 + half) * PT + tt) * PC + cc] = v;
                 }
-                continue;                                           // next chunk (its first barrier protects `red`)
-            }
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
-            const float* xr = xs + t * KC;
-            const float* ar = bs + c * BP;
-            const float* br = bs + (PC + c) * BP;
-            if (pair) {
-#pragma unroll 8
-                for (int k = 0; k < KC; k += 4) {
-                    const float4 xq = *reinterpret_cast<const float4*>(xr + k);
-                    const float4 av = *reinterpret_cast<const float4*>(ar + k);
-                    const float4 bq = *reinterpret_cast<const float4*>(br + k);
-                    a0 = fmaf(xq.x, av.x, a0); a1 = fmaf(xq.y, av.y, a1); a2 = fmaf(xq.z, av.z, a2); a3 = fmaf(xq.w, av.w, a3);
-                    b0 = fmaf(xq.x, bq.x, b0); b1 = fmaf(xq.y, bq.y, b1); b2 = fmaf(xq.z, bq.z, b2); b3 = fmaf(xq.w, bq.w, b3);
-                }
-            } else {
-#pragma unroll 8
-                for (int k = 0; k < KC; k += 4) {
-                    const float4 xq = *reinterpret_cast<const float4*>(xr + k);
-                    const float4 av = *reinterpret_cast<const float4*>(ar + k);
-                    a0 = fmaf(xq.x, av.x, a0); a1 = fmaf(xq.y, av.y, a1); a2 = fmaf(xq.z, av.z, a2); a3 = fmaf(xq.w, av.w, a3);
-                }
-            }
-            part[((ch * 2 + 0) * PT + t) * PC + c] = (a0 + a1) + (a2 + a3);
-            part[((ch * 2 + 1) * PT + t) * PC + c] = (b0 + b1) + (b2 + b3);
+            }                                                       // (the next chunk's first barrier protects `red`)
         }
         cluster.sync();                                             // every partial of the pass is in place
 
@@ -273,7 +252,7 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
     }
 }
 
-template <typename XT, bool SMALL>
+template <typename XT, int TG>
 __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs Wa, const pkv_absorb_impl::Args Aa, int batch) {
     extern __shared__ __align__(16) float sm[];
     // Wait first, trigger second (as pkv_absorb does): the attention kernel behind this one streams cache
@@ -287,12 +266,12 @@ __global__ void __launch_bounds__(NT) pkv_step_prologue_kernel(const WriteArgs W
         if (a < batch * n_hg) pkv_absorb_impl::body(Aa, a / n_hg, a % n_hg, sm);
         return;
     }
-    write_role<XT, SMALL>(Wa, sm);
+    write_role<XT, TG>(Wa, sm);
 }
 
-template <typename XT, bool SMALL>
+template <typename XT, int TG>
 cudaError_t launch_prologue(const WriteArgs& Wa, const pkv_absorb_impl::Args& Aa, int batch, size_t smem, cudaStream_t st) {
-    auto kern = pkv_step_prologue_kernel<XT, SMALL>;
+    auto kern = pkv_step_prologue_kernel<XT, TG>;
     static pkv_attr_flags smem_set;                      // per instantiation and device
     {
         cudaError_t e = pkv_set_max_smem(kern, (int)smem, smem_set);
@@ -373,12 +352,12 @@ extern "C" int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cach
     const int absorb_batch = q_dev ? batch : 0;                      // no queries: the write role alone
     const cudaStream_t cst = (cudaStream_t)stream;
     cudaError_t le;
-    if (batch <= PTS)                                                 // a few tokens: the register-tiled projection
-        le = x_dtype == PKV_F32 ? launch_prologue<float, true>(Wa, Aa, absorb_batch, smem, cst)
-                                : launch_prologue<uint16_t, true>(Wa, Aa, absorb_batch, smem, cst);
+    if (batch <= PTS)                                                 // a few tokens: one token group, 16 k slices
+        le = x_dtype == PKV_F32 ? launch_prologue<float, 1>(Wa, Aa, absorb_batch, smem, cst)
+                                : launch_prologue<uint16_t, 1>(Wa, Aa, absorb_batch, smem, cst);
     else
-        le = x_dtype == PKV_F32 ? launch_prologue<float, false>(Wa, Aa, absorb_batch, smem, cst)
-                                : launch_prologue<uint16_t, false>(Wa, Aa, absorb_batch, smem, cst);
+        le = x_dtype == PKV_F32 ? launch_prologue<float, 4>(Wa, Aa, absorb_batch, smem, cst)
+                                : launch_prologue<uint16_t, 4>(Wa, Aa, absorb_batch, smem, cst);
     PKV_CUDA_TRY(le);
     return PKV_OK;
 }

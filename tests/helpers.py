@@ -13,8 +13,8 @@ from phasorkv_b200.latent import PhasorKey
 
 class Scenario:
     def __init__(self, config="cfg2", seqlens=(300,), layer=0, gain=1.0, seed=11, d_model=4096, pos0=0,
-                 fused_write=True, x_dtype=torch.float32, v_bits=0):
-        self.spec = synth.make_layer(config, layer, d_model=d_model, factor_gain=gain)
+                 fused_write=True, x_dtype=torch.float32, v_bits=0, n_kv=None):
+        self.spec = synth.make_layer(config, layer, d_model=d_model, factor_gain=gain, n_kv=n_kv)
         self.pk = PhasorKey.from_spec(self.spec, device="cuda")
         self.opk = po.PhasorKeyOracle.from_spec(self.spec)
         self.seqlens = list(seqlens)

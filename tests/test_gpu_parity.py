@@ -446,9 +446,9 @@ def test_decode_time_write_path(config, n):
 def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
     """The one-launch step prologue (write of the newest tokens + absorb) leaves the bits of the two
     separate calls: cache codes and scales, V rows, unquantised rows, absorbed queries, operand.
-    cfg3 (R = 120, not a multiple of 16) takes the entry point's two-launch route. Up to 4 tokens the
-    prologue projects with a register tile that adds the d_model slices in another order: there the rows
-    agree to fp32 rounding, and the stored bits are the reference quantiser's bits of the prologue's own rows."""
+    cfg3 (R = 120, not a multiple of 16) takes the entry point's two-launch route. The one-launch prologue
+    projects with a register tile that adds the k slices in another order than the separate write: there the
+    rows agree to fp32 rounding, and the stored bits are the reference quantiser's bits of the prologue's own rows."""
     sc = Scenario(config, seqlens=(n,), pos0=32767)
     pk, W = sc.pk, sc.spec.cache_width
     x = sc.x[0].cuda().to(x_dtype)
@@ -473,8 +473,8 @@ def test_decode_prologue_equals_separate_calls(config, n, x_dtype):
         torch.cuda.synchronize()
         caches.append(cache), outs.append(out), wss.append(ws)
     assert float(outs[1].abs().max()) > 0
-    small = n <= 4 and config != "cfg3"                      # the register-tiled projection of the one-launch prologue
-    if small:
+    tiled = config != "cfg3"                                 # the register-tiled projection of the one-launch prologue
+    if tiled:
         assert rel(outs[1], outs[0]) < 2e-6
         if x_dtype == torch.float32:                           # rows_ref is the oracle's write of the fp32 hidden states
             assert rel(outs[1].cpu(), sc.rows_ref[0]) < 5e-6
@@ -637,6 +637,12 @@ def test_tc_decode_lengths(T):
                                          ("cfg5", 256.0)])
 def test_tc_decode_ragged_batch(config, gain):
     _check_decode(Scenario(config, seqlens=(513, 0, 77, 300), gain=gain, pos0=100000), n_split=4, simt=False)
+
+
+@pytest.mark.parametrize("gain", [1.0, 256.0])
+def test_tc_decode_eight_heads_per_kv_head(gain):
+    """32 query heads on 4 kv heads: the third grouping the tensor-core kernel is built for (1, 4 or 8 heads per kv head)."""
+    _check_decode(Scenario("cfg2", seqlens=(513, 0, 77, 300), gain=gain, pos0=100000, n_kv=4), n_split=4, simt=False)
 
 
 def test_tc_decode_long_single_split():

@@ -34,11 +34,12 @@ def test_vq_quantiser_matches_reference_golden_vectors(bits):
     assert np.array_equal(rows[:, 0].cpu().numpy(), g[f"xhat{bits}"])
 
 
-@pytest.mark.parametrize("config,bits,seqlens,n_split", [
-    ("cfg2", 3, (1, 15, 129, 300), 2), ("cfg2", 2, (513, 0, 77), 3), ("cfg3", 3, (260, 128), 1), ("cfg5", 3, (300, 127), 2),
-    ("cfg2", 3, (1400,), 4)])
-def test_vq_decode_against_oracle(config, bits, seqlens, n_split):
-    sc = Scenario(config, seqlens=seqlens, gain=16.0, pos0=9000, v_bits=bits)
+@pytest.mark.parametrize("config,bits,seqlens,n_split,n_kv", [
+    ("cfg2", 3, (1, 15, 129, 300), 2, None), ("cfg2", 2, (513, 0, 77), 3, None), ("cfg3", 3, (260, 128), 1, None),
+    ("cfg5", 3, (300, 127), 2, None), ("cfg2", 3, (1400,), 4, None),
+    ("cfg2", 3, (300, 127, 1), 2, 4), ("cfg2", 2, (1400,), 3, 4)])            # the last two: 8 query heads per kv head
+def test_vq_decode_against_oracle(config, bits, seqlens, n_split, n_kv):
+    sc = Scenario(config, seqlens=seqlens, gain=16.0, pos0=9000, v_bits=bits, n_kv=n_kv)
     ws = sc.pk.workspace(sc.B, n_split)
     sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws)
     sc.pk.attend_step(sc.cache, ws, out=ws.out, after_absorb=True)
