@@ -49,8 +49,8 @@ constexpr int NV_BARS = NVS_Q > NV_STAGES ? NVS_Q : NV_STAGES;    // barrier pai
 constexpr int V_STAGE_BYTES = PKV_PAGE_TOKENS * DH * 2;        // one kv head of one page
 constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weights of a page as hi + lo bf16 (2^-17 relative)
 constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
-constexpr int NTHREADS_SCORES = 16 * 32;      // scores only: K producer, three MMA issuers, three softmax groups; page i belongs to
-                                              // issuer, score buffer and group i % 3
+constexpr int NTHREADS_SCORES = 20 * 32;      // scores only: K producer, three MMA issuers (page i: issuer and score buffer i % 3), four
+                                              // softmax groups that split the heads of every page
 constexpr int NTHREADS_VQ = 20 * 32;          // quantised V: warps 0-2 as always, 3 second P.V issuer, 4-11 softmax (two groups that split
                                               // the kv heads), 12-19 converters (two per tile). Each role's chain of dependent instructions
                                               // is what bounds a page, so the roles are spread over as many warps as the layout allows
@@ -225,9 +225,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int s = 0; s < NV_BARS; ++s) { mbar_init(&X->v_full[s], VQ ? 2 : 1); mbar_init(&X->v_empty[s], 1); }
         for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 2); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 256); }
-        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], VQ ? 256 : 128); }
+        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], WV ? (VQ ? 256 : 128) : 512); }
         for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], VQ ? 256 : 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }
-        mbar_init(&X->sm_bar, WV ? (VQ ? 256 : 128) : 128 * NSB_S);
+        mbar_init(&X->sm_bar, WV ? (VQ ? 256 : 128) : 512);
         X->abort_flag = 0;
         fence_barrier_init();
     }
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     const int p_lo = split * pps, p_hi = min(npages, p_lo + pps);
     const int P = p_hi - p_lo;
     constexpr bool with_v = WV;                      // scores-only launches are a separate instantiation
-    constexpr int SG = WV ? 1 : NSB_S;               // softmax groups
+    constexpr int SG = 1;                            // softmax groups that split the pages (none does any more)
     constexpr int NSB = WV ? NSB_V : NSB_S;
     constexpr int nks = WV ? NK_STAGES : NK_MAX;      // without V its stages hold more latent pages in flight
     float* part = partials + ((size_t)b * n_split + split) * NQ * (DH + 2);
@@ -628,6 +628,110 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             mbar_arrive(&X->sm_bar);
             return wait_all(&X->sm_bar, (sync_phase++) & 1, 45);
         };
+        if constexpr (!WV) {
+            // ---------------- scores only: no weights, no P.V. The four softmax groups split the HEADS of every page
+            // (group hs takes heads 8 hs .. 8 hs + 7): a thread's state is 8 heads instead of 32 and the loop body a
+            // quarter of the code, every warp keeps its own statistics (reference maximum and row sums per head) and no
+            // rendezvous is needed inside the loop. A score buffer is free again when all four groups have read it.
+            constexpr int HS = 4, HPT = NQ / HS;
+            const int hs = (warp - W_SM) >> 2, h0 = hs * HPT;
+            if constexpr (INLQ) if (hs == 0) {
+                if (early && !(flags & PKV_ATTN_QUERY_READY)) pkv_grid_wait();
+                pkv_absorb_impl::body_tile<WP>(qa, b, smem + C::Q_OFF, reinterpret_cast<float*>(smem + C::P_OFF), tid - W_SM * 32);
+                fence_proxy_async_smem();                   // generic-proxy writes -> visible to tcgen05.mma / tcgen05.cp
+                mbar_arrive(&X->q_full);
+            }
+            bool ok = wait_all(&X->q_full, 0, 40);
+            float cs[HPT], m[HPT], l[HPT];
+#pragma unroll
+            for (int j = 0; j < HPT; ++j) { cs[j] = ok ? rs[h0 + j] * col_scale : 0.0f; m[j] = -INFINITY; l[j] = 0.0f; }
+            for (int i = 0; i < P && ok; ++i) {
+                const int sb = i % NSB;
+                ok = wait_all(&X->s_full[sb], (i / NSB) & 1, 41);
+                if (!ok) break;
+                if (i == 0 && warp == W_SM && lane == 0) PKV_TL(10);
+                tc_fence_after_sync();
+#ifdef PKV_WAITPROF
+                long long wp_t = clock64();
+#endif
+                float sv[HPT];
+                {
+                    uint32_t r[PKV_QUERY_TERMS][HPT];
+#pragma unroll
+                    for (int t = 0; t < PKV_QUERY_TERMS; ++t) tmem_ldn<HPT>(tl + TM_S + 128 * sb + 32 * t + h0, r[t]);
+                    tmem_ld_wait();
+                    tc_fence_before_sync();
+                    mbar_arrive(&X->s_empty[sb]);           // one of the 512 arrivals that free this S buffer
+#pragma unroll
+                    for (int j = 0; j < HPT; ++j) {
+                        float a = __uint_as_float(r[0][j]);
+#pragma unroll
+                        for (int t = 1; t < PKV_QUERY_TERMS; ++t) a += __uint_as_float(r[t][j]);   // the terms share the head's tensor scale
+                        sv[j] = a * cs[j];
+                    }
+                }
+                PKV_WPM(52);
+                const int token = (p_lo + i) * PKV_PAGE_TOKENS + row;
+                const bool valid = token < T;
+                if (scores_out && valid) {
+#pragma unroll
+                    for (int j = 0; j < HPT; ++j) scores_out[((size_t)b * NQ + h0 + j) * scores_stride + token] = sv[j] * inv_logit_scale;
+                }
+                float e2[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < HPT; ++j) {
+                    if (!valid) sv[j] = -INFINITY;
+                    e2[j & 1] = fmaxf(e2[j & 1], sv[j] - m[j]);       // +inf while the head has no reference yet
+                }
+                const bool grow = __any_sync(0xffffffffu, fmaxf(e2[0], e2[1]) > RESCALE_THRESHOLD);
+                PKV_WPM(53);
+                if (grow) {
+#pragma unroll
+                    for (int j = 0; j < HPT; ++j) {
+                        const float m_new = fmaxf(m[j], ord2f(__reduce_max_sync(0xffffffffu, f2ord(sv[j]))));
+                        l[j] *= m[j] > -INFINITY ? exp2f(m[j] - m_new) : 1.0f;      // nothing accumulated yet: leave as is
+                        m[j] = m_new;
+                    }
+                }
+                PKV_WPM(54);
+#pragma unroll
+                for (int j = 0; j < HPT; ++j) l[j] += ex2_fast(sv[j] - (m[j] > -INFINITY ? m[j] : 0.0f));   // exp2(-inf) = 0 for masked rows
+                PKV_WPM(56);
+            }
+            if (warp == W_SM && lane == 0) PKV_TL(11);
+            if (early) pkv_grid_wait();                     // (see the note at the same place of the other branch)
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < HPT; ++j) part[(h0 + j) * (DH + 2) + row] = 0.0f;
+                float lw = 0.0f, mw = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < HPT; ++j) {
+                    float v = l[j];
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == h0 + j) { lw = v; mw = m[j]; }
+                }
+                if (lane >= h0 && lane < h0 + HPT) {            // a head's sums come from the group that owns it, one set per warp
+                    X->lsum[0][quad][lane] = lw;
+                    X->mfin[0][quad][lane] = mw;
+                }
+                if (softmax_sync() && quad == 0 && hs == 0) {
+                    float M = -INFINITY, lt = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) M = fmaxf(M, X->mfin[0][w][lane]);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float mw2 = X->mfin[0][w][lane];
+                        if (mw2 > -INFINITY) lt = fmaf(X->lsum[0][w][lane], exp2f(mw2 - M), lt);
+                    }
+                    part[lane * (DH + 2) + DH] = M;
+                    part[lane * (DH + 2) + DH + 1] = lt;
+                }
+            } else {
+                softmax_sync();                             // keep the rendezvous count whole when a group gave up
+            }
+            if (warp == W_SM && lane == 0) PKV_TL(12);
+        } else {
         // Per head (all kept in registers, identical in every thread that shares statistics): the
         // column scale that turns the MMA result into a base-2 logit, the reference maximum, and
         // this thread's share of the sum of 2^(s - m).
@@ -1061,6 +1165,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             softmax_sync();                                 // keep the rendezvous count whole when a group gave up
         }
         if (warp == W_SM && lane == 0) PKV_TL(12);
+        }
     }
     // ---- teardown: everyone meets, tensor memory goes back
     tc_fence_before_sync();
