@@ -61,7 +61,7 @@ def parse():
     ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                     help="token-sharded exchange: own peer-memory kernel, or NCCL all-gather + merge")
-    ap.add_argument("--no-graph", action="store_true", help="time the token-sharded step eagerly instead of as a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="time the steps as eager launches instead of CUDA graph replays")
     ap.add_argument("--splits", type=int, default=0)
     return ap.parse_args()
 
@@ -420,7 +420,10 @@ def run_b200(args):
 
     def full_step():
         launches["n"] += st.step()
-    ms_step = timed(full_step, args.steps, args.warmup, dist)
+    # A step is replayed as ONE CUDA graph (96 launches: the host is out of the loop, and the dependent-launch chain
+    # keeps the 2-3 us between kernels that eager launches from Python lose); `--no-graph` times the eager step.
+    g_full = None if (args.no_graph or args.algo != "tc") else capture(full_step)
+    ms_step = timed(g_full if g_full else full_step, args.steps, args.warmup, dist)
     # ---- the same K steps once more with CUDA events around every attention launch: the per-launch
     # duration the roofline is computed from (the events sit between kernels of the chain, so this pass
     # is kept apart from the one that gives `value`)
@@ -544,7 +547,7 @@ def run_b200(args):
         "config": {"workload": "%s: %s layer shape, B=%d per GPU, T=%d, NVFP4 latent W=%d, %s %dx%d, %d layers%s"
                    % (args.workload, "7B multi-head-attention" if st.n_kv == st.n_q else "Llama-3.1-8B", st.B, st.T, st.W,
                       v_desc, st.n_kv, st.d, L, (", plus a %d-token chunk write per sequence per layer" % st.chunk) if st.chunk else ""),
-                   "algo": args.algo, "n_split": st.n_split, "parallelism": "batch-parallel x%d" % world,
+                   "algo": args.algo, "n_split": st.n_split, "cuda_graph": bool(g_full), "parallelism": "batch-parallel x%d" % world,
                    "l2": "inputs larger than L2 (%.2f GB streamed per layer, %.1f GB per step)"
                          % (st.bytes_full() / 1e9, L * st.bytes_full() / 1e9)},
         "k_path_us_per_layer": round(attn_k_ms * 1e3, 2),

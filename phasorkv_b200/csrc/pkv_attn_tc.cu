@@ -330,10 +330,12 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             }
             q_sent = true;
         };
+        // (the first page indices are asked for before anything else: their round trip is the longest wait of the start-up)
+        int mine = lane < P ? page_table[(size_t)b * max_pages + p_lo + lane] : 0;
         if (lane == 0 && !q_sent && !early) send_query();
         stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
         for (int base = 0; base < P && !stop; base += 32) {
-            const int mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
+            if (base > 0) mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
             for (int r0 = 0; r0 < 32 && base + r0 < P && !stop; r0 += nks) {
                 const int i = base + r0 + lane;                      // this lane's page of the round
                 const int pidx = __shfl_sync(0xffffffffu, mine, (r0 + lane) & 31);
