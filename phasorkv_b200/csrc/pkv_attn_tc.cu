@@ -294,10 +294,10 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // at one page per memory latency.
         if (lane == 0) { tma_prefetch_desc(&kmap); tma_prefetch_desc(&qmap); }
         // A lane's chain of wait, arm and copy costs ~0.4 - 0.7 us per page: as much as a page lasts in scores-only mode.
-        // So lane s takes the pages of stage s (page i, stage i % nks) and the lanes work side by side, round after
-        // round; lane 0 also fetches the query operand -- at once, or in early mode after the first round, so that the
-        // stages fill while the launch before this one still runs.
-        static_assert(32 % nks == 0, "a round of pages lies inside one fetch of 32 page indices");
+        // So lane s takes the pages of stage s (page i, stage i % nks) and the lanes work side by side, one sweep of
+        // nks pages after the other; lane 0 also fetches the query operand -- at once, or in early mode after the first
+        // sweep, so that the stages fill while the launch before this one still runs.
+        static_assert(32 % nks == 0, "a sweep of pages lies inside one fetch of 32 page indices");
         int issued = -1;                                             // the lane's own last page
         bool q_sent = inline_q, stop = false, waited = !early;
         auto send_query = [&]() {                                    // lane 0
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         for (int base = 0; base < P && !stop; base += 32) {
             if (base > 0) mine = base + lane < P ? page_table[(size_t)b * max_pages + p_lo + base + lane] : 0;
             for (int r0 = 0; r0 < 32 && base + r0 < P && !stop; r0 += nks) {
-                const int i = base + r0 + lane;                      // this lane's page of the round
+                const int i = base + r0 + lane;                      // this lane's page of the sweep
                 const int pidx = __shfl_sync(0xffffffffu, mine, (r0 + lane) & 31);
                 if (lane < nks && i < P) {
                     // a page that the launch before this one still writes (the newest token's) waits for that launch
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                         if (i == P - 1) PKV_TL(6);
                     }
                 }
-                if (lane == 0 && !q_sent && !stop) send_query();     // early mode: the first round of pages is on its way
+                if (lane == 0 && !q_sent && !stop) send_query();     // early mode: the first sweep of pages is on its way
                 stop = __any_sync(0xffffffffu, stop);
             }
         }

@@ -110,3 +110,47 @@ def test_full_size_properties(config, B, T, tc):
     es, eo = rel(S[b].cpu(), S_ref), rel(ws.out[b].cpu(), O_ref)
     print(f"{config}: sequence {b} against the oracle: logits {es:.2e}, outputs {eo:.2e}")
     assert es < 1e-3 and eo < 2e-3
+
+
+@pytest.mark.parametrize("config,B,T,bits", [("cfg2", 16, 32768, 3), ("cfg5", 8, 32768, 2)])
+def test_full_size_quantised_v(config, B, T, bits):
+    """The same sizes with V stored as per-token low-bit codes: split invariance, and one whole sequence against
+    the oracle's softmax . V on the dequantised value rows (2e-3)."""
+    spec = synth.make_layer(config, 0, factor_gain=64.0)
+    pk = PhasorKey.from_spec(spec)
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    xc = torch.randn((2048, pk.d_model), generator=gen, device="cuda")
+    rows = torch.empty((2048, pk.cache_width), device="cuda")
+    pk.write_paged(None, xc, torch.arange(2048, dtype=torch.int32, device="cuda"), None, latent_out=rows)
+    second = pk.calibrate_second(rows)
+    cache = pk.new_cache(B, T, v_bits=bits)
+    _fill(pk, cache, B, T, gen)
+    q = torch.randn((B, pk.n_q, pk.head_dim), generator=gen, device="cuda")
+    qpos = torch.full((B,), T, dtype=torch.int32, device="cuda")
+
+    def run(n_split):
+        ws = pk.workspace(B, n_split)
+        pk.absorb_step(q, qpos, ws)
+        pk.attend_step(cache, ws, out=ws.out, after_absorb=True)
+        torch.cuda.synchronize()
+        assert int(ws.status.abs().sum()) == 0
+        return ws.out.clone()
+
+    base = run(pk.default_splits(B, T))
+    assert torch.isfinite(base).all()
+    for ns in (1, 7, 40):
+        e = rel(run(ns).cpu(), base.cpu())
+        print(f"{config} q{bits}: n_split {ns} vs default: {e:.2e}")
+        assert e < 2e-3, ns
+    b = B - 1
+    lp = torch.arange(T, dtype=torch.int32, device="cuda")
+    slots = cache.slots(torch.full((T,), b, dtype=torch.int32, device="cuda"), lp)
+    deq, _, _ = cache.read(slots, second)
+    v_hat, _, _ = cache.read_vq(slots)
+    opk = po.PhasorKeyOracle.from_spec(spec)
+    ph = po.rope_phasors(spec.inv_freq, qpos[b:b + 1].cpu(), spec.attn_scale)
+    qa = opk.absorb(q[b].cpu()[:, None, :], ph)[:, 0]
+    O_ref = po.attend(opk.scores(qa, deq.cpu()), v_hat.cpu(), spec.n_kv, spec.head_dim)
+    eo = rel(base[b].cpu(), O_ref)
+    print(f"{config} q{bits}: sequence {b} against the oracle: outputs {eo:.2e}")
+    assert eo < 2e-3
