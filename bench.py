@@ -145,6 +145,8 @@ class Stack:
         # PKV_BENCH_POLLED=0: the attention waits for the whole launch before it instead of polling the
         # operand-ready counters that launch raises
         self.polled = os.environ.get("PKV_BENCH_POLLED", "1") == "1"
+        # behind the small absorb launch (the K-path pass) the plain dependent launch is as fast: off unless asked for
+        self.polled_absorb = os.environ.get("PKV_BENCH_POLLED_ABSORB", "0") == "1"
         self.layers, self.caches = [], []
         g = torch.Generator(device=device).manual_seed(seed)
         for l in range(n_layers):
@@ -246,7 +248,7 @@ class Stack:
                 if write:
                     pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)
                     n += 2
-                pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt)
+                pk.absorb_step(self.q[l], self.qpos, ws, operand=not self.simt, signal=self.polled_absorb and chained and not self.simt)
                 n += 1
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
@@ -258,7 +260,8 @@ class Stack:
                 pk.attend_q_step(cache, self.q[l], self.qpos, ws, early=chained, tail_written=True, query_ready=True)
             else:
                 pk.attend_step(cache, ws, simt=self.simt, scores_only=scores_only, after_absorb=chained and not fused,
-                               after_prologue=chained and fused, polled=self.polled and chained and fused and not self.simt)
+                               after_prologue=chained and fused,
+                               polled=chained and not self.simt and (self.polled if fused else self.polled_absorb))
             if events is not None:
                 e1.record()
                 events.append((e0, e1))
@@ -503,7 +506,9 @@ def run_b200(args):
                     ho[a:b_].copy_(st.out[a:b_], non_blocking=True)
         st.step(pre=pre, post=post)
         main.wait_stream(s_out)
-    ms_e2e = timed(e2e_step, args.steps, args.warmup, dist)
+    # the copies and the launches of a step replayed as one CUDA graph (three streams, joined before it ends), like `value`
+    g_e2e = None if (args.no_graph or args.algo != "tc") else capture(e2e_step)
+    ms_e2e = timed(g_e2e if g_e2e else e2e_step, args.steps, args.warmup, dist)
     h2d = hx.numel() * hx.element_size() + hv.numel() * hv.element_size() + hq.numel() * hq.element_size()
     if hc is not None:
         h2d += hc.numel() * hc.element_size()
@@ -562,7 +567,7 @@ def run_b200(args):
         "hbm_gbs": round(achieved, 1),
         "roofline": roof,
         "e2e": {"value": round(world * st.B / (ms_e2e * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "cuda_graph": bool(g_e2e)},
         "gpu_launches": gpu_launches,
         "clocks": clocks,
     }
