@@ -3,17 +3,20 @@
 //   latent[t, :] = x[t, :] . Bw^T   as tcgen05.mma kind::f16 with fp32 accumulation in tensor memory.
 // x is bf16 and therefore exact; the fp32 factor matrix enters as the sum of three bf16 matrices
 // (hi + mid + lo, exact to 2^-24 relative), i.e. three passes over the same x tile that accumulate in
-// the same 128 x W accumulator. One CTA owns 128 tokens and the whole latent row of each:
+// the same 128 x W accumulator. A tile is 128 tokens and the whole latent row of each; a CTA takes the tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... (the grid is at most one CTA per SM) and keeps two accumulators in tensor
+// memory, so that the epilogue of a tile runs under the MMAs of the next one:
 //   warp 0     producer: TMA tensor loads of the x tile [128 tokens x KT] and of the three factor
 //              tiles [W x KT] per KT-wide slice of d_model, through a ring of shared-memory stages
 //   warp 1     MMA issuer
-//   all 16 warps, once the accumulator is complete: the epilogue. A warp reads the tensor-memory lanes of
-//              its quarter (warp % 4: 32 tokens, one per lane) and takes every fourth *unit* (warp / 4): a
-//              unit is the 16 real columns 16u .. 16u+15 with their 16 imaginary partners R + 16u .., i.e.
-//              two whole NVFP4 blocks, or one block of the unrotated rest. Rotation by the token's phasors,
-//              NVFP4 quantisation with the reference's rounding and the store into the token's cache page
-//              all happen in registers, straight from tensor memory. (R not a multiple of 16: a real block
-//              and its partners do not line up; then four warps take a token row each through shared memory.)
+//   warps 2-15, once an accumulator is complete (warps 0 and 1 join them when the CTA has one tile): the epilogue.
+//              A warp reads the tensor-memory lanes of its quarter (warp % 4: 32 tokens, one per lane) and takes
+//              *units* from a counter of that quarter: a unit is the 16 real columns 16u .. 16u+15 with their 16
+//              imaginary partners R + 16u .., i.e. two whole NVFP4 blocks, or one block of the unrotated rest.
+//              Rotation by the token's phasors, NVFP4 quantisation with the reference's rounding and the store
+//              into the token's cache page all happen in registers, straight from tensor memory. (R not a
+//              multiple of 16: a real block and its partners do not line up; then a CTA has one tile and four
+//              warps take a token row each through shared memory, which the stages no longer need.)
 // Every wait is bounded; a give-up is recorded in `status` and the roles unwind.
 #include "pkv_common.cuh"
 #include "pkv_tcgen05.cuh"
@@ -50,10 +53,13 @@ struct WCfg {
 };
 
 struct WExtra {
-    uint64_t full[NST_MAX], empty[NST_MAX], done;
+    uint64_t full[NST_MAX], empty[NST_MAX];
+    uint64_t acc_full[2], acc_empty[2];      // accumulator b complete (MMA issuer -> epilogue) / read out (14 epilogue warps -> MMA issuer)
+    int next_unit[2][4];                     // epilogue units handed out, per accumulator and lane quarter
     uint32_t tmem_base;
     volatile int abort_flag;
 };
+constexpr int EPI_WARPS = NTHREADS / 32 - 2;
 
 // store one quantised block of a token row
 template <int WP>
@@ -77,7 +83,7 @@ __device__ __forceinline__ bool wwait(uint64_t* bar, uint32_t parity, WExtra* X,
 
 template <int WP>
 __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
-    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap bmap, int n_tokens, int D, int W, int R,
+    const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap bmap, int n_tokens, int n_tiles, int D, int W, int R,
     const int32_t* __restrict__ positions, const float2* __restrict__ phasors, int h2, const int32_t* __restrict__ slots,
     const int32_t* __restrict__ freq, const double* __restrict__ inv_freq, float attn_scale, const pkv_second second, int scale_up,
     uint8_t* __restrict__ latent, int n_pages, float* __restrict__ latent_out, int32_t* __restrict__ status) {
@@ -86,16 +92,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
     WExtra* X = reinterpret_cast<WExtra*>(smem + C::BODY);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int KT = C::KT, X_TILE = C::X_TILE;
-    const int tok0 = blockIdx.x * TM_TOK;
     const int n_kt = D / KT;
+    const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     pkv_grid_launch_dependents();
     if (tid == 0) {
         for (int s = 0; s < NST_MAX; ++s) { mbar_init(&X->full[s], 1); mbar_init(&X->empty[s], 1); }
-        mbar_init(&X->done, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&X->acc_full[b], 1);
+            mbar_init(&X->acc_empty[b], EPI_WARPS);
+            for (int q = 0; q < 4; ++q) X->next_unit[b][q] = 0;
+        }
         X->abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(&X->tmem_base, 256);
+    if (warp == 1) tmem_alloc(&X->tmem_base, 2 * WP);         // two accumulators of WP columns
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -107,49 +117,69 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
         if (lane == 0) {
             tma_prefetch_desc(&xmap);
             tma_prefetch_desc(&bmap);
-            int issued = 0;
-            for (int kt = 0; kt < n_kt; ++kt) {
-                const int s = kt % C::NST;
-                if (kt >= C::NST && !wwait(&X->empty[s], ((kt / C::NST) - 1) & 1, X, status, 60)) break;
-                uint8_t* st = smem + s * C::STAGE;
-                mbar_arrive_expect_tx(&X->full[s], C::STAGE);
-                tma_load_2d(st, &xmap, kt * KT, tok0, &X->full[s]);               // rows past n_tokens arrive as zeros
-                for (int t = 0; t < 3; ++t) tma_load_2d(st + X_TILE + t * C::B_TILE, &bmap, kt * KT, t * WP, &X->full[s]);
-                issued = kt + 1;
+            int c = 0;                                                             // slices asked for so far, over all tiles
+            bool ok = true;
+            for (int it = 0; it < my_tiles && ok; ++it) {
+                const int tok0 = ((int)blockIdx.x + it * (int)gridDim.x) * TM_TOK;
+                for (int kt = 0; kt < n_kt; ++kt, ++c) {
+                    const int s = c % C::NST;
+                    if (c >= C::NST && !wwait(&X->empty[s], ((c / C::NST) - 1) & 1, X, status, 60)) { ok = false; break; }
+                    uint8_t* st = smem + s * C::STAGE;
+                    mbar_arrive_expect_tx(&X->full[s], C::STAGE);
+                    tma_load_2d(st, &xmap, kt * KT, tok0, &X->full[s]);           // rows past n_tokens arrive as zeros
+                    for (int t = 0; t < 3; ++t) tma_load_2d(st + X_TILE + t * C::B_TILE, &bmap, kt * KT, t * WP, &X->full[s]);
+                }
             }
             if (X->abort_flag)                                                     // let copies in flight land before leaving
-                for (int kt = max(0, issued - C::NST); kt < issued; ++kt) mbar_wait(&X->full[kt % C::NST], (kt / C::NST) & 1, 1u << 16);
+                for (int k = max(0, c - C::NST); k < c; ++k) mbar_wait(&X->full[k % C::NST], (k / C::NST) & 1, 1u << 16);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_bf16(TM_TOK, WP, false, false);
             bool ok = true;
-            for (int kt = 0; kt < n_kt && ok; ++kt) {
-                const int s = kt % C::NST;
-                ok = wwait(&X->full[s], (kt / C::NST) & 1, X, status, 61);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t xa = sbase + s * C::STAGE;
+            int c = 0;
+            for (int it = 0; it < my_tiles && ok; ++it) {
+                const int b = it & 1;
+                if (it >= 2) {                                                     // accumulator b has been read out (tile it - 2)
+                    ok = wwait(&X->acc_empty[b], ((it >> 1) - 1) & 1, X, status, 63);
+                    if (!ok) break;
+                    for (int q = 0; q < 4; ++q) X->next_unit[b][q] = 0;
+                    __threadfence_block();
+                    tc_fence_after_sync();
+                }
+                for (int kt = 0; kt < n_kt && ok; ++kt, ++c) {
+                    const int s = c % C::NST;
+                    ok = wwait(&X->full[s], (c / C::NST) & 1, X, status, 61);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t xa = sbase + s * C::STAGE;
 #pragma unroll
-                for (int t = 0; t < 3; ++t)
+                    for (int t = 0; t < 3; ++t)
 #pragma unroll
-                    for (int k = 0; k < KT / 16; ++k)
-                        mma_bf16(tb, smem_desc(xa + k * 32, 0, C::SBO, C::SWZ),
-                                 smem_desc(xa + X_TILE + t * C::B_TILE + k * 32, 0, C::SBO, C::SWZ), idesc, (kt | t | k) != 0);
-                tc_commit(&X->empty[s]);
+                        for (int k = 0; k < KT / 16; ++k)
+                            mma_bf16(tb + b * WP, smem_desc(xa + k * 32, 0, C::SBO, C::SWZ),
+                                     smem_desc(xa + X_TILE + t * C::B_TILE + k * 32, 0, C::SBO, C::SWZ), idesc, (kt | t | k) != 0);
+                    tc_commit(&X->empty[s]);
+                }
+                if (ok) tc_commit(&X->acc_full[b]);
             }
-            if (ok) tc_commit(&X->done);
         }
     }
     __syncwarp();
 
-    // ================================================================== epilogue: every warp
-    {
-        const int quad = warp & 3, grp = warp >> 2;
+    // ================================================================== epilogue
+    // warps 2 .. 15 take every tile of the CTA; warps 0 and 1, done with their own loops by then, help when the CTA has
+    // a single tile (with several, a wait for the last tile alone could not tell its barrier phase from an earlier one)
+    const int it_first = warp >= 2 ? 0 : (my_tiles == 1 ? 0 : my_tiles);
+    for (int it = it_first; it < my_tiles; ++it) {
+        const int acc = it & 1;
+        const int tok0 = ((int)blockIdx.x + it * (int)gridDim.x) * TM_TOK;
+        const int quad = warp & 3;
         const int rowi = quad * 32 + lane;
         const int tok = tok0 + rowi;
-        const bool ok = __all_sync(0xffffffffu, wwait(&X->done, 0, X, status, 62));
-        const uint32_t tl = tb + ((uint32_t)(quad * 32) << 16);
+        const bool ok = __all_sync(0xffffffffu, wwait(&X->acc_full[acc], (it >> 1) & 1, X, status, 62));
+        if (!ok) break;
+        const uint32_t tl = tb + acc * WP + ((uint32_t)(quad * 32) << 16);
         const bool live = ok && tok < n_tokens;
         const int slot = live && latent ? slots[tok] : -1;
         const bool paged = slot >= 0 && slot < n_pages * PKV_PAGE_TOKENS;
@@ -162,7 +192,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
             // units: R / 16 rotated pairs of blocks (u, R / 16 + u), then the blocks behind 2R one by one
             const int n_pair = R >> 4, n_unit = n_pair + (NB - 2 * n_pair);
             const double pos = live && !phasors ? (double)positions[tok] : 0.0;
-            for (int u = grp; u < n_unit; u += 4) {
+            for (;;) {
+                int u = 0;
+                if (lane == 0) u = atomicAdd(&X->next_unit[acc][quad], 1);
+                u = __shfl_sync(0xffffffffu, u, 0);
+                if (u >= n_unit) break;
                 if (u < n_pair) {
                     uint32_t ra[16], rb[16];
                     tmem_ld16(tl + 16 * u, ra);                         // whole warp: tensor-memory loads are warp-wide
@@ -222,8 +256,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
                     }
                 }
             }
-        } else if (ok && grp == 0) {
-            // real blocks and their imaginary partners do not line up: a thread takes a whole token row through shared memory
+        } else if (ok && warp >= 2 && warp < 6) {
+            // real blocks and their imaginary partners do not line up: a thread takes a whole token row through shared
+            // memory (the CTA has this one tile: the launch makes the grid as large as the tile count)
             float* row = reinterpret_cast<float*>(smem) + (size_t)rowi * (WP + 1);     // the stages are idle now
 #pragma unroll 1
             for (int c0 = 0; c0 < WP; c0 += 16) {
@@ -267,10 +302,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pkv_cache_write_tc_kernel(
                 }
             }
         }
+        // this warp has read what it needs of the accumulator: the issuer may reuse it for the tile after next
+        tc_fence_before_sync();
+        __syncwarp();
+        if (warp >= 2 && lane == 0) mbar_arrive(&X->acc_empty[acc]);
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tb, 256);
+    if (warp == 1) tmem_dealloc(tb, 2 * WP);
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 g_encode_w = nullptr;
@@ -303,7 +342,17 @@ int launch_write_tc(const CUtensorMap& xmap, const CUtensorMap& bmap, const pkv_
     constexpr int smem = WCfg<WP>::SMEM;
     static pkv_attr_flags attr;                          // per instantiation and device
     PKV_CUDA_TRY(pkv_set_max_smem(kern, smem, attr));
-    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3((n + TM_TOK - 1) / TM_TOK), dim3(NTHREADS), smem, st, xmap, bmap, n, L->d_model,
+    // one CTA per SM at most, each taking every gridDim-th tile; a layer whose real and imaginary blocks do not line up
+    // needs the stages for its epilogue and gets a CTA per tile
+    const int n_tiles = (n + TM_TOK - 1) / TM_TOK;
+    int grid = n_tiles;
+    if ((L->R & 15) == 0) {
+        int dev = 0, sms = 0;
+        PKV_CUDA_TRY(cudaGetDevice(&dev));
+        PKV_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (sms > 0 && grid > sms) grid = sms;
+    }
+    PKV_CUDA_TRY(pkv_launch_chained(kern, dim3(grid), dim3(NTHREADS), smem, st, xmap, bmap, n, n_tiles, L->d_model,
                                     2 * L->R + L->R_s, L->R, pos, (const float2*)ph, L->head_dim / 2, slots, L->freq_dev,
                                     L->inv_freq_dev, L->attn_scale, pkv_second_of(L), pkv_scale_round_up_mode(),
                                     C ? C->latent_dev : nullptr, C ? C->n_pages : 0, latent_out, status));

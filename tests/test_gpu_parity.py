@@ -624,6 +624,34 @@ def test_attention_behind_chunk_write_and_prologue():
     assert not torch.equal(early[0, 0], early[1, 0])                    # the rounds really differ (sequence 0 holds the chunk)
 
 
+@pytest.mark.parametrize("config", ["cfg2", "cfg5"])
+def test_chunk_write_of_many_tiles_equals_small_chunks(config):
+    """More 128-token tiles than the GPU has SMs: a CTA of the tensor-core write then takes several tiles, and the
+    epilogue of one runs under the MMAs of the next. Same pages, bit for bit, as the same tokens written 4096 at a
+    time (a CTA per tile), the ragged last tile included."""
+    spec = synth.make_layer(config, 0)
+    pk = PhasorKey.from_spec(spec, device="cuda")
+    pk.set_second(0.02)
+    n = 148 * 128 * 2 + 300
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn((n, pk.d_model), generator=g, device="cuda").to(torch.bfloat16)
+    pos = torch.arange(n, dtype=torch.int32, device="cuda") + 1000
+    caches, rows = [], []
+    for chunk in (n, 4096):
+        cache = pk.new_cache(1, n, with_v=False)
+        out = torch.zeros((n, pk.cache_width), device="cuda")
+        slots = cache.slots(torch.zeros(n, dtype=torch.int32, device="cuda"), torch.arange(n, dtype=torch.int32, device="cuda"))
+        for t0 in range(0, n, chunk):
+            t1 = min(n, t0 + chunk)
+            pk.write_paged(cache, x[t0:t1], pos[t0:t1], slots[t0:t1], latent_out=out[t0:t1])
+        torch.cuda.synchronize()
+        assert int(pk._dev["status"].abs().sum()) == 0
+        caches.append(cache), rows.append(out)
+    assert float(rows[0].abs().max()) > 0
+    assert torch.equal(rows[0], rows[1])
+    assert torch.equal(caches[0].latent, caches[1].latent)
+
+
 # ------------------------------------------------------------------------------------------------
 # tensor-core kernel (tcgen05 block-scaled NVFP4 scores, bf16 P.V): same checks, same tolerances
 # ------------------------------------------------------------------------------------------------
