@@ -63,3 +63,22 @@ def test_vq_cache_refuses_the_cuda_core_kernel():
     sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws, operand=False)
     with pytest.raises(_lib.PhasorKVError, match="unsupported"):
         sc.pk.attend_step(sc.cache, ws, simt=True)
+
+
+def test_vq_logits_dump_and_packed_triples():
+    """With quantised V the attention still dumps its logits (the softmax reads the scores from tensor memory in
+    chunks there) and hands out merged (o, m, l) triples for token sharding: both against the oracle."""
+    sc = Scenario("cfg2", seqlens=(700, 129), gain=16.0, pos0=5000, v_bits=3)
+    ws = sc.pk.workspace(sc.B, 3)
+    S = torch.zeros((sc.B, sc.spec.n_q, max(sc.seqlens)), device="cuda")
+    sc.pk.absorb_step(sc.q.cuda(), sc.qpos.cuda(), ws)
+    sc.pk.attend_step(sc.cache, ws, scores_out=S, packed_out=ws.packed, after_absorb=True)
+    out = torch.empty_like(ws.out)
+    sc.pk.merge_gathered(ws.packed[None].contiguous(), out)
+    torch.cuda.synchronize()
+    assert int(ws.status.abs().sum()) == 0
+    for b, T in enumerate(sc.seqlens):
+        rows, _, _ = sc.cache.read_vq(sc.slots_of(b))
+        _, S_ref, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b), V=rows.cpu())
+        assert rel(S[b, :, :T].cpu(), S_ref) < 1e-3, (b, T)
+        assert rel(out[b].cpu(), O_ref) < OUT_TOL, (b, T)
