@@ -51,9 +51,10 @@ constexpr int P_BYTES = 2 * PKV_PAGE_TOKENS * NQ * 2;          // softmax weight
 constexpr int NTHREADS = 7 * 32;              // with V: producers, MMA issuer, one softmax group
 constexpr int NTHREADS_SCORES = 20 * 32;      // scores only: K producer, three MMA issuers (page i: issuer and score buffer i % 3), four
                                               // softmax groups that split the heads of every page
-constexpr int NTHREADS_VQ = 20 * 32;          // quantised V: warps 0-2 as always, 3 second P.V issuer, 4-11 softmax (two groups that split
-                                              // the kv heads), 12-19 converters (two per tile). Each role's chain of dependent instructions
-                                              // is what bounds a page, so the roles are spread over as many warps as the layout allows
+constexpr int NTHREADS_VQ = 21 * 32;          // quantised V: warps 0, 1 producers, 2 scores issuer, 3 and 20 P.V issuers (odd / even kv heads),
+                                              // 4-11 softmax (two groups that split the kv heads), 12-19 converters (two per tile). Each
+                                              // role's chain of dependent instructions is what bounds a page, so the roles are spread
+                                              // over as many warps as the layout allows
 template <bool WV, bool VQ> constexpr int n_threads() { return VQ ? NTHREADS_VQ : (WV ? NTHREADS : NTHREADS_SCORES); }
 constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logits
 constexpr uint32_t WAIT_LIMIT = 1u << 19;     // probes of a bounded wait (a probe may itself block for microseconds): a second or two, then give up
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 }
             }
         }
-    } else if (warp == 2 || warp == 1 || ((VQ || !WV) && warp == 3)) {
+    } else if (warp == 2 || warp == 1 || ((VQ || !WV) && warp == 3) || (VQ && warp == 20)) {
         // ================================================================== MMA issuer
         // One thread issues every tcgen05 instruction of its pages; what bounds it is the latency of its own
         // instruction chain (two satisfied barrier waits, 4 + 4 tcgen05 issues of ~75 cycles, two commits:
@@ -450,8 +451,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // softmax are what a page costs, so there are three of each: warp 2 takes the pages 0, 3, 6 .., warp 1 (which the
         // V stream leaves idle) 1, 4, 7 .., warp 3 the rest; each feeds the softmax group of the same number through a
         // score buffer of its own.
-        // With quantised V a page's bytes last a third as long, and the P.V issue chain (8 MMAs, a wait and a commit per
-        // kv head) becomes the longest link: warp 3 then issues the P.V of the odd kv heads, warp 2 scores + even heads.
+        // With quantised V a page's bytes last a third as long, and the issue chains become the longest link: warp 2 then
+        // issues the scores alone (a P.V issuer that waits for a converted tile must not hold up the next page's scores:
+        // 116 -> 109 us per layer), warp 20 the P.V of the even kv heads, warp 3 of the odd ones.
         constexpr int PV_STEP = VQ ? 2 : 1;
         if (lane == 0) {
             const int first = WV ? 0 : (warp == 2 ? 0 : (warp == 1 ? 1 : 2));
@@ -459,7 +461,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
             const uint32_t sfb_tm = tb + TM_SFB + 16u * (uint32_t)first;
             constexpr uint32_t idesc_s = idesc_nvfp4(128, PKV_QUERY_TERMS * NQ);
             constexpr uint32_t idesc_o = VQ ? idesc_f8(128, NPV, true, true, 0u, 1u) : idesc_bf16(128, 16, true, false);   // V: E4M3, weights: E5M2
-            const bool pv_only = VQ && warp == 3;
+            // quantised V: warp 2 issues the scores only, so that a P.V issuer waiting for a converted tile never holds up
+            // the scores of the next page; warp 20 takes the P.V of the even kv heads, warp 3 of the odd ones
+            const bool pv_only = VQ && (warp == 3 || warp == 20);
             bool ok = pv_only || wait_or_abort(&X->q_full, 0, X, status, 30);
             if (warp == 2) PKV_TL(7);
             if (ok && !pv_only) {
@@ -472,7 +476,7 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 const int pb = i & 1;
                 if (!wait_or_abort(&X->p_full[pb], (i >> 1) & 1, X, status, 31)) return false;
                 tc_fence_after_sync();
-                for (int g = pv_only ? 1 : 0; g < NKV; g += PV_STEP) {
+                for (int g = (VQ && warp == 3) ? 1 : 0; g < NKV; g += PV_STEP) {
                     const int j = i * NKV + g, s = j % C::NVS;
                     uint64_t* const empty_bar = &X->v_empty[s];
                     if (!wait_or_abort(&X->v_full[s], (j / C::NVS) & 1, X, status, 32)) return false;
@@ -540,13 +544,13 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
                 tc_commit(&X->k_empty[s]);
                 tc_commit(&X->s_full[buf]);
                 if (i + STEP >= P) PKV_TL(9);
-                if (with_v && i >= 1) ok = do_pv(i - 1);
+                if (with_v && !VQ && i >= 1) ok = do_pv(i - 1);
                 s += STEP;
                 if (s >= nks) { s -= nks; k_phase ^= 1u; }
                 buf += STEP;
                 if (buf >= NSB) { buf -= NSB; ++s_round; }
             }
-            if (ok && with_v && !pv_only) do_pv(P - 1);
+            if (ok && with_v && !VQ && !pv_only) do_pv(P - 1);
         }
     } else if (VQ && warp >= 12) {
         // ================================================================== V converter (quantised V pages)
