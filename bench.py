@@ -243,7 +243,7 @@ class Stack:
             elif fused:                                               # newest token's write + absorb: one launch
                 pk.prologue_step(cache, self.x_new[l], self.wpos, self.wslots[l], self.q[l], self.qpos, ws, v=self.v_new[l],
                                  signal=self.polled and chained and not self.simt)
-                n += 2 if self.v_bits else 1                          # quantised V pages: their own writer launch
+                n += 1
             else:
                 if write:
                     pk.write_paged(cache, self.x_new[l], self.wpos, self.wslots[l], v=self.v_new[l], scratch=ws.wscratch)

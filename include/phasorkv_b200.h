@@ -270,8 +270,9 @@ int pkv_absorb_rows_f64(const double* A_re_dev, const double* A_im_dev, const do
  * quantiser's bits of the rows this call forms). The single launch needs batch <= PKV_SMALL_WRITE_TOKENS, R a
  * multiple of 16 and d_model a multiple of 32 and at most 16384; otherwise the two separate launches
  * are made (scratch_dev, optional, is only used then). latent_out_dev, qabs_out_dev, qop_out_dev,
- * v_rows_dev are optional as in the separate calls. q_dev NULL: the write alone (the queries are then
- * absorbed by pkv_decode_attn_q). */
+ * v_rows_dev are optional as in the separate calls (with quantised V pages, cache->v_bits != 0, the value rows
+ * are quantised and stored by the same launch, bit for bit as pkv_vq_write does). q_dev NULL: the write alone
+ * (the queries are then absorbed by pkv_decode_attn_q). */
 int pkv_decode_prologue(const pkv_layer_t* layer, const pkv_cache_t* cache, const void* x_dev, int32_t x_dtype,
                         const int32_t* write_positions_dev, const int32_t* slots_dev, const void* v_rows_dev,
                         const float* q_dev, const int32_t* query_positions_dev, int32_t batch,

@@ -15,6 +15,7 @@
 //
 // Absorb role: the grid rows behind the column tiles run pkv_absorb_impl::body unchanged.
 #include "pkv_absorb.cuh"
+#include "pkv_vq.cuh"
 
 #include <cooperative_groups.h>
 
@@ -53,6 +54,8 @@ struct WriteArgs {
     float* latent_out;            // [n_tokens][W] or null
     const uint4* v_rows;          // [n_tokens][v_vecs] or null
     uint4* v_pool;
+    uint8_t* vq_pool;             // quantised V pages instead (v_bits = 3 or 2): the rows are quantised here
+    int v_bits;
     int v_vecs, n_kv;
     int n_tiles;                  // grid rows of the write role: R / 16 pair tiles, then (WP - 2R) / 16 plain tiles
 };
@@ -123,7 +126,16 @@ __device__ __forceinline__ void write_role(const WriteArgs& A, float* sm) {
             (void)t;
             if (ch == 0) {
                 // while the tiles are in flight: the V rows of this CTA's tokens, and the phasors it will need
-                if (ct == 0 && A.v_rows) {
+                if (ct == 0 && A.v_rows && A.vq_pool) {              // a warp per (token, kv head) row
+                    for (int r = tid >> 5; r < TPR * A.n_kv; r += NT / 32) {
+                        const int tok = t0 + ks * TPR + r / A.n_kv;
+                        if (tok >= n_tokens) break;
+                        const int slot = A.slots[tok];
+                        if (slot < 0 || slot >= A.n_pages * PKV_PAGE_TOKENS) continue;
+                        const uint2 u = reinterpret_cast<const uint2*>(A.v_rows)[((size_t)tok * A.n_kv + r % A.n_kv) * 32 + (tid & 31)];
+                        pkv_vq_store_row(u, tid & 31, slot, r % A.n_kv, A.n_kv, A.v_bits, A.vq_pool);
+                    }
+                } else if (ct == 0 && A.v_rows) {
                     for (int i = tid; i < TPR * A.v_vecs; i += NT) {
                         const int tok = t0 + ks * TPR + i / A.v_vecs;
                         if (tok >= n_tokens) break;
@@ -327,8 +339,12 @@ extern "C" int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cach
                        layer->head_dim / 2 <= pkv_absorb_impl::MAX_H && !(layer->head_dim & 1) &&
                        (!qop_out_dev || (layer->n_q * PKV_QUERY_TERMS == 128 && !(((uintptr_t)qop_out_dev) & 1023u)));
     if (!fused) {                                        // same results from the separate launches
+        if (cache->v_bits && v_rows_dev) {               // quantised V pages have their own writer
+            st = pkv_vq_write(cache, v_rows_dev, slots_dev, batch, stream);
+            if (st) return st;
+        }
         st = pkv_cache_write(layer, cache, x_dev, x_dtype, write_positions_dev, nullptr, slots_dev, batch, latent_out_dev,
-                             scratch_dev, v_rows_dev, status_dev, stream);
+                             scratch_dev, cache->v_bits ? nullptr : v_rows_dev, status_dev, stream);
         if (st || !q_dev) return st;
         return pkv_absorb_sync(layer, q_dev, query_positions_dev, nullptr, batch, qabs_out_dev, qop_out_dev, qsync_dev, stream);
     }
@@ -337,9 +353,12 @@ extern "C" int pkv_decode_prologue_sync(const pkv_layer_t* layer, const pkv_cach
     Wa.positions = write_positions_dev; Wa.slots = slots_dev; Wa.freq = layer->freq_dev; Wa.inv_freq = layer->inv_freq_dev;
     Wa.attn_scale = layer->attn_scale; Wa.second = pkv_second_of(layer); Wa.scale_up = pkv_scale_round_up_mode();
     Wa.latent = cache->latent_dev; Wa.n_pages = cache->n_pages; Wa.latent_out = latent_out_dev;
-    const bool with_v = cache->v_dev && v_rows_dev;
+    const bool with_vq = cache->v_bits != 0 && cache->vq_dev && v_rows_dev && cache->head_dim == 128;
+    const bool with_v = (cache->v_dev && v_rows_dev && !cache->v_bits) || with_vq;
     Wa.v_rows = with_v ? reinterpret_cast<const uint4*>(v_rows_dev) : nullptr;
-    Wa.v_pool = with_v ? reinterpret_cast<uint4*>(cache->v_dev) : nullptr;
+    Wa.v_pool = with_v && !with_vq ? reinterpret_cast<uint4*>(cache->v_dev) : nullptr;
+    Wa.vq_pool = with_vq ? reinterpret_cast<uint8_t*>(cache->vq_dev) : nullptr;
+    Wa.v_bits = cache->v_bits;
     Wa.v_vecs = with_v ? cache->n_kv * cache->head_dim * 2 / 16 : 0;
     Wa.n_kv = cache->n_kv;
     Wa.n_tiles = layer->R / PC + (WP - 2 * layer->R) / PC;

@@ -459,10 +459,7 @@ class PhasorKey:
         self._need_inv_freq("prologue_step")
         L = self._layer()
         x = self._x(x)
-        if v is not None and cache.v_bits:                              # quantised V pages have their own writer
-            cache.write_v(v, slots)
-            v = None
-        if v is not None:
+        if v is not None:                                               # (quantised V pages: the rows are quantised by the same launch)
             v = v.to(torch.bfloat16).contiguous()
         _lib.check(_lib.load().pkv_decode_prologue_sync(ctypes.byref(L), ctypes.byref(cache.c), _lib.ptr(x), self._xdt(x),
                                                         _lib.ptr(write_positions), _lib.ptr(slots), _lib.ptr(v), _lib.ptr(q),

@@ -82,3 +82,30 @@ def test_vq_logits_dump_and_packed_triples():
         _, S_ref, O_ref = sc.oracle_scores_and_output(b, sc.dequantised(b), V=rows.cpu())
         assert rel(S[b, :, :T].cpu(), S_ref) < 1e-3, (b, T)
         assert rel(out[b].cpu(), O_ref) < OUT_TOL, (b, T)
+
+
+@pytest.mark.parametrize("config,bits", [("cfg2", 3), ("cfg5", 2), ("cfg3", 3)])
+def test_prologue_quantises_the_value_rows_like_the_writer(config, bits):
+    """The step prologue stores the newest tokens' value rows into quantised V pages itself: same codes and
+    scales as the stand-alone writer (cfg3, R = 120, goes through the entry point's separate launches)."""
+    sc = Scenario(config, seqlens=(5,), pos0=700, v_bits=bits)
+    pk, n = sc.pk, 5
+    x, v = sc.x[0].cuda(), sc.v[0].cuda()
+    wpos = sc.pos[0].to(torch.int32).cuda()
+    slots = sc.slots_of(0)
+    q = torch.randn((n, sc.spec.n_q, sc.spec.head_dim), generator=torch.Generator().manual_seed(3)).cuda()
+    caches = []
+    for fused in (False, True):
+        cache = pk.new_cache(1, n, v_bits=bits)
+        ws = pk.workspace(n, 1)
+        if fused:
+            pk.prologue_step(cache, x, wpos, slots, q, (wpos + 1).contiguous(), ws, v=v)
+        else:
+            pk.write_paged(cache, x, wpos, slots, v=v, scratch=ws.wscratch)
+        torch.cuda.synchronize()
+        caches.append(cache)
+    a, b = caches[0].read_vq(slots), caches[1].read_vq(slots)
+    assert float(a[0].abs().max()) > 0
+    for u, w in zip(a, b):
+        assert torch.equal(u, w)
+    assert torch.equal(caches[0].vq, caches[1].vq)
