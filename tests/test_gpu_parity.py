@@ -564,27 +564,38 @@ def test_attention_polls_operand_ready_counters(producer):
     assert torch.equal(a[..., -2:], ws.packed[..., -2:]) and int(ws.qsync.abs().sum()) == 0
 
 
-def test_polling_attention_gives_up_when_nothing_signals():
+@pytest.mark.parametrize("v_bits,scores_only", [(0, False), (3, False), (0, True)])
+def test_polling_attention_gives_up_when_nothing_signals(v_bits, scores_only):
     """A polled attention launch whose producer never raises the counters: the bounded poll runs out, status says
-    so (1 = a wait gave up, where = 11: the operand), the outputs are zero (every CTA leaves the neutral partial),
-    the counters are clean again, and the next, properly signalled round is right."""
-    sc = Scenario("cfg2", seqlens=(200, 64))
+    so (1 = a wait gave up; where = 11: the operand poll, or 30 / 40: a role that waits for the operand), the outputs
+    are zero (every CTA leaves the neutral partial), the counters are clean again, and the next, properly signalled
+    round is right. Every instantiation of the kernel (bf16 V, quantised V, scores only) has its own set of roles."""
+    sc = Scenario("cfg2", seqlens=(200, 64), v_bits=v_bits)
     pk = sc.pk
     ws = pk.workspace(sc.B, 2)
     q, qpos = sc.q.cuda(), sc.qpos.cuda()
+    S = torch.zeros((sc.B, sc.spec.n_q, 200), device="cuda")
+    kw = dict(scores_only=True, scores_out=S) if scores_only else {}
     pk.absorb_step(q, qpos, ws)                                           # no signal
     out = torch.ones((sc.B, sc.spec.n_q, sc.spec.head_dim), device="cuda")
-    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True)
+    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True, **kw)
     torch.cuda.synchronize()
-    assert int(ws.status[0]) == 1 and int(ws.status[1]) in (11, 30)      # the poll, or the role that waits for the operand it feeds
+    assert int(ws.status[0]) == 1 and int(ws.status[1]) in (11, 30, 40)  # the poll, or a role that waits for the operand it feeds
     assert float(out.abs().max()) == 0.0 and int(ws.qsync.abs().sum()) == 0
     ws.status.zero_()
+    S.zero_()
     pk.absorb_step(q, qpos, ws, signal=True)
-    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True)
+    pk.attend_step(sc.cache, ws, out=out, after_absorb=True, polled=True, **kw)
+    got = S.clone()
     ref = torch.zeros_like(out)
-    pk.attend_step(sc.cache, ws, out=ref)
+    S.zero_()
+    pk.attend_step(sc.cache, ws, out=ref, **kw)
     torch.cuda.synchronize()
-    assert int(ws.status.abs().sum()) == 0 and torch.equal(out, ref) and float(ref.abs().max()) > 0
+    assert int(ws.status.abs().sum()) == 0 and torch.equal(out, ref)
+    if scores_only:
+        assert torch.equal(got, S) and float(S.abs().max()) > 0
+    else:
+        assert float(ref.abs().max()) > 0
 
 
 def test_attention_behind_chunk_write_and_prologue():
