@@ -50,9 +50,9 @@ class LayerDecodeState:
     cached, the next token of b is written at position ``lengths[b]`` and attends to positions
     ``0 .. lengths[b]``."""
 
-    def __init__(self, pk: PhasorKey, batch: int, max_tokens: int, write_chunk: int = 4096):
+    def __init__(self, pk: PhasorKey, batch: int, max_tokens: int, write_chunk: int = 4096, v_bits: int = 0):
         self.pk, self.batch, self.max_tokens, self.write_chunk = pk, batch, max_tokens, write_chunk
-        self.cache = pk.new_cache(batch, max_tokens)
+        self.cache = pk.new_cache(batch, max_tokens, v_bits=v_bits)     # v_bits 3 / 2: V as per-token low-bit codes
         self.ws = pk.workspace(batch, pk.default_splits(batch, max_tokens))
         self.seq = torch.arange(batch, dtype=torch.int32, device=pk.device)
         self.lengths = [0] * batch                          # tokens cached per sequence (host copy of cache.seqlens)
@@ -134,9 +134,10 @@ def _patched_forward(attn, state_of, original):
 
 class PhasorKeyPatch:
     def __init__(self, tag: str = "phasor.nvfp4", bits_v: float = 16.0, install_forward: bool = False,
-                 max_tokens: int = 4096):
+                 max_tokens: int = 4096, v_bits: int = 0):
         self.tag = tag
         self.bits_v = bits_v
+        self.v_bits = v_bits              # 0: bf16 V pages; 3 / 2: the reference's per-token tiers (phasorkv/kernels/nvfp4.py:58-67)
         self.install_forward = install_forward
         self.max_tokens = ((max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS
         self.layer_stats = {}
@@ -169,7 +170,8 @@ class PhasorKeyPatch:
         had = (getattr(attn, "phasor_key", None), getattr(attn, "phasor_layer", None))
         attn.phasor_key, attn.phasor_layer = pk, i
         self.keys[i] = pk
-        self.layer_stats[i] = dict(bits_k=NVFP4_BITS * pk.cache_width, bits_v=self.bits_v * n_kv * d,
+        bits_v = (self.v_bits * d + 16) * n_kv if self.v_bits else self.bits_v * n_kv * d      # codes + one bf16 scale per (token, kv head)
+        self.layer_stats[i] = dict(bits_k=NVFP4_BITS * pk.cache_width, bits_v=bits_v,
                                    width=pk.cache_width, R=pk.R, R_s=pk.R_s)
 
         original = None
@@ -181,7 +183,7 @@ class PhasorKeyPatch:
             def state_of(batch, i=i, pk=pk):
                 st = self.states.get(i)
                 if st is None or st.batch != batch:
-                    st = self.states[i] = LayerDecodeState(pk, batch, max_tokens)
+                    st = self.states[i] = LayerDecodeState(pk, batch, max_tokens, v_bits=self.v_bits)
                 return st
             attn.forward = _patched_forward(attn, state_of, original)
 

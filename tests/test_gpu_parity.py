@@ -1038,8 +1038,10 @@ def test_mean_direction_split_through_the_kernels():
     assert rel(ws.out[0].cpu(), po.attend(S_ref, v, spec.n_kv, spec.head_dim)) < OUT_TOL
 
 
-def test_patched_layer_state_keeps_one_length_per_sequence():
-    """A ragged batch through the decode state of a patched layer (prefill right-padded with per-sequence
+@pytest.mark.parametrize("v_bits", [0, 3])
+def test_patched_layer_state_keeps_one_length_per_sequence(v_bits):
+    """A ragged batch through the decode state of a patched layer (V pages in bf16, or as per-token 3-bit codes: the
+    oracle then attends over the dequantised value rows) (prefill right-padded with per-sequence
     token counts, as the reference's runner passes them in attn.kv_lengths, phasorkv/runner.py:94-99; then two
     decode steps): every sequence is written and attended at its own positions, so each gives what it gives
     alone in a batch of one, and what the oracle gives."""
@@ -1055,7 +1057,7 @@ def test_patched_layer_state_keeps_one_length_per_sequence():
     q = torch.randn((B, steps, spec.n_q, spec.head_dim), generator=g).cuda()
 
     def run(rows):
-        st = LayerDecodeState(pk, len(rows), 512)
+        st = LayerDecodeState(pk, len(rows), 512, v_bits=v_bits)
         st.calibrated = True                                  # keep the tensor scale set above
         xs = torch.stack([x[b, :T] for b in rows]); vs = torch.stack([v[b, :T] for b in rows])
         st.prefill(xs, vs, lengths=[lens[b] for b in rows])
