@@ -216,20 +216,25 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
     pkv_grid_launch_dependents();
 
     // ---- prologue that touches no global memory: barriers, tensor memory
-    if (tid == 0) {
+    if (warp == 0) {                                 // lane s initialises entry s of every barrier array (62 barriers: ~0.3 us for one thread)
+        if (lane == 0) {
 #ifdef PKV_WAITPROF
-        for (int k = 0; k < 64; ++k) X->waited[k] = 0;
+            for (int k = 0; k < 64; ++k) X->waited[k] = 0;
 #endif
-        mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
-        for (int s = 0; s < NK_MAX; ++s) { mbar_init(&X->k_full[s], 1); mbar_init(&X->k_empty[s], 1); }
+            mbar_init(&X->q_full, inline_q ? pkv_absorb_impl::TILE_THREADS : 1);
+            mbar_init(&X->sm_bar, WV ? (VQ ? 256 : 128) : 512);
+            X->abort_flag = 0;
+        }
+        static_assert(NK_MAX <= 32 && NV_BARS <= 32 && NVR <= 32 && NSB_S <= 32, "a lane per barrier of an array");
+        if (lane < NK_MAX) { mbar_init(&X->k_full[lane], 1); mbar_init(&X->k_empty[lane], 1); }
         // quantised V: two converter warps per tile, 256 softmax threads, two P.V issuers
-        for (int s = 0; s < NV_BARS; ++s) { mbar_init(&X->v_full[s], VQ ? 2 : 1); mbar_init(&X->v_empty[s], 1); }
-        for (int s = 0; s < NVR; ++s) { mbar_init(&X->vr_full[s], 1); mbar_init(&X->vr_empty[s], 2); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&X->sc_full[s], 1); mbar_init(&X->sc_empty[s], 256); }
-        for (int s = 0; s < NSB_S; ++s) { mbar_init(&X->s_full[s], 1); mbar_init(&X->s_empty[s], WV ? (VQ ? 256 : 128) : 512); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&X->p_full[s], VQ ? 256 : 128); mbar_init(&X->pv_done[s], VQ ? 2 : 1); }
-        mbar_init(&X->sm_bar, WV ? (VQ ? 256 : 128) : 512);
-        X->abort_flag = 0;
+        if (lane < NV_BARS) { mbar_init(&X->v_full[lane], VQ ? 2 : 1); mbar_init(&X->v_empty[lane], 1); }
+        if (lane < NVR) { mbar_init(&X->vr_full[lane], 1); mbar_init(&X->vr_empty[lane], 2); }
+        if (lane < 2) {
+            mbar_init(&X->sc_full[lane], 1); mbar_init(&X->sc_empty[lane], 256);
+            mbar_init(&X->p_full[lane], VQ ? 256 : 128); mbar_init(&X->pv_done[lane], VQ ? 2 : 1);
+        }
+        if (lane < NSB_S) { mbar_init(&X->s_full[lane], 1); mbar_init(&X->s_empty[lane], WV ? (VQ ? 256 : 128) : 512); }
         fence_barrier_init();
     }
     if (warp == 2) tmem_alloc(&X->tmem_base, TM_COLS);
