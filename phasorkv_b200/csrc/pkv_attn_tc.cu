@@ -13,9 +13,11 @@
 //   warps 3-6  softmax    : one token row (TMEM lane) per thread; adds the four term columns of a head; online
 //                           base-2 softmax whose reference maximum only moves when a tile exceeds it by 2^8,
 //                           P to smem as hi + lo bf16, and the rare rescale of the O accumulators in TMEM
-// Scores-only launches (no V) are a separate instantiation with eleven warps: warp 1 becomes a second MMA
-// issuer and warps 7-10 a second softmax group (even / odd pages). A further instantiation absorbs raw
-// queries itself (pkv_absorb_impl::body_tile) instead of loading the operand.
+// Scores-only launches (no V) are a separate instantiation with 20 warps: warps 1-3 issue the MMAs (page i belongs to
+// issuer and score buffer i % 3) and warps 4-19 are four softmax groups that split the heads of every page. Quantised V
+// pages (per-token low-bit codes) have a third instantiation with 21 warps: converter warps turn code tiles into E4M3
+// operands, P.V runs as kind::f8f6f4 with the token scales folded into the weights. A further instantiation absorbs
+// raw queries itself (pkv_absorb_impl::body_tile) instead of loading the operand.
 // Stages are handed over through mbarriers; every wait is bounded and a give-up is recorded in
 // `status` while all roles unwind, free TMEM and return.
 #include "pkv_absorb.cuh"
@@ -60,8 +62,8 @@ constexpr float RESCALE_THRESHOLD = 8.0f;                      // in base-2 logi
 constexpr uint32_t WAIT_LIMIT = 1u << 19;     // probes of a bounded wait (a probe may itself block for microseconds): a second or two, then give up
 
 // tensor memory columns
-// Score buffers (pages in flight between MMA and softmax): two. In scores-only mode buffer = page parity, so
-// each MMA issuer shares its buffer and barriers with exactly one softmax group (a barrier whose phases are
+// Score buffers (pages in flight between MMA and softmax): two; three in scores-only mode, where buffer = page % 3 =
+// issuer, so that a buffer's barriers are waited for by one issuer, phase after phase (a barrier whose phases are
 // waited for by two threads in turn could be seen a whole phase early by the one that runs ahead).
 constexpr int NSB_V = 2, NSB_S = 3;
 constexpr uint32_t TM_S = 0;          // NSB x 128 : scores, tokens x (4 residual terms x 32 heads)
@@ -110,7 +112,7 @@ struct Extra {                       // lives at X_OFF
     volatile int abort_flag;
     float wmax[2][4][NQ];
     int wflag[2][8];
-    float lsum[NSB_S][4][NQ];        // [softmax group][warp][head]
+    float lsum[NSB_S][4][NQ];        // [0][warp quarter][head] (the leading index is left from groups that split the pages)
     float mfin[NSB_S][4][NQ];
 };
 
@@ -452,10 +454,9 @@ __global__ void __launch_bounds__(n_threads<WV, VQ>(), 1) pkv_attn_tc_kernel(
         // ================================================================== MMA issuer
         // One thread issues every tcgen05 instruction of its pages; what bounds it is the latency of its own
         // instruction chain (two satisfied barrier waits, 4 + 4 tcgen05 issues of ~75 cycles, two commits:
-        // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V the chains of issuer and
-        // softmax are what a page costs, so there are three of each: warp 2 takes the pages 0, 3, 6 .., warp 1 (which the
-        // V stream leaves idle) 1, 4, 7 .., warp 3 the rest; each feeds the softmax group of the same number through a
-        // score buffer of its own.
+        // ~1600 cycles per page). With V that is a fifth of a page's HBM time. Without V the issuer's chain is what a page
+        // costs, so there are three: warp 2 takes the pages 0, 3, 6 .., warp 1 (which the V stream leaves idle) 1, 4, 7 ..,
+        // warp 3 the rest, each with a score buffer of its own; all softmax groups read every buffer (a part of the heads each).
         // With quantised V a page's bytes last a third as long, and the issue chains become the longest link: warp 2 then
         // issues the scores alone (a P.V issuer that waits for a converted tile must not hold up the next page's scores:
         // 116 -> 109 us per layer), warp 20 the P.V of the even kv heads, warp 3 of the odd ones.
