@@ -402,7 +402,9 @@ def run_b200(args):
             "metric": "decode tokens/s (token-sharded B=4, T=131072, %d layers)" % L,
             "value": sh["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": sh["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; bf16 V", "data": "synthetic",
+            "dtype": "nvfp4 latent (e2m1 x ue4m3) x nvfp4 query, fp32 accumulate; %s"
+                     % ("bf16 V" if not st.v_bits else "V as per-token %d-bit codes + bf16 scale per (token, kv head)" % st.v_bits),
+            "data": "synthetic",
             "config": {"workload": sh["workload"], "algo": args.algo, "parallelism": "token-sharded x%d" % world,
                        "l2": "inputs larger than L2 (%.2f GB streamed per GPU per layer)" % (sh["bytes_per_gpu_per_layer"] / 1e9)},
             "roofline": sh.pop("roofline"), "e2e": sh.pop("e2e"), "gpu_launches": sh["gpu_launches"], "clocks": clocks,
@@ -706,7 +708,7 @@ def run_sharded(st, args, dist, world, want_e2e=False):
         ms = timed(fn, args.steps, args.warmup, dist)
         torch.cuda.synchronize()
         out_timed = out.clone()                                     # what the timed replays left behind
-        per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.n_kv * st.d * 2)
+        per_gpu_bytes = B4 * Tl * (st.W // 2 + st.W // 16 + st.bytes_v_per_token())
         res = {"workload": "cfg4: B=4, T=131072, tokens split evenly over %d GPU(s), %d layers" % (world, L),
                "value": round(B4 / (ms * 1e-3), 2), "unit": "tokens/s", "ms_per_step": round(ms, 4), "n_gpus": world,
                "us_per_layer": round(ms * 1e3 / L, 2),
@@ -742,26 +744,29 @@ def run_sharded(st, args, dist, world, want_e2e=False):
             # tensor-core result of the timed step (tolerance of the attention output: 2e-3)
             ws_s = pk0.workspace(B4, max(1, min(pages, (sms * 3) // B4)))
             worst = 0.0
+            # (quantised V pages are read by the tensor-core kernel only: the second opinion is then that kernel with
+            # another number of token splits, i.e. other reference maxima and another merge)
+            by_simt = not st.v_bits
             for l in check_layers:
                 pkl, cache = st.layers[l], st.caches[l]
-                pkl.absorb_step(st.q[l, :B4], qpos, ws_s, operand=False)
+                pkl.absorb_step(st.q[l, :B4], qpos, ws_s, operand=not by_simt)
                 o_s = torch.empty((B4, st.n_q, st.d), dtype=torch.float32, device=dev)
                 if world == 1:
-                    pkl.attend_step(cache, ws_s, simt=True, out=o_s)
+                    pkl.attend_step(cache, ws_s, simt=by_simt, out=o_s)
                 else:
-                    pkl.attend_step(cache, ws_s, simt=True, packed_out=ws_s.packed)
+                    pkl.attend_step(cache, ws_s, simt=by_simt, packed_out=ws_s.packed)
                     dist.all_gather_into_tensor(gathered, ws_s.packed)
                     pkl.merge_gathered(gathered, o_s)
                 torch.cuda.synchronize()
                 worst = max(worst, relerr(out_timed[l], o_s))
-            chk["rel_tc_vs_simt"] = worst
+            chk["rel_tc_vs_simt" if by_simt else "rel_tc_vs_other_split"] = worst
             ok = ok and worst <= 2e-3
         if dist is not None:                                        # every rank must agree that it is fine
             flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             ok = bool(int(flag.item()))
         chk["ok"] = ok
-        chk["bounds"] = {"rel_p2p_vs_nccl": 1e-5, "rel_tc_vs_simt": 2e-3, "status": "all zero"}
+        chk["bounds"] = {"rel_p2p_vs_nccl": 1e-5, "rel_tc_vs_simt": 2e-3, "rel_tc_vs_other_split": 2e-3, "status": "all zero"}
         res["check"] = chk
         if not ok:
             res["failed"] = "correctness check of the token-sharded step failed: value withdrawn"
